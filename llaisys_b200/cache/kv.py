@@ -1,0 +1,159 @@
+"""Device storage of the cache and the per-step views the mixers get.
+
+Storage is paged: a page holds `PAGE` consecutive tokens of one sequence, for every call of its
+group, laid out [page, kv head, token, dim] so that one head's keys of a page are contiguous.
+Calls (entries of the model's run order) whose mixers need the same head count, head size and
+ring length form a group and share one page numbering; a group that keeps every key and a
+group that keeps a window have pools and page tables of their own.
+
+Beside the pages each slot owns a fixed-size float32 state row per call that asks for one
+(`Mixer.state_size()`), zeroed when the slot is acquired.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from ..parts.base import KVNeed
+from .slots import CacheError, CacheFull, SlotBook
+
+PAGE = 64
+
+
+@dataclass(frozen=True)
+class CacheConfig:
+    """max_tokens: the most tokens all live sequences hold together, each sequence's count
+    rounded up to a whole page.  max_seqs: the most live sequences (default: one per page)."""
+    max_tokens: int
+    max_seqs: Optional[int] = None
+
+
+def ring_pages(window: Optional[int]) -> Optional[int]:
+    """Pages of a ring that always holds the last `window` keys while one page is being filled:
+    ceil((window - 1) / PAGE) + 1."""
+    if window is None:
+        return None
+    return -(-(window - 1) // PAGE) + 1
+
+
+@dataclass
+class KVView:
+    """What a mixer sees of the cache in one step: its call's pools and the batch's page table."""
+    k: torch.Tensor                 # [pages, kv heads, PAGE, dim]
+    v: torch.Tensor
+    page_table: torch.Tensor        # int32 [n_seqs, width]
+    ring: int
+    writable: bool
+
+
+class PagedCache:
+    def __init__(self, needs: List[Optional[KVNeed]], cache_of: List[Optional[int]], state_sizes: List[int],
+                 config: CacheConfig, dtype: torch.dtype, device, allocate: bool = True):
+        """needs[c], state_sizes[c]: what call c's mixer asks for; cache_of[c]: an earlier call
+        whose keys and values call c reads instead of keeping its own."""
+        self.config, self.dtype, self.device = config, dtype, torch.device(device)
+        n_pages = max(1, -(-config.max_tokens // PAGE))
+        self.n_pages = n_pages
+        self.n_slots = min(config.max_seqs or n_pages, n_pages) if config.max_seqs else n_pages
+        # ---- groups
+        self.group_keys: List[tuple] = []
+        self.call_group: List[Optional[int]] = []
+        self.call_entry: List[Optional[int]] = []
+        self.call_owner: List[Optional[int]] = []
+        entries_per_group: List[int] = []
+        for c, need in enumerate(needs):
+            owner = cache_of[c]
+            if owner is not None:
+                if not (0 <= owner < c) or needs[owner] is None or cache_of[owner] is not None:
+                    raise CacheError(f"call {c} reads the cache of call {owner}, which keeps none of its own")
+                if needs[owner].window is not None:
+                    raise CacheError(f"call {c} reads the cache of call {owner}, which keeps a window only; "
+                                     f"a shared cache has to keep every key")
+                if need is not None and (need.num_kv_heads, need.head_dim) != (needs[owner].num_kv_heads, needs[owner].head_dim):
+                    raise CacheError(f"call {c} reads the cache of call {owner} but their head shapes differ")
+                self.call_group.append(self.call_group[owner])
+                self.call_entry.append(self.call_entry[owner])
+                self.call_owner.append(owner)
+                continue
+            self.call_owner.append(None)
+            if need is None:
+                self.call_group.append(None)
+                self.call_entry.append(None)
+                continue
+            key = (need.num_kv_heads, need.head_dim, ring_pages(need.window))
+            if key not in self.group_keys:
+                self.group_keys.append(key)
+                entries_per_group.append(0)
+            g = self.group_keys.index(key)
+            self.call_group.append(g)
+            self.call_entry.append(entries_per_group[g])
+            entries_per_group[g] += 1
+        self.rings = [k[2] for k in self.group_keys]
+        self.book = SlotBook(self.n_slots, [n_pages] * len(self.group_keys), self.rings, PAGE)
+        # ---- storage
+        self.k_pools: List[torch.Tensor] = []
+        self.v_pools: List[torch.Tensor] = []
+        self.state: Dict[int, torch.Tensor] = {}
+        self.state_sizes = list(state_sizes)
+        if allocate:
+            for (nkvh, dh, _), n_entries in zip(self.group_keys, entries_per_group):
+                shape = (n_entries, n_pages, nkvh, PAGE, dh)
+                self.k_pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
+                self.v_pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
+            for c, n in enumerate(state_sizes):
+                if n > 0:
+                    self.state[c] = torch.zeros((self.n_slots, n), dtype=torch.float32, device=self.device)
+
+    # ---- sequences
+    def acquire(self) -> int:
+        slot = self.book.acquire()
+        for st in self.state.values():
+            st[slot].zero_()
+        return slot
+
+    def release(self, slot: int) -> None:
+        self.book.release(slot)
+
+    def length(self, slot: int) -> int:
+        return self.book.length(slot)
+
+    @property
+    def live_slots(self) -> List[int]:
+        return sorted(self.book.seqs)
+
+    def bytes_per_token(self) -> int:
+        es = torch.empty((), dtype=self.dtype).element_size()
+        return sum(2 * p.shape[0] * p.shape[2] * p.shape[4] * es for p in self.k_pools)
+
+    # ---- per-step tables
+    def table_width(self, group: int, slots: List[int]) -> int:
+        return max(1, max(len(self.book.pages(s, group)) for s in slots))
+
+    def page_table(self, group: int, slots: List[int], width: Optional[int] = None) -> np.ndarray:
+        """int32 [len(slots), width]: entry i of a row is the physical page at ring position i."""
+        width = width or self.table_width(group, slots)
+        t = np.zeros((len(slots), width), dtype=np.int32)
+        for r, s in enumerate(slots):
+            pages = self.book.pages(s, group)
+            t[r, :len(pages)] = pages
+        return t
+
+    def ring_of(self, group: int, width: int) -> int:
+        """The modulus the kernels use: the ring length, or (no ring) anything >= the width."""
+        ring = self.rings[group]
+        return ring if ring is not None else max(width, 1)
+
+    def view(self, call: int, tables: Dict[int, torch.Tensor]) -> KVView:
+        g = self.call_group[call]
+        if g is None:
+            raise CacheError(f"call {call} keeps no keys and values")
+        table = tables[g]
+        e = self.call_entry[call]
+        return KVView(self.k_pools[g][e], self.v_pools[g][e], table, self.ring_of(g, table.shape[1]),
+                      writable=self.call_owner[call] is None)
+
+
+__all__ = ["PAGE", "CacheConfig", "CacheError", "CacheFull", "KVView", "PagedCache", "ring_pages"]

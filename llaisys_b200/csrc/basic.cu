@@ -1,0 +1,241 @@
+// Row-wise and element-wise kernels of the decoder: embedding gather, residual add fused with
+// RMSNorm, half-split rotary encoding fused with the append to the paged cache, SwiGLU.
+//
+// Conventions: the residual stream is float32 in both precisions; activations that feed a
+// matrix product have the model's activation dtype; sums of squares, the reciprocal root, the
+// rotation and the residual sum are float32.  Formulas follow xsmccc/llaisys' CPU operators
+// (src/ops/rms_norm/cpu/rms_norm_cpu.cpp:15-34, src/ops/rope/cpu/rope_cpu.cpp:16-46,
+// src/ops/swiglu/cpu/swiglu_cpu.cpp:13-21, src/ops/embedding/cpu/embedding_cpu.cpp:16-22).
+#include "common.cuh"
+
+// ------------------------------------------------------------------ embedding
+template <typename TW>
+__global__ void embedding_kernel(float* __restrict__ out, const TW* __restrict__ table,
+                                 const int* __restrict__ ids, int H, int V, int* err) {
+    int t = blockIdx.x;
+    int id = ids[t];
+    bool ok = id >= 0 && id < V;
+    if (!ok && threadIdx.x == 0) atomicExch(err, 1);
+    const TW* row = table + (size_t)(ok ? id : 0) * H;
+    for (int j = threadIdx.x; j < H; j += blockDim.x)
+        out[(size_t)t * H + j] = ok ? to_f32(row[j]) : 0.f;
+}
+
+LLB_API int llb_embedding(float* out, const void* table, int table_dtype, const int* ids, int T,
+                          int H, int V, int* err, cudaStream_t stream) {
+    if (T == 0) return 0;
+    LLB_DISPATCH_DTYPE(table_dtype, TW,
+        embedding_kernel<TW><<<T, 256, 0, stream>>>(out, (const TW*)table, ids, H, V, err));
+    return llb_status();
+}
+
+// ------------------------------------------------------------------ residual add + RMSNorm
+// Row r of the output is norm(residual[src] + sum_p delta[p][src]) with src = rows ? rows[r] : r.
+// When write_back is set the summed row replaces residual[src] (never together with `rows`).
+template <typename TD, typename TW, typename TO>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
+                                   int n_part, size_t part_stride, const TW* __restrict__ weight,
+                                   TO* __restrict__ out, const int* __restrict__ rows, int H,
+                                   float eps, int write_back) {
+    extern __shared__ float rowbuf[];          // H floats
+    __shared__ float red[32];
+    int r = blockIdx.x;
+    size_t src = rows ? (size_t)rows[r] : (size_t)r;
+    float* res = residual + src * H;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < H; j += blockDim.x) {
+        float x = res[j];
+        if (delta) {
+            float d = 0.f;
+            for (int p = 0; p < n_part; ++p) d += to_f32(delta[p * part_stride + src * H + j]);
+            x += d;
+            if (write_back) res[j] = x;
+        }
+        rowbuf[j] = x;
+        ss += x * x;
+    }
+    ss = warp_sum(ss);
+    int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    if (lane == 0) red[w] = ss;
+    __syncthreads();
+    if (w == 0) {
+        float v = lane < (blockDim.x >> 5) ? red[lane] : 0.f;
+        v = warp_sum(v);
+        if (lane == 0) red[0] = v;
+    }
+    __syncthreads();
+    float inv = 1.0f / sqrtf(red[0] / (float)H + eps);
+    if (out)
+        for (int j = threadIdx.x; j < H; j += blockDim.x)
+            out[(size_t)r * H + j] = from_f32<TO>(rowbuf[j] * to_f32(weight[j]) * inv);
+}
+
+template <typename TD, typename TW>
+static int add_rmsnorm_out(float* residual, const void* delta, int n_part, size_t part_stride,
+                           const void* weight, void* out, int out_dtype, const int* rows, int R,
+                           int H, float eps, int write_back, cudaStream_t stream) {
+    size_t smem = (size_t)H * sizeof(float);
+    LLB_DISPATCH_DTYPE(out_dtype, TO, {
+        auto k = add_rmsnorm_kernel<TD, TW, TO>;
+        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        k<<<R, 256, smem, stream>>>(residual, (const TD*)delta, n_part, part_stride,
+                                    (const TW*)weight, (TO*)out, rows, H, eps, write_back);
+    });
+    return llb_status();
+}
+
+LLB_API int llb_add_rmsnorm(float* residual, const void* delta, int delta_dtype, int n_part,
+                            long long part_stride, const void* weight, int weight_dtype, void* out,
+                            int out_dtype, const int* rows, int R, int H, float eps,
+                            int write_back, cudaStream_t stream) {
+    if (R == 0) return 0;
+    if ((size_t)H * sizeof(float) > 200 * 1024) return (int)cudaErrorInvalidValue;
+    if (rows && write_back) return (int)cudaErrorInvalidValue;
+    if (!delta) delta_dtype = LLB_F32;
+    LLB_DISPATCH_DTYPE(delta_dtype, TD, {
+        LLB_DISPATCH_DTYPE(weight_dtype, TW, {
+            return add_rmsnorm_out<TD, TW>(residual, delta, n_part, (size_t)part_stride, weight, out,
+                                           out_dtype, rows, R, H, eps, write_back, stream);
+        });
+    });
+    return llb_status();
+}
+
+// ------------------------------------------------------------------ plain residual add
+// residual[t] += sum_p delta[p][t]  (used where no norm follows).
+template <typename TD>
+__global__ void add_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_part,
+                           size_t part_stride, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float d = 0.f;
+    for (int p = 0; p < n_part; ++p) d += to_f32(delta[p * part_stride + i]);
+    residual[i] += d;
+}
+
+LLB_API int llb_residual_add(float* residual, const void* delta, int delta_dtype, int n_part,
+                             long long part_stride, long long n, cudaStream_t stream) {
+    if (n == 0) return 0;
+    LLB_DISPATCH_DTYPE(delta_dtype, TD,
+        add_kernel<TD><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
+            residual, (const TD*)delta, n_part, (size_t)part_stride, (size_t)n));
+    return llb_status();
+}
+
+// ------------------------------------------------------------------ rotary + cache append
+// qkv is the packed projection output [T, row_stride]: nh query heads, then nkvh key heads,
+// then nkvh value heads, each of dh elements.  With ROPE the query and key heads are rotated in
+// place (half-split pairs (j, j + dh/2), angle from the float32 cos/sin table built in double
+// precision on the host).  With APPEND the (rotated) keys and the values of each token are
+// written to the token's row of the paged cache.  A window layer keeps a ring of `ring` pages:
+// tokens whose page would be overwritten within the same step are skipped.
+template <typename T, bool ROPE, bool APPEND>
+__global__ void rope_append_kernel(T* __restrict__ qkv, int row_stride, int nh, int nkvh, int dh,
+                                   const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                   int table_rows, const int* __restrict__ tok_pos,
+                                   const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
+                                   const int* __restrict__ seq_len_before,
+                                   T* __restrict__ kpool, T* __restrict__ vpool,
+                                   const int* __restrict__ page_table, int table_stride, int ring,
+                                   int* err) {
+    int t = blockIdx.x;
+    int pos = tok_pos[t];
+    T* row = qkv + (size_t)t * row_stride;
+    int half = dh >> 1;
+    const int* table = nullptr;
+    bool store = false;
+    if (APPEND) {
+        int s = tok_seq[t];
+        table = page_table + (size_t)s * table_stride;
+        int last = seq_len_before[s] + (seq_start[s + 1] - seq_start[s]) - 1;
+        store = (pos / LLB_PAGE) + ring > (last / LLB_PAGE);
+    }
+    if (ROPE) {
+        if (pos < 0 || pos >= table_rows) {
+            if (threadIdx.x == 0) atomicExch(err, 2);
+            return;
+        }
+        int n_rot = (nh + nkvh) * half;
+        for (int i = threadIdx.x; i < n_rot; i += blockDim.x) {
+            int h = i / half, j = i - h * half;
+            float c = cos_t[(size_t)pos * half + j], s = sin_t[(size_t)pos * half + j];
+            T* x = row + h * dh;
+            float a = to_f32(x[j]), b = to_f32(x[j + half]);
+            T ya = from_f32<T>(a * c - b * s), yb = from_f32<T>(b * c + a * s);
+            x[j] = ya;
+            x[j + half] = yb;
+            if (APPEND && store && h >= nh) {
+                size_t o = paged_row(table, ring, pos, h - nh, nkvh, dh);
+                kpool[o + j] = ya;
+                kpool[o + j + half] = yb;
+            }
+        }
+    } else if (APPEND && store) {
+        for (int i = threadIdx.x; i < nkvh * dh; i += blockDim.x) {
+            int h = i / dh, j = i - h * dh;
+            kpool[paged_row(table, ring, pos, h, nkvh, dh) + j] = row[(nh + h) * dh + j];
+        }
+    }
+    if (APPEND && store) {
+        for (int i = threadIdx.x; i < nkvh * dh; i += blockDim.x) {
+            int h = i / dh, j = i - h * dh;
+            vpool[paged_row(table, ring, pos, h, nkvh, dh) + j] = row[(nh + nkvh + h) * dh + j];
+        }
+    }
+}
+
+template <typename TT>
+static void launch_rope_append(TT* qkv, int T, int row_stride, int nh, int nkvh, int dh, int do_rope,
+                               const float* cos_t, const float* sin_t, int table_rows,
+                               const int* tok_pos, int do_append, const int* tok_seq,
+                               const int* seq_start, const int* seq_len_before, TT* kpool, TT* vpool,
+                               const int* page_table, int table_stride, int ring, int* err,
+                               cudaStream_t stream) {
+#define LLB_RA(R, A)                                                                          \
+    rope_append_kernel<TT, R, A><<<T, 128, 0, stream>>>(                                      \
+        qkv, row_stride, nh, nkvh, dh, cos_t, sin_t, table_rows, tok_pos, tok_seq, seq_start, \
+        seq_len_before, kpool, vpool, page_table, table_stride, ring, err)
+    if (do_rope && do_append) LLB_RA(true, true);
+    else if (do_rope) LLB_RA(true, false);
+    else if (do_append) LLB_RA(false, true);
+#undef LLB_RA
+}
+
+LLB_API int llb_rope_append(void* qkv, int dtype, int T, int row_stride, int nh, int nkvh, int dh,
+                            int do_rope, const float* cos_t, const float* sin_t, int table_rows,
+                            const int* tok_pos, int do_append, const int* tok_seq,
+                            const int* seq_start, const int* seq_len_before, void* kpool,
+                            void* vpool, const int* page_table, int table_stride, int ring,
+                            int* err, cudaStream_t stream) {
+    if (T == 0) return 0;
+    if (dh % 2) return (int)cudaErrorInvalidValue;
+    LLB_DISPATCH_DTYPE(dtype, TT,
+        launch_rope_append<TT>((TT*)qkv, T, row_stride, nh, nkvh, dh, do_rope, cos_t, sin_t,
+                               table_rows, tok_pos, do_append, tok_seq, seq_start, seq_len_before,
+                               (TT*)kpool, (TT*)vpool, page_table, table_stride, ring, err, stream));
+    return llb_status();
+}
+
+// ------------------------------------------------------------------ SwiGLU
+// gate_up is [T, 2I] with the gate columns first; out[t, i] = up * gate / (1 + exp(-gate)).
+template <typename T>
+__global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int I, size_t n) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    size_t t = i / I;
+    int c = (int)(i - t * I);
+    float g = to_f32(gate_up[t * 2 * I + c]);
+    float u = to_f32(gate_up[t * 2 * I + I + c]);
+    out[i] = from_f32<T>(u * (g / (1.0f + expf(-g))));
+}
+
+LLB_API int llb_swiglu(void* out, const void* gate_up, int dtype, int T, int I, cudaStream_t stream) {
+    size_t n = (size_t)T * I;
+    if (n == 0) return 0;
+    LLB_DISPATCH_DTYPE(dtype, TT,
+        swiglu_kernel<TT><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((TT*)out, (const TT*)gate_up, I, n));
+    return llb_status();
+}
+
+// ------------------------------------------------------------------ misc
+LLB_API const char* llb_error_string(int code) { return cudaGetErrorString((cudaError_t)code); }

@@ -1,0 +1,55 @@
+// Shared declarations of the CUDA modules: dtype codes, conversions, the paged key/value
+// cache addressing, and the launch-status convention of the C entry points.
+//
+// Every exported function is `extern "C" int llb_*(..., cudaStream_t stream)`; it returns 0 or
+// the cudaError_t of the launch, never allocates, and works on the stream it is given.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define LLB_API extern "C" __attribute__((visibility("default")))
+
+enum { LLB_F32 = 0, LLB_BF16 = 1 };
+
+// Tokens of a cache page.  Attention kernels walk keys in tiles of one page.
+constexpr int LLB_PAGE = 64;
+
+typedef __nv_bfloat16 bf16;
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(bf16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// One layer's keys or values live in pages of LLB_PAGE tokens: pool[page][kv_head][token][dim].
+// A sequence's page table lists its physical pages; logical page lp sits at entry lp % ring
+// (ring is the table length for layers that keep every key, and the ring length for layers
+// that keep a window).
+__device__ __forceinline__ size_t paged_row(const int* table, int ring, int pos, int kvh,
+                                            int n_kv_heads, int head_dim) {
+    int lp = pos / LLB_PAGE;
+    int page = table[lp % ring];
+    return (((size_t)page * n_kv_heads + kvh) * LLB_PAGE + (pos % LLB_PAGE)) * (size_t)head_dim;
+}
+
+static inline int llb_status() { return (int)cudaGetLastError(); }
+
+#define LLB_DISPATCH_DTYPE(code, T, ...)                                   \
+    do {                                                                   \
+        if ((code) == LLB_F32) { typedef float T; __VA_ARGS__; }           \
+        else if ((code) == LLB_BF16) { typedef bf16 T; __VA_ARGS__; }      \
+        else return (int)cudaErrorInvalidValue;                            \
+    } while (0)

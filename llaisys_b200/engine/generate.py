@@ -1,0 +1,109 @@
+"""The generation loop above the step function.
+
+xsmccc/llaisys generates for one sequence: the prompt token by token, then one token per call
+until max_new_tokens or the end token (python/llaisys/models/qwen2.py:234-283; its end test
+skips the first generated token).  Here any number of prompts of unequal lengths are served:
+as many as fit start together as a batch (their prompts in one step), then each live sequence
+gets one token per step; a sequence that meets a stop token or its token limit leaves the
+batch at once and its slot is given back; when a batch is done the next one starts, until no
+request is left.  The stop test applies to every generated token.
+
+The loop needs of its engine only: acquire(), release(slot), step(entries) -> logits,
+`max_tokens`, `max_seqs`, `max_positions`, `page`; and of its sampler a call
+(logits, keys, steps) -> token ids.  That keeps its decisions testable without a device.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Sequence
+
+from .engine import StepEntry
+
+
+@dataclass
+class Generation:
+    """Result for one request: the new tokens (a stop token included) and why it ended:
+    "stop", "length" (max_new_tokens) or "limit" (the model's position limit)."""
+    tokens: List[int] = field(default_factory=list)
+    reason: str = ""
+
+
+class GenerationLoop:
+    def __init__(self, engine, sampler: Callable, stop_ids: Sequence[int] = (), max_batch: Optional[int] = None):
+        self.engine, self.sampler = engine, sampler
+        self.stop_ids = frozenset(int(s) for s in stop_ids)
+        self.max_batch = max_batch
+        self.batches_run = 0
+        self.steps_run = 0
+
+    # ---- admission: how many of the waiting requests start together
+    def _room(self, prompt_len: int, max_new: int) -> int:
+        page = self.engine.page
+        n = min(prompt_len + max_new, self.engine.max_positions)
+        return -(-n // page) * page
+
+    def _admit(self, waiting: List[int], prompts, max_new: int) -> List[int]:
+        batch, tokens = [], 0
+        limit = min(self.engine.max_seqs, self.max_batch or self.engine.max_seqs)
+        for r in waiting:
+            need = self._room(len(prompts[r]), max_new)
+            if batch and (tokens + need > self.engine.max_tokens or len(batch) >= limit):
+                break
+            if need > self.engine.max_tokens:
+                raise ValueError(f"request {r} needs room for {need} tokens; the cache holds {self.engine.max_tokens}")
+            batch.append(r)
+            tokens += need
+        return batch
+
+    # ---- the loop
+    def run(self, prompts: Sequence[Sequence[int]], max_new_tokens: int) -> List[Generation]:
+        for r, p in enumerate(prompts):
+            if len(p) == 0:
+                raise ValueError(f"request {r} has an empty prompt")
+            if len(p) >= self.engine.max_positions and max_new_tokens > 0:
+                raise ValueError(f"request {r}: a prompt of {len(p)} tokens leaves no position to generate at "
+                                 f"(the model allows {self.engine.max_positions})")
+        results = [Generation() for _ in prompts]
+        waiting = list(range(len(prompts)))
+        if max_new_tokens <= 0:
+            for g in results:
+                g.reason = "length"
+            return results
+        while waiting:
+            batch = self._admit(waiting, prompts, max_new_tokens)
+            waiting = waiting[len(batch):]
+            self._run_batch(batch, prompts, max_new_tokens, results)
+            self.batches_run += 1
+        return results
+
+    def _run_batch(self, batch: List[int], prompts, max_new: int, results: List[Generation]) -> None:
+        eng = self.engine
+        slot = {r: eng.acquire() for r in batch}
+        length = {r: len(prompts[r]) for r in batch}
+        live = list(batch)
+        try:
+            entries = [StepEntry(slot[r], list(prompts[r]), [len(prompts[r]) - 1]) for r in live]
+            while live:
+                logits = eng.step(entries)
+                self.steps_run += 1
+                new = self.sampler(logits, live, [len(results[r].tokens) for r in live])
+                still, entries = [], []
+                for r, tok in zip(live, new):
+                    g = results[r]
+                    g.tokens.append(int(tok))
+                    length[r] += 1
+                    if int(tok) in self.stop_ids:
+                        g.reason = "stop"
+                    elif len(g.tokens) >= max_new:
+                        g.reason = "length"
+                    elif length[r] >= eng.max_positions:
+                        g.reason = "limit"
+                    if g.reason:
+                        eng.release(slot.pop(r))
+                    else:
+                        still.append(r)
+                        entries.append(StepEntry(slot[r], [int(tok)], [0]))
+                live = still
+        finally:
+            for s in slot.values():
+                eng.release(s)

@@ -1,0 +1,267 @@
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_double, c_float, c_int, c_longlong, c_ulonglong, c_void_p
+from typing import Optional
+
+import torch
+
+from ..csrc.build import load_module
+
+PAGE = 64                      # tokens of a cache page (LLB_PAGE in csrc/common.cuh)
+DT = {torch.float32: 0, torch.bfloat16: 1}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"dtype {t.dtype} is not supported by the kernels (float32 or bfloat16)") from None
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*ts):
+    for t in ts:
+        if t is not None and not t.is_cuda:
+            raise KernelError("the kernels of llaisys_b200 run on a CUDA device only; got a CPU tensor")
+
+
+_basic = None
+
+
+def _lib_basic():
+    global _basic
+    if _basic is None:
+        _basic = load_module("basic.cu")
+        _basic.llb_error_string.restype = ctypes.c_char_p
+        _basic.llb_error_string.argtypes = [c_int]
+    return _basic
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        msg = _lib_basic().llb_error_string(rc)
+        raise KernelError(f"{what}: CUDA error {rc} ({msg.decode() if msg else '?'})")
+
+
+_configured = set()
+
+
+def _fn(lib, name, argtypes):
+    f = getattr(lib, name)
+    if (id(lib), name) not in _configured:
+        f.argtypes = argtypes
+        f.restype = c_int
+        _configured.add((id(lib), name))
+    return f
+
+
+# ------------------------------------------------------------------ row-wise kernels
+def embedding(ids: torch.Tensor, table: torch.Tensor, err: torch.Tensor) -> torch.Tensor:
+    """float32 [T, H] rows of `table` (float32 or bfloat16) for int32 `ids`; an id outside the
+    table sets err[0] = 1 and yields a zero row."""
+    _need_cuda(ids, table)
+    T, (V, H) = ids.numel(), table.shape
+    out = torch.empty((T, H), dtype=torch.float32, device=table.device)
+    f = _fn(_lib_basic(), "llb_embedding", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(out), _ptr(table), _dt(table), _ptr(ids), T, H, V, _ptr(err), _stream()), "embedding")
+    return out
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None, want_out: bool = True):
+    """residual (float32 [T, H]) += delta, then out = residual * weight / sqrt(mean(residual^2) + eps).
+
+    delta is [T, H] or [parts, T, H] (partial sums, added in order).  With `rows` (int32) only those
+    rows are normalised, into an [len(rows), H] output, and the residual is left as it was."""
+    _need_cuda(residual, delta, weight, rows)
+    T, H = residual.shape
+    n_part, stride = 1, 0
+    if delta is not None:
+        if delta.dim() == 3:
+            n_part, stride = delta.shape[0], delta.stride(0)
+        assert delta.shape[-2:] == residual.shape and delta.is_contiguous()
+    R = T if rows is None else rows.numel()
+    out = torch.empty((R, H), dtype=out_dtype, device=residual.device) if want_out else None
+    f = _fn(_lib_basic(), "llb_add_rmsnorm", [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_int,
+                                              c_void_p, c_int, c_void_p, c_int, c_int, c_float, c_int, c_void_p])
+    _check(f(_ptr(residual), _ptr(delta), _dt(delta) if delta is not None else 0, n_part, stride,
+             _ptr(weight), _dt(weight), _ptr(out), DT[out_dtype], _ptr(rows), R, H, eps,
+             0 if rows is not None else 1, _stream()), "add_rmsnorm")
+    return out
+
+
+def residual_add(residual: torch.Tensor, delta: torch.Tensor):
+    _need_cuda(residual, delta)
+    n_part, stride = (delta.shape[0], delta.stride(0)) if delta.dim() == 3 else (1, 0)
+    f = _fn(_lib_basic(), "llb_residual_add", [c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_void_p])
+    _check(f(_ptr(residual), _ptr(delta), _dt(delta), n_part, stride, residual.numel(), _stream()), "residual_add")
+
+
+def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
+    """[T, 2I] (gate columns first) -> [T, I]: up * gate / (1 + exp(-gate))."""
+    _need_cuda(gate_up)
+    T, I2 = gate_up.shape
+    out = torch.empty((T, I2 // 2), dtype=gate_up.dtype, device=gate_up.device)
+    f = _fn(_lib_basic(), "llb_swiglu", [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(gate_up), _dt(gate_up), T, I2 // 2, _stream()), "swiglu")
+    return out
+
+
+def rope_append(qkv: torch.Tensor, nh: int, nkvh: int, dh: int, *, cos=None, sin=None, tok_pos=None,
+                append=None, err=None):
+    """In place on the packed projections [T, (nh + 2 nkvh) dh]: rotate the query and key heads
+    (when cos/sin tables are given) and/or write keys and values to the paged cache.
+
+    append = dict(tok_seq, seq_start, seq_len_before, kpool, vpool, page_table, ring)."""
+    _need_cuda(qkv)
+    T = qkv.shape[0]
+    assert qkv.stride(1) == 1
+    do_rope, do_app = cos is not None, append is not None
+    a = append or {}
+    pt = a.get("page_table")
+    f = _fn(_lib_basic(), "llb_rope_append",
+            [c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p,
+             c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(qkv), _dt(qkv), T, qkv.stride(0), nh, nkvh, dh, int(do_rope), _ptr(cos), _ptr(sin),
+             cos.shape[0] if do_rope else 0, _ptr(tok_pos), int(do_app), _ptr(a.get("tok_seq")),
+             _ptr(a.get("seq_start")), _ptr(a.get("seq_len_before")), _ptr(a.get("kpool")), _ptr(a.get("vpool")),
+             _ptr(pt), pt.shape[1] if do_app else 0, a.get("ring", 1), _ptr(err), _stream()), "rope_append")
+
+
+# ------------------------------------------------------------------ matrix products
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """x [M, K] (row stride free) times weight [N, K] transposed, plus bias [N]; float32 accumulation."""
+    _need_cuda(x, weight, bias)
+    M, K = x.shape
+    N, K2 = weight.shape
+    if K != K2:
+        raise KernelError(f"linear: x has {K} columns but the weight has {K2}")
+    assert x.stride(1) == 1 and weight.is_contiguous()
+    out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+    lib = load_module("gemm_simt.cu")
+    f = _fn(lib, "llb_gemm_simt", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
+                                   c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_ptr(x), _dt(x), _ptr(weight), _dt(weight), _ptr(bias), _dt(bias) if bias is not None else 0,
+             _ptr(out), _dt(out), M, N, K, x.stride(0), out.stride(0), _stream()), "linear")
+    return out
+
+
+# ------------------------------------------------------------------ attention
+class _AttnParams(ctypes.Structure):
+    _fields_ = [("q", c_void_p), ("k_new", c_void_p), ("v_new", c_void_p), ("row_stride", c_int),
+                ("out", c_void_p), ("kpool", c_void_p), ("vpool", c_void_p), ("page_table", c_void_p),
+                ("table_stride", c_int), ("ring", c_int), ("seq_start", c_void_p),
+                ("seq_len_before", c_void_p), ("nh", c_int), ("nkvh", c_int), ("window", c_int),
+                ("scale", c_float), ("all_from_cache", c_int), ("n_splits", c_int), ("part_o", c_void_p), ("part_ml", c_void_p)]
+
+
+def _attn_lib(dh: int):
+    if dh % 2 or dh > 256:
+        raise KernelError(f"attention: head size {dh} is not supported (even, at most 256)")
+    return load_module("attention_simt.cu", {"LLB_HEAD_DIM": dh})
+
+
+def _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before,
+                 window, scale):
+    es = qkv.element_size()
+    p = _AttnParams()
+    p.q = qkv.data_ptr()
+    p.k_new = qkv.data_ptr() + nh * dh * es
+    p.v_new = qkv.data_ptr() + (nh + nkvh) * dh * es
+    p.row_stride = qkv.stride(0)
+    p.out = out.data_ptr()
+    p.kpool, p.vpool = kpool.data_ptr(), vpool.data_ptr()
+    p.page_table, p.table_stride, p.ring = page_table.data_ptr(), page_table.shape[1], ring
+    p.seq_start, p.seq_len_before = seq_start.data_ptr(), seq_len_before.data_ptr()
+    p.nh, p.nkvh, p.window, p.scale = nh, nkvh, int(window or 0), scale
+    p.all_from_cache, p.n_splits, p.part_o, p.part_ml = 0, 1, None, None
+    return p
+
+
+def attention_prefill(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before,
+                      n_seqs: int, max_new: int, window, scale, all_from_cache: bool = False) -> torch.Tensor:
+    """Attention of the new tokens of each sequence over its cached keys (positions before the
+    step) and the step's own keys, read from the packed projections `qkv` [T, (nh + 2 nkvh) dh]
+    whose query and key heads are already rotated.  With all_from_cache the step's keys are
+    read from the cache too (they were put there by an earlier call).  Returns [T, nh * dh]."""
+    _need_cuda(qkv, kpool, vpool, page_table)
+    assert qkv.dtype == kpool.dtype == vpool.dtype
+    out = torch.empty((qkv.shape[0], nh * dh), dtype=qkv.dtype, device=qkv.device)
+    p = _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before, window, scale)
+    p.all_from_cache = int(all_from_cache)
+    f = _fn(_attn_lib(dh), "llb_attn_prefill", [_AttnParams, c_int, c_int, c_int, c_void_p])
+    _check(f(p, _dt(qkv), n_seqs, max_new, _stream()), "attention_prefill")
+    return out
+
+
+def attention_decode(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before,
+                     n_seqs: int, window, scale, n_splits: int = 1) -> torch.Tensor:
+    """Attention of one new token per sequence (already appended to the cache) over the cache."""
+    _need_cuda(qkv, kpool, vpool, page_table)
+    assert qkv.dtype == kpool.dtype == vpool.dtype
+    out = torch.empty((qkv.shape[0], nh * dh), dtype=qkv.dtype, device=qkv.device)
+    p = _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before, window, scale)
+    keep = None
+    if n_splits > 1:
+        part_o = torch.empty((n_seqs, nh, n_splits, dh), dtype=torch.float32, device=qkv.device)
+        part_ml = torch.empty((n_seqs, nh, n_splits, 2), dtype=torch.float32, device=qkv.device)
+        p.n_splits, p.part_o, p.part_ml = n_splits, part_o.data_ptr(), part_ml.data_ptr()
+        keep = (part_o, part_ml)
+    f = _fn(_attn_lib(dh), "llb_attn_decode", [_AttnParams, c_int, c_int, c_void_p])
+    _check(f(p, _dt(qkv), n_seqs, _stream()), "attention_decode")
+    del keep
+    return out
+
+
+# ------------------------------------------------------------------ choice of the next token
+def argmax(logits: torch.Tensor) -> torch.Tensor:
+    """int32 index of the first maximum of every row of float32 logits [R, V]."""
+    _need_cuda(logits)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    R, V = logits.shape
+    out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    f = _fn(load_module("sampling.cu"), "llb_argmax", [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(logits), logits.stride(0), R, V, _ptr(out), _stream()), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: float, top_k: int, top_p: float, seed: int,
+           keys: Optional[torch.Tensor] = None, steps: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row of float32 logits [R, V]; see csrc/sampling.cu for the rule.  keys and
+    steps (int32 [R]) are the request number and the number of tokens the request has drawn."""
+    _need_cuda(logits, keys, steps)
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1
+    R, V = logits.shape
+    out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    f = _fn(load_module("sampling.cu"), "llb_sample",
+            [c_void_p, c_longlong, c_int, c_int, c_void_p, c_float, c_int, c_float, c_ulonglong,
+             c_void_p, c_void_p, c_void_p])
+    _check(f(_ptr(logits), logits.stride(0), R, V, _ptr(out), temperature, top_k, top_p,
+             seed & 0xFFFFFFFFFFFFFFFF, _ptr(keys), _ptr(steps), _stream()), "sample")
+    return out
+
+
+def uniform(seed: int, key: int, step: int) -> float:
+    """The uniform in [0, 1) that `sample` uses for (seed, key, step) (splitmix64 finaliser)."""
+    mask, G = 0xFFFFFFFFFFFFFFFF, 0x9E3779B97F4A7C15
+
+    def mix(z):
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & mask
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & mask
+        return z ^ (z >> 31)
+
+    z = mix((mix((seed + G * (key + 1)) & mask) + G * (step + 1)) & mask)
+    return (z >> 11) / 9007199254740992.0

@@ -1,0 +1,143 @@
+"""What a part is, and the registry parts are chosen from.
+
+A model is put together from parts of five categories:
+
+  mixer     mixes information across the positions of a sequence (attention here)
+  ffn       position-wise feed-forward (dense here; a routed one would register the same way)
+  norm      normalisation of one activation row
+  position  position encoding applied by a mixer to its queries and keys
+  block     the arrangement of a mixer, a feed-forward and their norms around the residual stream
+
+plus the token embedding and the output head.  Every part is built from a `PartSpec` (its sizes
+and constants) and a `BuildEnv` (activation dtype, device); it declares the tensors it wants by
+local name, receives them from the loader, and knows nothing of the model it sits in.
+
+Registering another part:  `@register_part("mixer", "my_kind") class MyMixer(Mixer): ...` and
+name `"my_kind"` in a `PartSpec`.  Interfaces are the abstract classes below.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from ..config.spec import PartSpec
+
+CATEGORIES = ("mixer", "ffn", "norm", "position", "block", "embedding", "head")
+_REGISTRY: Dict[Tuple[str, str], type] = {}
+
+
+def register_part(category: str, kind: str):
+    if category not in CATEGORIES:
+        raise ValueError(f"unknown part category {category!r}; categories: {CATEGORIES}")
+
+    def deco(cls):
+        _REGISTRY[(category, kind)] = cls
+        cls.category, cls.kind = category, kind
+        return cls
+    return deco
+
+
+def known_parts(category: str):
+    return sorted(k for c, k in _REGISTRY if c == category)
+
+
+def part_class(category: str, kind: str) -> type:
+    cls = _REGISTRY.get((category, kind))
+    if cls is None:
+        raise KeyError(f"no {category} part of kind {kind!r} is registered; known: {known_parts(category)}")
+    return cls
+
+
+def build_part(category: str, spec: PartSpec, env: "BuildEnv"):
+    return part_class(category, spec.kind)(spec, env)
+
+
+@dataclass(frozen=True)
+class BuildEnv:
+    """dtype: the activation dtype (torch.float32: everything in true 32-bit; torch.bfloat16:
+    bfloat16 activations, weights and cache with float32 residual stream and reductions)."""
+    dtype: torch.dtype
+    device: torch.device
+
+
+@dataclass(frozen=True)
+class TensorDecl:
+    """A tensor a part wants from the weights file.  kind: "float" or "int".  init: how the
+    random-weights mode fills it ("normal": N(0, 0.02); "one_plus_normal": 1 + N(0, 0.02))."""
+    shape: Tuple[int, ...]
+    kind: str = "float"
+    init: str = "normal"
+
+
+@dataclass(frozen=True)
+class KVNeed:
+    """Keys and values a mixer keeps per token: `window` None keeps all, else the last `window`."""
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+class Part:
+    """Base of all parts."""
+    category = kind = "?"
+
+    def __init__(self, spec: PartSpec, env: BuildEnv):
+        self.spec, self.env = spec, env
+
+    def tensors(self) -> Dict[str, TensorDecl]:
+        """local tensor name -> declaration; the file's name is spec.prefix + "." + local name."""
+        return {}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """Receives the declared tensors, on the device, in the dtype they are to be kept in."""
+
+
+class Norm(Part):
+    def forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor] = None,
+                rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """residual (float32 [T, H]) += delta (if given), then the normalised rows in the
+        activation dtype.  With `rows` only those rows, and the residual is not written."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def apply(self, qkv: torch.Tensor, num_heads: int, num_kv_heads: int, ctx, append=None) -> None:
+        """Encodes the positions ctx.tok_pos into the query and key heads of the packed
+        projections, in place; `append` (see kernels.rope_append) asks it to also store keys
+        and values in the cache, which saves a pass over them."""
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def kv_need(self) -> Optional[KVNeed]:
+        """Growing per-token storage this mixer needs, or None."""
+        return None
+
+    def state_size(self) -> int:
+        """float32 elements of fixed-size state per sequence (zeroed when a sequence starts)."""
+        return 0
+
+    def forward(self, x: torch.Tensor, ctx, call: int) -> torch.Tensor:
+        """x: normalised activations [T, H] of the step's packed tokens.  Returns what is to be
+        added to the residual stream: [T, H] or [parts, T, H].  `ctx.kv(call)` is this call's
+        cache view, `ctx.state(call)` its state rows [n_slots, state_size]."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    """Arrangement of one layer.  Built with the layer's parts instead of a PartSpec."""
+
+    def __init__(self, mixer: Mixer, mixer_norm: Norm, ffn: FeedForward, ffn_norm: Norm, env: BuildEnv):
+        self.mixer, self.mixer_norm, self.ffn, self.ffn_norm, self.env = mixer, mixer_norm, ffn, ffn_norm, env
+
+    def forward(self, residual: torch.Tensor, pending: Optional[torch.Tensor], ctx, call: int):
+        """residual: float32 [T, H]; pending: a delta not yet added to it (or None).
+        Returns (residual, pending) for the next block."""
+        raise NotImplementedError

@@ -1,0 +1,33 @@
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from .base import FeedForward, TensorDecl, register_part
+
+
+@register_part("ffn", "swiglu_mlp")
+class SwiGLUMLP(FeedForward):
+    """down(up(x) * silu(gate(x))), no biases (xsmccc/llaisys src/models/qwen2/mlp.hpp:18-39,
+    src/ops/swiglu/cpu/swiglu_cpu.cpp:13-21).  The gate and up matrices are kept as one
+    [2I, H] matrix so that one product serves both.  params: hidden_size, intermediate_size."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.hidden, self.inter = int(spec.params["hidden_size"]), int(spec.params["intermediate_size"])
+        self.gate_up = self.down = None
+
+    def tensors(self):
+        return {"gate_proj.weight": TensorDecl((self.inter, self.hidden)),
+                "up_proj.weight": TensorDecl((self.inter, self.hidden)),
+                "down_proj.weight": TensorDecl((self.hidden, self.inter))}
+
+    def load(self, tensors):
+        g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        dt = torch.promote_types(g.dtype, u.dtype)
+        self.gate_up = torch.cat([g.to(dt), u.to(dt)], dim=0).contiguous()
+        self.down = tensors["down_proj.weight"].contiguous()
+
+    def forward(self, x, ctx):
+        gu = kernels.linear(x, self.gate_up)
+        return kernels.linear(kernels.swiglu(gu), self.down)

@@ -1,0 +1,137 @@
+"""Binding weights to a model by tensor name.
+
+xsmccc/llaisys maps every tensor of every *.safetensors file of the folder to a slot of its
+weights struct by exact name, converts 16-bit tensors to float32 and silently skips what it
+does not know (python/llaisys/models/qwen2.py:99-210).  Here the model's parts declare the
+tensors they want; the file must hold exactly those, with those shapes, or loading stops with
+one error that lists everything that is missing, unexpected or mis-shaped.
+
+Kept dtypes: under a float32 model every floating tensor becomes float32.  Under a bfloat16
+model a tensor stored in 16 bits is kept as bfloat16 and a tensor stored in 32 (or 64) bits
+stays float32 (the kernels take either); integer tensors are kept as int32.
+"""
+from __future__ import annotations
+
+import hashlib
+from pathlib import Path
+from typing import Dict, Tuple
+
+import torch
+
+from .safetensors_io import DTYPES, SafetensorsFile
+
+
+class WeightsError(ValueError):
+    """The tensors on offer do not fit the model.  `missing`, `unexpected`, `wrong_shape`
+    (name -> (got, want)) and `wrong_kind` hold the details that the message lists."""
+
+    def __init__(self, where, missing, unexpected, wrong_shape, wrong_kind):
+        self.missing, self.unexpected = sorted(missing), sorted(unexpected)
+        self.wrong_shape, self.wrong_kind = dict(wrong_shape), dict(wrong_kind)
+        lines = [f"weights of {where} do not fit the model:"]
+        if self.missing:
+            lines.append(f"  missing tensors ({len(self.missing)}): " + ", ".join(self.missing))
+        if self.unexpected:
+            lines.append(f"  unexpected tensors ({len(self.unexpected)}): " + ", ".join(self.unexpected))
+        for n, (got, want) in sorted(self.wrong_shape.items()):
+            lines.append(f"  wrong shape: {n} is {list(got)}, the model wants {list(want)}")
+        for n, (got, want) in sorted(self.wrong_kind.items()):
+            lines.append(f"  wrong type: {n} is stored as {got}, the model wants a {want} tensor")
+        super().__init__("\n".join(lines))
+
+
+_FLOAT = {"F64", "F32", "F16", "BF16"}
+_INT = {"I64", "I32", "I16", "I8", "U8"}
+
+
+class FolderSource:
+    """All *.safetensors files of a model folder, in sorted order."""
+
+    def __init__(self, folder):
+        self.folder = Path(folder)
+        self.files = [SafetensorsFile(p) for p in sorted(self.folder.glob("*.safetensors"))]
+        if not self.files:
+            raise FileNotFoundError(f"no *.safetensors file in {self.folder}")
+        self._where: Dict[str, SafetensorsFile] = {}
+        for f in self.files:
+            for name in f.entries:
+                if name in self._where:
+                    raise ValueError(f"tensor {name!r} appears in both {self._where[name].path.name} and {f.path.name}")
+                self._where[name] = f
+
+    def describe(self) -> str:
+        return str(self.folder)
+
+    def entries(self) -> Dict[str, Tuple[str, Tuple[int, ...]]]:
+        return {n: f.entries[n] for n, f in self._where.items()}
+
+    def get(self, name: str) -> torch.Tensor:
+        return self._where[name].get(name)
+
+
+class RandomSource:
+    """Seeded random tensors for a model's declarations: matrices, embeddings and biases
+    N(0, 0.02), norm weights 1 + N(0, 0.02), drawn in float32 and rounded to `dtype`.  Every
+    tensor has a generator of its own, keyed by (seed, name), so its values do not depend on
+    which other tensors exist."""
+
+    def __init__(self, decls, seed: int, dtype: torch.dtype = torch.bfloat16, device="cpu", std: float = 0.02):
+        self.decls, self.seed, self.dtype, self.device, self.std = dict(decls), int(seed), dtype, torch.device(device), std
+
+    def describe(self) -> str:
+        return f"random weights (seed {self.seed})"
+
+    def entries(self):
+        from .safetensors_io import NAMES
+        return {n: (NAMES[self.dtype] if d.kind == "float" else "I32", tuple(d.shape)) for n, d in self.decls.items()}
+
+    def get(self, name: str) -> torch.Tensor:
+        d = self.decls[name]
+        key = int.from_bytes(hashlib.sha256(f"{self.seed}:{name}".encode()).digest()[:8], "little") >> 1
+        gen = torch.Generator(device=self.device).manual_seed(key)
+        if d.kind == "int":
+            return torch.zeros(d.shape, dtype=torch.int32, device=self.device)
+        x = torch.randn(d.shape, generator=gen, dtype=torch.float32, device=self.device) * self.std
+        if d.init == "one_plus_normal":
+            x += 1.0
+        return x.to(self.dtype)
+
+
+def kept_dtype(stored: str, compute: torch.dtype) -> torch.dtype:
+    if stored in _INT:
+        return torch.int32
+    if compute == torch.float32:
+        return torch.float32
+    return torch.bfloat16 if stored in ("F16", "BF16") else torch.float32
+
+
+def check_tensors(model, source) -> None:
+    expected = model.expected_tensors()
+    have = source.entries()
+    ignorable = set(model.ignorable_tensors())
+    missing = [n for n in expected if n not in have]
+    unexpected = [n for n in have if n not in expected and n not in ignorable]
+    wrong_shape, wrong_kind = {}, {}
+    for n, decl in expected.items():
+        if n not in have:
+            continue
+        stored, shape = have[n]
+        if tuple(shape) != tuple(decl.shape):
+            wrong_shape[n] = (tuple(shape), tuple(decl.shape))
+        if (decl.kind == "float" and stored not in _FLOAT) or (decl.kind == "int" and stored not in _INT):
+            wrong_kind[n] = (stored, "floating-point" if decl.kind == "float" else "integer")
+    if missing or unexpected or wrong_shape or wrong_kind:
+        raise WeightsError(source.describe(), missing, unexpected, wrong_shape, wrong_kind)
+
+
+def load_weights(model, source) -> None:
+    """Checks `source` against the model's declarations, then moves every tensor to the
+    model's device in the dtype it is kept in and hands them to the parts."""
+    check_tensors(model, source)
+    have = source.entries()
+    env = model.env
+    tensors = {}
+    for name in model.expected_tensors():
+        t = source.get(name)
+        tensors[name] = t.to(device=env.device, dtype=kept_dtype(have[name][0], env.dtype))
+    model.bind(tensors)

@@ -1,0 +1,121 @@
+"""The engine against the plain implementation under every way of cutting requests into steps."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import (CONFIGS, Oracle, build_engine, compare, make_folder, random_requests, run_batches,
+                     run_tail_by_one, run_whole)
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.float32, torch.bfloat16]
+
+# request lengths: a single token, page edges (63, 64, 65), the window's ring (B: 2 pages, C: 3), some hundreds
+LENGTHS = {"A": [5, 9, 2, 64, 150], "B": [1, 7, 13, 20, 65, 200], "C": [3, 70, 71, 129, 300]}
+
+
+@pytest.fixture(scope="module", params=["A", "B", "C"])
+def model(request, tmp_path_factory):
+    name = request.param
+    folder = make_folder(tmp_path_factory.mktemp(f"tiny{name}"), CONFIGS[name], seed=ord(name), attn_gain=12.0)
+    requests = random_requests(CONFIGS[name], LENGTHS[name], seed=ord(name))
+    return name, folder, Oracle(folder), requests
+
+
+def _rooms(requests):
+    return sum(-(-len(r) // 64) * 64 for r in requests)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_each_request_alone_and_whole(model, dtype):
+    name, folder, oracle, requests = model
+    engine = build_engine(folder, dtype, max_tokens=max(-(-len(r) // 64) * 64 for r in requests))
+    worst = compare(run_whole(engine, requests), oracle, requests, dtype, CONFIGS[name], f"{name} whole")
+    print(f"{name} {dtype} whole: worst error/tolerance {worst}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_last_tokens_one_by_one(model, dtype):
+    name, folder, oracle, requests = model
+    engine = build_engine(folder, dtype, max_tokens=max(-(-len(r) // 64) * 64 for r in requests))
+    worst = compare(run_tail_by_one(engine, requests), oracle, requests, dtype, CONFIGS[name], f"{name} tail-by-one")
+    print(f"{name} {dtype} tail: worst error/tolerance {worst}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_unequal_batches_with_slot_reuse(model, dtype):
+    name, folder, oracle, requests = model
+    n = len(requests)
+    # two batches, one after the other, in a cache that only just holds the larger one: pages and
+    # slots of the first batch are used again by the second
+    batches = [list(range(0, n, 2)), list(range(1, n, 2))]
+    prompt_lens = [max(1, len(r) - (3 + 5 * i)) for i, r in enumerate(requests)]
+    room = max(_rooms([requests[r] for r in b]) for b in batches)
+    engine = build_engine(folder, dtype, max_tokens=room, max_seqs=len(batches[0]))
+    got = run_batches(engine, requests, batches, prompt_lens)
+    worst = compare(got, oracle, requests, dtype, CONFIGS[name], f"{name} batches")
+    assert not engine.cache.live_slots and all(p.available == engine.cache.n_pages for p in engine.cache.book.pools)
+    # and once more in the other order on the same engine, over the pages the first run dirtied
+    got = run_batches(engine, requests, batches[::-1], prompt_lens)
+    compare(got, oracle, requests, dtype, CONFIGS[name], f"{name} batches again")
+    print(f"{name} {dtype} batches: worst error/tolerance {worst}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_decoding(model, dtype):
+    """One short prompt, then some hundred tokens one by one (across several pages and, for
+    window layers, several turns of the ring), beside a second sequence that ends early."""
+    name, folder, oracle, _ = model
+    cfg = CONFIGS[name]
+    long_req, short_req = random_requests(cfg, [280, 40], seed=99)
+    engine = build_engine(folder, dtype, max_tokens=320 + 64)
+    got = run_batches(engine, [long_req, short_req], [[0, 1]], [3, 2])
+    compare(got, oracle, [long_req, short_req], dtype, cfg, f"{name} long decoding")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_first_tokens(model, dtype):
+    """Positions 0, 1, 2 of a sequence, fed one by one from an empty slot."""
+    name, folder, oracle, _ = model
+    cfg = CONFIGS[name]
+    reqs = random_requests(cfg, [4, 3], seed=5)
+    engine = build_engine(folder, dtype, max_tokens=128)
+    got = run_batches(engine, reqs, [[0, 1]], [1, 1])
+    compare(got, oracle, reqs, dtype, cfg, f"{name} first tokens")
+
+
+def test_padding_and_company_change_nothing(model):
+    """float32: a request's logits are the same alone and in a batch, up to rounding."""
+    name, folder, oracle, requests = model
+    engine = build_engine(folder, torch.float32, max_tokens=_rooms(requests))
+    alone = run_whole(engine, requests)
+    together = run_batches(engine, requests, [list(range(len(requests)))], [len(r) for r in requests])
+    for key, row in alone.items():
+        assert np.abs(row - together[key]).max() < 2e-5, key
+
+
+def test_step_errors_leave_the_cache_alone(model):
+    from llaisys_b200.cache import CacheFull
+    from llaisys_b200.engine import StepEntry, StepError
+    name, folder, _, requests = model
+    cfg = CONFIGS[name]
+    engine = build_engine(folder, torch.float32, max_tokens=128, max_seqs=2)
+    a, b = engine.acquire(), engine.acquire()
+    with pytest.raises(CacheFull):
+        engine.acquire()
+    with pytest.raises(StepError, match="vocabulary"):
+        engine.step([StepEntry(a, [cfg["vocab_size"]], [0])])
+    with pytest.raises(StepError, match="twice"):
+        engine.step([StepEntry(a, [1], [0]), StepEntry(a, [2], [0])])
+    with pytest.raises(StepError, match="wanted"):
+        engine.step([StepEntry(a, [1], [1])])
+    with pytest.raises(StepError, match="at least one"):
+        engine.step([StepEntry(a, [], [])])
+    with pytest.raises(CacheFull):
+        engine.step([StepEntry(a, [1] * 60, []), StepEntry(b, [1] * 70, [])])       # 64 + 128 > 128
+    assert engine.length(a) == 0 and engine.length(b) == 0
+    assert engine.cache.book.pools[0].available == engine.cache.n_pages            # the failed step kept no page
+    assert engine.step([StepEntry(a, [1, 2, 3], [])]) is None and engine.length(a) == 3
+    with pytest.raises(StepError, match="positions"):
+        engine.step([StepEntry(b, [1] * (cfg["max_position_embeddings"] + 1), [])])
+    engine.release(a)
+    engine.release(b)

@@ -1,0 +1,305 @@
+"""Each kernel alone against the plain formulas, at sizes other than the tiny models'."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen2 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def _tol(dtype, scale=1.0):
+    return (2e-5 if dtype == torch.float32 else 2.0 ** -7) * scale
+
+
+def _rt(x, dtype):
+    """float64 numpy values as the kernel sees them after rounding to dtype."""
+    return torch.from_numpy(np.asarray(x)).to(dtype).double().numpy()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding(dtype):
+    from llaisys_b200 import kernels
+    rng = np.random.default_rng(0)
+    table = torch.from_numpy(rng.normal(size=(301, 72))).to(dtype).to(DEV)
+    ids = torch.tensor([0, 300, 17, 17, 5], dtype=torch.int32, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = kernels.embedding(ids, table, err)
+    assert out.dtype == torch.float32 and torch.equal(out, table[ids.long()].float()) and int(err) == 0
+    bad = torch.tensor([3, 301], dtype=torch.int32, device=DEV)
+    out = kernels.embedding(bad, table, err)
+    assert int(err) == 1 and float(out[1].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H", [(1, 8), (5, 200), (37, 1536), (3, 5000)])
+def test_add_rmsnorm(dtype, T, H):
+    from llaisys_b200 import kernels
+    rng = np.random.default_rng(T * H)
+    res, delta, w = rng.normal(size=(T, H)), rng.normal(size=(T, H)), 1 + 0.1 * rng.normal(size=H)
+    res_t = torch.from_numpy(res).float().to(DEV)
+    delta_t = torch.from_numpy(delta).to(dtype).to(DEV)
+    w_t = torch.from_numpy(w).to(dtype).to(DEV)
+    x = res_t.double().cpu().numpy() + _rt(delta, dtype)
+    want = plain.rms_norm(x, _rt(w, dtype), 1e-5)
+    out = kernels.add_rmsnorm(res_t, delta_t, w_t, 1e-5, dtype)
+    assert np.abs(res_t.double().cpu().numpy() - x).max() < 1e-6          # the sum is kept in float32
+    assert np.abs(out.double().cpu().numpy() - want).max() < _tol(dtype, 4)
+    # no delta; a float32 weight under a bfloat16 model; a gather that leaves the residual alone
+    keep = res_t.clone()
+    rows = torch.tensor([T - 1, 0], dtype=torch.int32, device=DEV)
+    out = kernels.add_rmsnorm(res_t, None, torch.from_numpy(w).float().to(DEV), 1e-5, dtype, rows=rows)
+    want = plain.rms_norm(keep.double().cpu().numpy()[[T - 1, 0]], _rt(w, torch.float32), 1e-5)
+    assert torch.equal(res_t, keep) and np.abs(out.double().cpu().numpy() - want).max() < _tol(dtype, 4)
+    # partial sums are added in order
+    parts = torch.from_numpy(rng.normal(size=(3, T, H))).float().to(DEV)
+    kernels.add_rmsnorm(res_t, parts, w_t, 1e-5, dtype)
+    assert np.abs(res_t.double().cpu().numpy() - (keep.double().cpu().numpy() + parts.double().sum(0).cpu().numpy())).max() < 1e-5
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 33, 70), (7, 130, 257), (8, 64, 64), (9, 100, 48), (70, 200, 300), (130, 67, 1000)])
+def test_linear(dtype, M, N, K):
+    from llaisys_b200 import kernels
+    rng = np.random.default_rng(M + N + K)
+    x, w, b = rng.normal(size=(M, K)), rng.normal(size=(N, K)) * 0.1, rng.normal(size=N)
+    xt, wt, bt = (torch.from_numpy(a).to(dtype).to(DEV) for a in (x, w, b))
+    want = plain.linear(_rt(x, dtype), _rt(w, dtype), _rt(b, dtype))
+    got = kernels.linear(xt, wt, bt, out_dtype=torch.float32)
+    assert np.abs(got.double().cpu().numpy() - want).max() < 1e-4 * math.sqrt(K)
+    got = kernels.linear(xt, wt)                      # no bias, activation dtype out
+    want = plain.linear(_rt(x, dtype), _rt(w, dtype))
+    assert np.abs(got.double().cpu().numpy() - want).max() < _tol(dtype, 8)
+    # a strided view as input, a float32 weight under bfloat16 activations
+    wide = torch.zeros((M, K + 24), dtype=dtype, device=DEV)
+    wide[:, 8:8 + K] = xt
+    got = kernels.linear(wide[:, 8:8 + K], torch.from_numpy(w).float().to(DEV), out_dtype=torch.float32)
+    want = plain.linear(_rt(x, dtype), _rt(w, torch.float32))
+    assert np.abs(got.double().cpu().numpy() - want).max() < 1e-4 * math.sqrt(K)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(dtype):
+    from llaisys_b200 import kernels
+    rng = np.random.default_rng(4)
+    gu = rng.normal(size=(11, 2 * 136)) * 3
+    got = kernels.swiglu(torch.from_numpy(gu).to(dtype).to(DEV))
+    r = _rt(gu, dtype)
+    assert np.abs(got.double().cpu().numpy() - plain.swiglu(r[:, :136], r[:, 136:])).max() < _tol(dtype, 8)
+
+
+def _paged(kv, page_ids, dtype):
+    """kv: [L, nkvh, d] numpy -> pool [pages, nkvh, 64, d] with the sequence's pages at page_ids."""
+    L, nkvh, d = kv.shape
+    pool = torch.full((max(page_ids) + 2, nkvh, 64, d), float("nan"), dtype=dtype)
+    for lp, pid in enumerate(page_ids):
+        chunk = torch.from_numpy(kv[lp * 64:(lp + 1) * 64]).to(dtype)          # [n, nkvh, d]
+        pool[pid, :, :chunk.shape[0]] = chunk.permute(1, 0, 2)
+    return pool.to(DEV)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("theta,dh", [(1e4, 32), (1e6, 48)])
+def test_rope_and_append(dtype, theta, dh):
+    from llaisys_b200 import kernels
+    from llaisys_b200.config import PartSpec
+    from llaisys_b200.parts import BuildEnv, build_part
+    nh, nkvh = 3, 1
+    rope = build_part("position", PartSpec("rope_half_split", {"head_dim": dh, "theta": theta}),
+                      BuildEnv(dtype, torch.device(DEV)))
+    rng = np.random.default_rng(5)
+    # two sequences: 70 cached + 3 new, 0 cached + 66 new
+    lens, news = [70, 0], [3, 66]
+    T = sum(news)
+    qkv = rng.normal(size=(T, (nh + 2 * nkvh) * dh))
+    qkv_t = torch.from_numpy(qkv).to(dtype).to(DEV)
+    tok_seq = torch.tensor([0] * 3 + [1] * 66, dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([70, 71, 72] + list(range(66)), dtype=torch.int32, device=DEV)
+    seq_start = torch.tensor([0, 3, 69], dtype=torch.int32, device=DEV)
+    len_before = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    table = torch.tensor([[4, 1], [0, 3]], dtype=torch.int32, device=DEV)
+    kpool = torch.zeros((5, nkvh, 64, dh), dtype=dtype, device=DEV)
+    vpool = torch.zeros_like(kpool)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    cos, sin = rope.table(73)
+    kernels.rope_append(qkv_t, nh, nkvh, dh, cos=cos, sin=sin, tok_pos=tok_pos, err=err,
+                        append=dict(tok_seq=tok_seq, seq_start=seq_start, seq_len_before=len_before,
+                                    kpool=kpool, vpool=vpool, page_table=table, ring=2))
+    assert int(err) == 0
+    r = _rt(qkv, dtype).reshape(T, nh + 2 * nkvh, dh)
+    pos = tok_pos.cpu().numpy()
+    want_qk = plain.rope(r[:, :nh + nkvh], pos, theta)
+    got = qkv_t.double().cpu().numpy().reshape(T, nh + 2 * nkvh, dh)
+    assert np.abs(got[:, :nh + nkvh] - want_qk).max() < _tol(dtype, 4)
+    assert np.array_equal(got[:, nh + nkvh:], r[:, nh + nkvh:])               # values untouched
+    kp, vp = kpool.double().cpu().numpy(), vpool.double().cpu().numpy()
+    pages = table.cpu().numpy()
+    for t in range(T):
+        s, p = int(tok_seq[t]), int(pos[t])
+        page = pages[s][p // 64]
+        assert np.array_equal(kp[page, 0, p % 64], got[t, nh]) and np.array_equal(vp[page, 0, p % 64], r[t, nh + 1])
+    assert float(kpool[2].abs().sum()) == 0.0                                 # a page of no one stays untouched
+    # a position beyond the table is reported, not read
+    kernels.rope_append(qkv_t, nh, nkvh, dh, cos=cos[:10], sin=sin[:10], tok_pos=tok_pos, err=err)
+    assert int(err) == 2
+
+
+def _attention_case(dtype, nh, nkvh, dh, lens_before, news, window, seed, ring=None, gain=3.0):
+    """Random q, k, v with sharp scores; returns device inputs and the plain outputs."""
+    rng = np.random.default_rng(seed)
+    B, T = len(news), sum(news)
+    width = nh + 2 * nkvh
+    qkv = rng.normal(size=(T, width, dh))
+    qkv[:, :nh + nkvh] *= gain
+    n_pages_seq = [-(-(l + n) // 64) for l, n in zip(lens_before, news)]
+    perm = rng.permutation(sum(n_pages_seq) + 3).tolist()
+    past_k = [rng.normal(size=(l, nkvh, dh)) * gain for l in lens_before]
+    past_v = [rng.normal(size=(l, nkvh, dh)) for l in lens_before]
+    tables, outs, t0 = [], [], 0
+    P = max(n_pages_seq)
+    kpool = torch.full((len(perm), nkvh, 64, dh), float("nan"), dtype=dtype)
+    vpool = torch.full_like(kpool, float("nan"))
+    for b in range(B):
+        ids = [perm.pop() for _ in range(n_pages_seq[b])]
+        tables.append(ids + [0] * (P - len(ids)))
+        for lp, pid in enumerate(ids):
+            for pool, past in ((kpool, past_k[b]), (vpool, past_v[b])):
+                chunk = torch.from_numpy(past[lp * 64:(lp + 1) * 64]).to(dtype)
+                if chunk.shape[0]:
+                    pool[pid, :, :chunk.shape[0]] = chunk.permute(1, 0, 2)
+        new = _rt(qkv[t0:t0 + news[b]], dtype)
+        k = np.concatenate([_rt(past_k[b], dtype), new[:, nh:nh + nkvh]])
+        v = np.concatenate([_rt(past_v[b], dtype), new[:, nh + nkvh:]])
+        outs.append(plain.self_attention(new[:, :nh], k, v, 1 / math.sqrt(dh), window))
+        t0 += news[b]
+    dev = dict(
+        qkv=torch.from_numpy(qkv.reshape(T, width * dh)).to(dtype).to(DEV), kpool=kpool.to(DEV), vpool=vpool.to(DEV),
+        table=torch.tensor(tables, dtype=torch.int32, device=DEV),
+        seq_start=torch.tensor(np.concatenate([[0], np.cumsum(news)]), dtype=torch.int32, device=DEV),
+        len_before=torch.tensor(lens_before, dtype=torch.int32, device=DEV))
+    return dev, np.concatenate(outs).reshape(T, nh * dh)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkvh,dh,window", [(4, 2, 32, None), (6, 1, 48, 70), (3, 3, 64, 5), (8, 2, 128, None), (2, 1, 16, 64)])
+def test_attention_prefill(dtype, nh, nkvh, dh, window):
+    from llaisys_b200 import kernels
+    lens_before, news = [0, 130, 64, 5], [100, 37, 1, 200]
+    d, want = _attention_case(dtype, nh, nkvh, dh, lens_before, news, window, seed=nh * dh)
+    got = kernels.attention_prefill(d["qkv"], nh, nkvh, dh, d["kpool"], d["vpool"], d["table"], d["table"].shape[1],
+                                    d["seq_start"], d["len_before"], len(news), max(news), window, 1 / math.sqrt(dh))
+    err = np.abs(got.double().cpu().numpy() - want)
+    assert np.isfinite(err).all() and err.max() < _tol(dtype, 4), np.unravel_index(err.argmax(), err.shape)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh,nkvh,dh,window", [(4, 2, 32, None), (6, 1, 48, 70), (12, 2, 128, None), (5, 5, 64, 3), (40, 1, 16, 129)])
+@pytest.mark.parametrize("splits", [1, 3, 7])
+def test_attention_decode(dtype, nh, nkvh, dh, window, splits):
+    from llaisys_b200 import kernels
+    lens_before, news = [0, 129, 63, 64, 500], [1, 1, 1, 1, 1]
+    d, want = _attention_case(dtype, nh, nkvh, dh, lens_before, news, window, seed=nh + dh + splits)
+    # decode reads the cache alone: put the new keys and values there first
+    tok = torch.arange(5, dtype=torch.int32, device=DEV)
+    kernels.rope_append(d["qkv"], nh, nkvh, dh, append=dict(
+        tok_seq=tok, seq_start=d["seq_start"], seq_len_before=d["len_before"], kpool=d["kpool"], vpool=d["vpool"],
+        page_table=d["table"], ring=d["table"].shape[1]), err=torch.zeros(1, dtype=torch.int32, device=DEV))
+    got = kernels.attention_decode(d["qkv"], nh, nkvh, dh, d["kpool"], d["vpool"], d["table"], d["table"].shape[1],
+                                   d["seq_start"], d["len_before"], 5, window, 1 / math.sqrt(dh), n_splits=splits)
+    err = np.abs(got.double().cpu().numpy() - want)
+    assert np.isfinite(err).all() and err.max() < _tol(dtype, 4), np.unravel_index(err.argmax(), err.shape)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_a_far_key(dtype):
+    """One key among several hundred matches the query; the output must be its value."""
+    from llaisys_b200 import kernels
+    nh, nkvh, dh, L = 2, 1, 32, 700
+    for far in (0, 63, 64, 401, 698):
+        rng = np.random.default_rng(far)
+        k = rng.normal(size=(L + 1, nkvh, dh)) * 0.1
+        v = rng.normal(size=(L + 1, nkvh, dh))
+        q = np.zeros((1, nh + 2, dh))
+        q[0, :nh] = 20.0 * np.sign(rng.normal(size=dh))
+        k[far, 0] = q[0, 0] * 1.0
+        q[0, nh], q[0, nh + 1] = k[L, 0], v[L, 0]
+        pages = list(range(11, 0, -1))
+        kpool, vpool = _paged(k[:L], pages, dtype), _paged(v[:L], pages, dtype)
+        qkv = torch.from_numpy(q.reshape(1, -1)).to(dtype).to(DEV)
+        table = torch.tensor([pages], dtype=torch.int32, device=DEV)
+        ss = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+        lb = torch.tensor([L], dtype=torch.int32, device=DEV)
+        kernels.rope_append(qkv, nh, nkvh, dh, append=dict(tok_seq=torch.zeros(1, dtype=torch.int32, device=DEV),
+                            seq_start=ss, seq_len_before=lb, kpool=kpool, vpool=vpool, page_table=table, ring=11),
+                            err=torch.zeros(1, dtype=torch.int32, device=DEV))
+        for splits in (1, 4):
+            out = kernels.attention_decode(qkv, nh, nkvh, dh, kpool, vpool, table, 11, ss, lb, 1, None, 1.0, n_splits=splits)
+            assert np.abs(out[0, :dh].double().cpu().numpy() - _rt(v[far, 0], dtype)).max() < 1e-2
+        out = kernels.attention_prefill(qkv, nh, nkvh, dh, kpool, vpool, table, 11, ss, lb, 1, 1, None, 1.0)
+        assert np.abs(out[0, :dh].double().cpu().numpy() - _rt(v[far, 0], dtype)).max() < 1e-2
+
+
+def test_argmax_first_maximum():
+    from llaisys_b200 import kernels
+    rng = np.random.default_rng(1)
+    x = rng.normal(size=(6, 5003)).astype(np.float32)
+    x[1, 4000] = x[1, 77] = 9.0
+    x[2, :] = -np.inf
+    x[3, 5002] = 50.0
+    x[4, 0] = 50.0
+    got = kernels.argmax(torch.from_numpy(x).to(DEV)).tolist()
+    assert got == [plain.argmax(r) for r in x] and got[1] == 77 and got[2] == 0
+
+
+@pytest.mark.parametrize("V", [257, 5000, 151936])
+@pytest.mark.parametrize("temperature,top_k,top_p", [(1.0, 0, 1.0), (0.7, 0, 1.0), (1.0, 50, 1.0), (1.0, 0, 0.8),
+                                                     (0.8, 50, 0.8), (1.3, 7, 0.3), (1.0, 1, 1.0), (0.0, 0, 1.0)])
+def test_sampling_follows_the_rule(V, temperature, top_k, top_p):
+    from llaisys_b200 import kernels
+    rng = np.random.default_rng(V + top_k)
+    R = 24
+    logits = (rng.normal(size=(R, V)) * 3).astype(np.float32)
+    logits[0, 5:9] = logits[0].max() + 1.0                  # ties at the top
+    logits[1, :] = 0.25                                     # all equal
+    lt = torch.from_numpy(logits).to(DEV)
+    keys = torch.arange(R, dtype=torch.int32, device=DEV) + 100
+    steps = torch.arange(R, dtype=torch.int32, device=DEV) * 3
+    got = kernels.sample(lt, temperature, top_k, top_p, 1234, keys, steps).tolist()
+    miss = 0
+    for r in range(R):
+        u = kernels.uniform(1234, 100 + r, 3 * r)
+        want = plain.sample(logits[r], temperature, top_k, top_p, u)
+        if got[r] != want:
+            # float32 exp against float64: a draw that lands within rounding of a boundary may fall to
+            # the neighbour; it must still be a kept token right next to the boundary
+            lo, hi = plain.sample(logits[r], temperature, top_k, top_p, max(0.0, u - 1e-5)), \
+                plain.sample(logits[r], temperature, top_k, top_p, min(1 - 1e-12, u + 1e-5))
+            assert got[r] in (lo, hi), (r, got[r], want)
+            miss += 1
+    assert miss <= 1
+
+
+def test_sampling_statistics_and_reproducibility():
+    from llaisys_b200 import kernels
+    p = np.array([0.5, 0.25, 0.125, 0.125])
+    logits = torch.from_numpy(np.log(p)).float().to(DEV).repeat(4000, 1)
+    keys = torch.arange(4000, dtype=torch.int32, device=DEV)
+    steps = torch.zeros(4000, dtype=torch.int32, device=DEV)
+    a = kernels.sample(logits, 1.0, 0, 1.0, 7, keys, steps)
+    assert torch.equal(a, kernels.sample(logits, 1.0, 0, 1.0, 7, keys, steps))
+    assert not torch.equal(a, kernels.sample(logits, 1.0, 0, 1.0, 8, keys, steps))
+    freq = np.bincount(a.cpu().numpy(), minlength=4) / 4000
+    assert np.abs(freq - p).max() < 0.03
+    b = kernels.sample(logits, 1.0, 2, 1.0, 7, keys, steps).cpu().numpy()
+    assert set(b.tolist()) == {0, 1} and abs((b == 0).mean() - 2 / 3) < 0.03
+    # the device's uniform is the documented function of (seed, key, step)
+    import ctypes
+    from llaisys_b200.csrc.build import load_module
+    f = load_module("sampling.cu").llb_uniform_host
+    f.restype, f.argtypes = ctypes.c_double, [ctypes.c_ulonglong] * 3
+    for s, k, t in [(0, 0, 0), (7, 3, 9), (2 ** 40 + 5, 2 ** 31 - 1, 12345)]:
+        assert f(s, k, t) == kernels.uniform(s, k, t)
