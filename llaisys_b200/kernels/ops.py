@@ -125,9 +125,11 @@ def rope_append(qkv: torch.Tensor, nh: int, nkvh: int, dh: int, *, cos=None, sin
     (when cos/sin tables are given) and/or write keys and values to the paged cache.
 
     append = dict(tok_seq, seq_start, seq_len_before, kpool, vpool, page_table, ring)."""
-    _need_cuda(qkv)
+    _need_cuda(qkv, tok_pos)
     T = qkv.shape[0]
     assert qkv.stride(1) == 1
+    if tok_pos is None or tok_pos.numel() != T or err is None:
+        raise KernelError("rope_append needs tok_pos (one position per packed token) and an error word")
     do_rope, do_app = cos is not None, append is not None
     a = append or {}
     pt = a.get("page_table")

@@ -77,7 +77,7 @@ class GQAttention(Mixer):
         if self.position is not None:
             self.position.apply(qkv, self.nh, self.nkvh, ctx, append=append if decode else None)
         elif decode and append:
-            kernels.rope_append(qkv, self.nh, self.nkvh, self.dh, append=append, err=ctx.err)
+            kernels.rope_append(qkv, self.nh, self.nkvh, self.dh, tok_pos=ctx.tok_pos, append=append, err=ctx.err)
         common = (qkv, self.nh, self.nkvh, self.dh, kv.k, kv.v, kv.page_table, kv.ring,
                   ctx.seq_start, ctx.seq_len_before, ctx.n_seqs)
         if decode:
@@ -86,5 +86,5 @@ class GQAttention(Mixer):
             out = kernels.attention_prefill(*common, ctx.max_new, self.window, self.scale,
                                             all_from_cache=not kv.writable)
             if append:
-                kernels.rope_append(qkv, self.nh, self.nkvh, self.dh, append=append, err=ctx.err)
+                kernels.rope_append(qkv, self.nh, self.nkvh, self.dh, tok_pos=ctx.tok_pos, append=append, err=ctx.err)
         return kernels.linear(out, self.w_o, self.b_o)

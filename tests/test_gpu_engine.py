@@ -13,12 +13,32 @@ DTYPES = [torch.float32, torch.bfloat16]
 LENGTHS = {"A": [5, 9, 2, 64, 150], "B": [1, 7, 13, 20, 65, 200], "C": [3, 70, 71, 129, 300]}
 
 
+# Query and key projections are scaled up so that attention is not flat and a lost or misplaced
+# key shows in the logits.  Under float32 the scores spread over about +-10; under bfloat16 a
+# score's own rounding error grows with its size (|s| * 2^-9) and passes through the softmax, so
+# the spread is kept near +-3 there, where that stays inside the bound of helpers.tolerance.
+GAIN = {torch.float32: 12.0, torch.bfloat16: 5.0}
+
+
+class Model:
+    def __init__(self, name, tmp):
+        self.name, self.requests = name, random_requests(CONFIGS[name], LENGTHS[name], seed=ord(name))
+        self._tmp, self._made = tmp, {}
+
+    def __iter__(self):           # (name, folder, oracle, requests) of the float32 variant
+        return iter((self.name, *self.at(torch.float32), self.requests))
+
+    def at(self, dtype):
+        if dtype not in self._made:
+            folder = make_folder(self._tmp / f"gain{int(GAIN[dtype])}", CONFIGS[self.name], seed=ord(self.name),
+                                 attn_gain=GAIN[dtype])
+            self._made[dtype] = (folder, Oracle(folder))
+        return self._made[dtype]
+
+
 @pytest.fixture(scope="module", params=["A", "B", "C"])
 def model(request, tmp_path_factory):
-    name = request.param
-    folder = make_folder(tmp_path_factory.mktemp(f"tiny{name}"), CONFIGS[name], seed=ord(name), attn_gain=12.0)
-    requests = random_requests(CONFIGS[name], LENGTHS[name], seed=ord(name))
-    return name, folder, Oracle(folder), requests
+    return Model(request.param, tmp_path_factory.mktemp(f"tiny{request.param}"))
 
 
 def _rooms(requests):
@@ -27,7 +47,8 @@ def _rooms(requests):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_each_request_alone_and_whole(model, dtype):
-    name, folder, oracle, requests = model
+    name, requests = model.name, model.requests
+    folder, oracle = model.at(dtype)
     engine = build_engine(folder, dtype, max_tokens=max(-(-len(r) // 64) * 64 for r in requests))
     worst = compare(run_whole(engine, requests), oracle, requests, dtype, CONFIGS[name], f"{name} whole")
     print(f"{name} {dtype} whole: worst error/tolerance {worst}")
@@ -35,7 +56,8 @@ def test_each_request_alone_and_whole(model, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_last_tokens_one_by_one(model, dtype):
-    name, folder, oracle, requests = model
+    name, requests = model.name, model.requests
+    folder, oracle = model.at(dtype)
     engine = build_engine(folder, dtype, max_tokens=max(-(-len(r) // 64) * 64 for r in requests))
     worst = compare(run_tail_by_one(engine, requests), oracle, requests, dtype, CONFIGS[name], f"{name} tail-by-one")
     print(f"{name} {dtype} tail: worst error/tolerance {worst}")
@@ -43,7 +65,8 @@ def test_last_tokens_one_by_one(model, dtype):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_unequal_batches_with_slot_reuse(model, dtype):
-    name, folder, oracle, requests = model
+    name, requests = model.name, model.requests
+    folder, oracle = model.at(dtype)
     n = len(requests)
     # two batches, one after the other, in a cache that only just holds the larger one: pages and
     # slots of the first batch are used again by the second
@@ -64,7 +87,8 @@ def test_unequal_batches_with_slot_reuse(model, dtype):
 def test_long_decoding(model, dtype):
     """One short prompt, then some hundred tokens one by one (across several pages and, for
     window layers, several turns of the ring), beside a second sequence that ends early."""
-    name, folder, oracle, _ = model
+    name = model.name
+    folder, oracle = model.at(dtype)
     cfg = CONFIGS[name]
     long_req, short_req = random_requests(cfg, [280, 40], seed=99)
     engine = build_engine(folder, dtype, max_tokens=320 + 64)
@@ -75,7 +99,8 @@ def test_long_decoding(model, dtype):
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_first_tokens(model, dtype):
     """Positions 0, 1, 2 of a sequence, fed one by one from an empty slot."""
-    name, folder, oracle, _ = model
+    name = model.name
+    folder, oracle = model.at(dtype)
     cfg = CONFIGS[name]
     reqs = random_requests(cfg, [4, 3], seed=5)
     engine = build_engine(folder, dtype, max_tokens=128)

@@ -16,10 +16,27 @@ pytestmark = pytest.mark.gpu
 ROOT = Path(__file__).resolve().parents[1]
 
 
+class Folders:
+    """Model folders per configuration; the bfloat16 runs get a milder attention gain (see
+    test_gpu_engine.GAIN for why)."""
+
+    def __init__(self, tmp):
+        self._tmp, self._made = tmp, {}
+
+    def get(self, name, dtype="float32"):
+        gain = 5.0 if dtype == "bfloat16" else 8.0
+        if (name, gain) not in self._made:
+            self._made[(name, gain)] = make_folder(self._tmp / f"{name}{int(gain)}", CONFIGS[name],
+                                                   seed=7 + ord(name), attn_gain=gain)
+        return self._made[(name, gain)]
+
+    def __getitem__(self, name):
+        return self.get(name)
+
+
 @pytest.fixture(scope="module")
 def folders(tmp_path_factory):
-    return {n: make_folder(tmp_path_factory.mktemp(f"gen{n}"), CONFIGS[n], seed=7 + i, attn_gain=8.0)
-            for i, n in enumerate("AB")}
+    return Folders(tmp_path_factory.mktemp("gen"))
 
 
 def _greedy_is_consistent(oracle, prompt, new, dtype, config):
@@ -38,8 +55,9 @@ def _greedy_is_consistent(oracle, prompt, new, dtype, config):
 def test_greedy_generation_through_the_entry_point(folders, name, dtype):
     from llaisys_b200.models import DeviceType, Qwen2
     cfg = CONFIGS[name]
-    oracle = Oracle(folders[name])
-    model = Qwen2(folders[name], DeviceType.NVIDIA, dtype=dtype, max_tokens=64 * 4)
+    folder = folders.get(name, dtype)
+    oracle = Oracle(folder)
+    model = Qwen2(folder, DeviceType.NVIDIA, dtype=dtype, max_tokens=64 * 4)
     prompts = random_requests(cfg, [5, 9, 2, 30, 1, 17], seed=3)
     # the cache holds four rooms of 64: the six requests take two batches, slots are used again
     outs = model.generate_batch(prompts, max_new_tokens=8, top_k=1, stop_ids=[])
@@ -133,7 +151,8 @@ def test_trace_run(folders, tmp_path, dtype):
     lines.insert(3, json.dumps({"step": 1000, "entries": [], "end": []}))        # a step with nothing in it
     out_dir = tmp_path / "out"
     room = max(sum(-(-len(requests[r]) // 64) * 64 for r in b) for b in batches)
-    proc = subprocess.run([str(ROOT / "bin" / "trace_run"), "--model", str(folders[name]), "--dtype", dtype, "--out", str(out_dir),
+    folder = folders.get(name, dtype)
+    proc = subprocess.run([str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out_dir),
                            "--max-tokens", str(room)], input="\n".join(lines) + "\n", capture_output=True, text=True, timeout=900)
     assert proc.returncode == 0, proc.stderr[-3000:]
     done = [l for l in proc.stdout.splitlines() if l.startswith("done ")]
@@ -144,4 +163,4 @@ def test_trace_run(folders, tmp_path, dtype):
         for i, key in enumerate(rows):
             got[key] = data[i]
     assert not (out_dir / "1000.f32").exists()
-    compare(got, Oracle(folders[name]), requests, torch.float32 if dtype == "float32" else torch.bfloat16, cfg, "trace_run")
+    compare(got, Oracle(folder), requests, torch.float32 if dtype == "float32" else torch.bfloat16, cfg, "trace_run")

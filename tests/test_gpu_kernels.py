@@ -16,6 +16,21 @@ def _tol(dtype, scale=1.0):
     return (2e-5 if dtype == torch.float32 else 2.0 ** -7) * scale
 
 
+def _close(got, want, dtype, atol=None):
+    """The kernel computes in float32 from the same rounded inputs as the plain formula, so what
+    remains is float32 summation error and, for bfloat16, the rounding of the output itself
+    (half a unit in the last place: 2^-9 relative; 2^-8 is allowed)."""
+    got = got.double().cpu().numpy() if isinstance(got, torch.Tensor) else got
+    if dtype == torch.float32:
+        bound = (atol or 2e-5) + 1e-5 * np.abs(want)
+    else:
+        bound = (atol or 1e-3) + 2.0 ** -8 * np.abs(want)
+    err = np.abs(got - want)
+    assert np.isfinite(got).all(), "non-finite output"
+    worst = np.unravel_index(np.argmax(err - bound), err.shape)
+    assert (err <= bound).all(), f"worst at {worst}: got {got[worst]}, want {want[worst]}"
+
+
 def _rt(x, dtype):
     """float64 numpy values as the kernel sees them after rounding to dtype."""
     return torch.from_numpy(np.asarray(x)).to(dtype).double().numpy()
@@ -48,13 +63,14 @@ def test_add_rmsnorm(dtype, T, H):
     want = plain.rms_norm(x, _rt(w, dtype), 1e-5)
     out = kernels.add_rmsnorm(res_t, delta_t, w_t, 1e-5, dtype)
     assert np.abs(res_t.double().cpu().numpy() - x).max() < 1e-6          # the sum is kept in float32
-    assert np.abs(out.double().cpu().numpy() - want).max() < _tol(dtype, 4)
+    _close(out, want, dtype)
     # no delta; a float32 weight under a bfloat16 model; a gather that leaves the residual alone
     keep = res_t.clone()
     rows = torch.tensor([T - 1, 0], dtype=torch.int32, device=DEV)
     out = kernels.add_rmsnorm(res_t, None, torch.from_numpy(w).float().to(DEV), 1e-5, dtype, rows=rows)
     want = plain.rms_norm(keep.double().cpu().numpy()[[T - 1, 0]], _rt(w, torch.float32), 1e-5)
-    assert torch.equal(res_t, keep) and np.abs(out.double().cpu().numpy() - want).max() < _tol(dtype, 4)
+    assert torch.equal(res_t, keep)
+    _close(out, want, dtype)
     # partial sums are added in order
     parts = torch.from_numpy(rng.normal(size=(3, T, H))).float().to(DEV)
     kernels.add_rmsnorm(res_t, parts, w_t, 1e-5, dtype)
@@ -73,7 +89,7 @@ def test_linear(dtype, M, N, K):
     assert np.abs(got.double().cpu().numpy() - want).max() < 1e-4 * math.sqrt(K)
     got = kernels.linear(xt, wt)                      # no bias, activation dtype out
     want = plain.linear(_rt(x, dtype), _rt(w, dtype))
-    assert np.abs(got.double().cpu().numpy() - want).max() < _tol(dtype, 8)
+    _close(got, want, dtype, atol=1e-4 if dtype == torch.float32 else 2e-3)
     # a strided view as input, a float32 weight under bfloat16 activations
     wide = torch.zeros((M, K + 24), dtype=dtype, device=DEV)
     wide[:, 8:8 + K] = xt
@@ -89,7 +105,7 @@ def test_swiglu(dtype):
     gu = rng.normal(size=(11, 2 * 136)) * 3
     got = kernels.swiglu(torch.from_numpy(gu).to(dtype).to(DEV))
     r = _rt(gu, dtype)
-    assert np.abs(got.double().cpu().numpy() - plain.swiglu(r[:, :136], r[:, 136:])).max() < _tol(dtype, 8)
+    _close(got, plain.swiglu(r[:, :136], r[:, 136:]), dtype)
 
 
 def _paged(kv, page_ids, dtype):
@@ -134,7 +150,7 @@ def test_rope_and_append(dtype, theta, dh):
     pos = tok_pos.cpu().numpy()
     want_qk = plain.rope(r[:, :nh + nkvh], pos, theta)
     got = qkv_t.double().cpu().numpy().reshape(T, nh + 2 * nkvh, dh)
-    assert np.abs(got[:, :nh + nkvh] - want_qk).max() < _tol(dtype, 4)
+    _close(got[:, :nh + nkvh], want_qk, dtype)
     assert np.array_equal(got[:, nh + nkvh:], r[:, nh + nkvh:])               # values untouched
     kp, vp = kpool.double().cpu().numpy(), vpool.double().cpu().numpy()
     pages = table.cpu().numpy()
@@ -192,8 +208,7 @@ def test_attention_prefill(dtype, nh, nkvh, dh, window):
     d, want = _attention_case(dtype, nh, nkvh, dh, lens_before, news, window, seed=nh * dh)
     got = kernels.attention_prefill(d["qkv"], nh, nkvh, dh, d["kpool"], d["vpool"], d["table"], d["table"].shape[1],
                                     d["seq_start"], d["len_before"], len(news), max(news), window, 1 / math.sqrt(dh))
-    err = np.abs(got.double().cpu().numpy() - want)
-    assert np.isfinite(err).all() and err.max() < _tol(dtype, 4), np.unravel_index(err.argmax(), err.shape)
+    _close(got, want, dtype, atol=1e-4 if dtype == torch.float32 else 2e-3)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -205,13 +220,12 @@ def test_attention_decode(dtype, nh, nkvh, dh, window, splits):
     d, want = _attention_case(dtype, nh, nkvh, dh, lens_before, news, window, seed=nh + dh + splits)
     # decode reads the cache alone: put the new keys and values there first
     tok = torch.arange(5, dtype=torch.int32, device=DEV)
-    kernels.rope_append(d["qkv"], nh, nkvh, dh, append=dict(
+    kernels.rope_append(d["qkv"], nh, nkvh, dh, tok_pos=d["len_before"], append=dict(
         tok_seq=tok, seq_start=d["seq_start"], seq_len_before=d["len_before"], kpool=d["kpool"], vpool=d["vpool"],
         page_table=d["table"], ring=d["table"].shape[1]), err=torch.zeros(1, dtype=torch.int32, device=DEV))
     got = kernels.attention_decode(d["qkv"], nh, nkvh, dh, d["kpool"], d["vpool"], d["table"], d["table"].shape[1],
                                    d["seq_start"], d["len_before"], 5, window, 1 / math.sqrt(dh), n_splits=splits)
-    err = np.abs(got.double().cpu().numpy() - want)
-    assert np.isfinite(err).all() and err.max() < _tol(dtype, 4), np.unravel_index(err.argmax(), err.shape)
+    _close(got, want, dtype, atol=1e-4 if dtype == torch.float32 else 2e-3)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -233,7 +247,7 @@ def test_attention_finds_a_far_key(dtype):
         table = torch.tensor([pages], dtype=torch.int32, device=DEV)
         ss = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
         lb = torch.tensor([L], dtype=torch.int32, device=DEV)
-        kernels.rope_append(qkv, nh, nkvh, dh, append=dict(tok_seq=torch.zeros(1, dtype=torch.int32, device=DEV),
+        kernels.rope_append(qkv, nh, nkvh, dh, tok_pos=lb, append=dict(tok_seq=torch.zeros(1, dtype=torch.int32, device=DEV),
                             seq_start=ss, seq_len_before=lb, kpool=kpool, vpool=vpool, page_table=table, ring=11),
                             err=torch.zeros(1, dtype=torch.int32, device=DEV))
         for splits in (1, 4):

@@ -78,7 +78,9 @@ def test_attention_part_prefill_then_decode(dtype, window):
                                       "position": PartSpec("rope_half_split", {"head_dim": dh, "theta": theta})}, prefix="a")
     att = build_part("mixer", spec, _env(dtype))
     rng = np.random.default_rng(2)
-    ws = {n: rng.normal(size=d.shape) * (0.6 if "q_proj" in n or "k_proj" in n else 0.2) for n, d in att.tensors().items()}
+    # sharp scores under float32; milder under bfloat16, where a score's rounding error grows with its size
+    qk = 0.6 if dtype == torch.float32 else 0.15
+    ws = {n: rng.normal(size=d.shape) * (qk if "q_proj" in n or "k_proj" in n else 0.2) for n, d in att.tensors().items()}
     att.load({n: torch.from_numpy(w).to(dtype).to(DEV) for n, w in ws.items()})
     cache = PagedCache([att.kv_need()], [None], [0], CacheConfig(max_tokens=128), dtype, DEV)
     x = rng.normal(size=(75, H))
@@ -95,7 +97,9 @@ def test_attention_part_prefill_then_decode(dtype, window):
     cfg = {"num_attention_heads": nh, "num_key_value_heads": nkvh, "head_dim": dh, "hidden_size": H, "rope_theta": theta}
     r = {"a." + n: torch.from_numpy(w).to(dtype).double().numpy() for n, w in ws.items()}
     want = plain.attention_block(torch.from_numpy(x).to(dtype).double().numpy(), np.arange(75), cfg, r, "a.", window)
-    assert np.abs(got - want).max() < (2e-5 if dtype == torch.float32 else 0.06)
+    # bfloat16: four roundings on the way (projections, rotation, attention output, output projection)
+    bound = 2e-5 if dtype == torch.float32 else 8 * 2.0 ** -9 * 2 * float(np.sqrt(np.mean(want ** 2)))
+    assert np.abs(got - want).max() < bound
 
 
 def test_rope_part_table_grows():
@@ -173,7 +177,7 @@ def _register_toys():
             qk = qkv[:, :(num_heads + num_kv_heads) * self.dh].view(T, -1, self.dh)
             qk += (0.01 * ctx.tok_pos.to(qkv.dtype))[:, None, None]
             if append is not None:
-                kernels.rope_append(qkv, num_heads, num_kv_heads, self.dh, append=append, err=ctx.err)
+                kernels.rope_append(qkv, num_heads, num_kv_heads, self.dh, tok_pos=ctx.tok_pos, append=append, err=ctx.err)
 
 
 def _toy_spec():
