@@ -1,0 +1,273 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of llaisys_b200 on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+The model has the layer sizes of the Qwen2-1.5B shape (DeepSeek-R1-Distill-Qwen-1.5B's
+config) with seeded random bfloat16 weights; requests are seeded uniform-random token ids.
+A "step" is one decode step.  The run times K decode steps of a batch of 8 sequences that hold
+2,048 tokens each (context 4,096), and reports on one JSON line:
+
+  value      decoded tokens a second at batch 8, timed on the device with CUDA events
+  e2e        the same through the Python entry point (generate_batch: host token ids in,
+             host token ids out, every step a pinned host-to-device copy of the step's
+             description and a device-to-host read of the chosen tokens)
+  prefill    one step over 2,048 prompt tokens: tokens a second, and its flops over the time
+             over the peak of its dtype
+  roofline   the decode step's bytes (every weight it uses once, and the cache of the live
+             requests) over its time, against the measured copy bandwidth
+  points     decode tokens a second at batch 1 and batch 64
+
+Between timed steps nothing flushes L2: each decode step streams the 3.1 GB of weights, which
+is larger than L2 (126 MB), so no step finds its inputs cached.  Peaks come from
+MEASURED_PEAKS.json beside this file when it exists, else from the fallback figures below.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN2_1_5B = {
+    "architectures": ["Qwen2ForCausalLM"],
+    "num_hidden_layers": 28, "hidden_size": 1536, "num_attention_heads": 12, "num_key_value_heads": 2,
+    "intermediate_size": 8960, "vocab_size": 151936, "max_position_embeddings": 131072,
+    "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "tie_word_embeddings": False,
+    "use_sliding_window": False, "sliding_window": 4096, "max_window_layers": 21,
+    "eos_token_id": 151643,
+}
+PROMPT_LEN, CONTEXT, PREFILL_TOKENS = 2048, 4096, 2048
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            d = json.load(open(path))
+            out = dict(FALLBACK_PEAKS)
+            out.update({k: float(v) for k, v in d.items() if k in out and isinstance(v, (int, float))})
+            return out, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm = [int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        return {"sm_mhz": int(statistics.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(sm)}
+
+
+def linear_params(cfg, layers):
+    H, I = cfg["hidden_size"], cfg["intermediate_size"]
+    dh = H // cfg["num_attention_heads"]
+    qkv = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * dh
+    per_layer = qkv * H + cfg["num_attention_heads"] * dh * H + 3 * I * H
+    return per_layer * layers, cfg["vocab_size"] * H
+
+
+def reference_arm():
+    print(json.dumps({"impl": "reference", "unavailable":
+                      "xsmccc/llaisys cannot be installed offline (pip: no setup.py or pyproject.toml at its root; its "
+                      "python package needs libllaisys.so built by xmake, which is not installed) and it has no CUDA "
+                      "path: every NVIDIA entry point is TO_BE_IMPLEMENTED, and it serves one sequence on the CPU"}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / batch 64 points and the end-to-end run")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py: llaisys_b200 is a single-GPU library; --gpus {args.gpus} is not supported (use --gpus 1)")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import numpy as np
+    import torch
+
+    from llaisys_b200 import kernels
+    from llaisys_b200.cache import CacheConfig
+    from llaisys_b200.config import config_from_dict
+    from llaisys_b200.engine import DecoderModel, Engine, StepEntry
+    from llaisys_b200.engine.generate import GenerationLoop
+    from llaisys_b200.parts import BuildEnv
+    from llaisys_b200.sampling import Sampler, SamplingParams
+    from llaisys_b200.weights import RandomSource, load_weights
+
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    cfg_dict = dict(QWEN2_1_5B)
+    full_layers = cfg_dict["num_hidden_layers"]
+    layers = args.layers or full_layers
+    cfg_dict["num_hidden_layers"] = layers
+    cfg = config_from_dict(cfg_dict)
+    model = DecoderModel(cfg.to_spec(), BuildEnv(torch.bfloat16, dev))
+    load_weights(model, RandomSource(model.expected_tensors(), seed=0, dtype=torch.bfloat16, device=dev))
+    pk, pk_src = peaks()
+    rng = np.random.default_rng(0)
+    V = cfg.vocab_size
+
+    def events():
+        return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    # ---- prefill: one step over 2,048 tokens
+    engine = Engine(model, CacheConfig(max_tokens=max(64, args.batch) * CONTEXT, max_seqs=max(64, args.batch)))
+    prompt = rng.integers(0, V, size=PREFILL_TOKENS).tolist()
+
+    def prefill_once():
+        s = engine.acquire()
+        engine.step([StepEntry(s, prompt, [PREFILL_TOKENS - 1])])
+        engine.release(s)
+
+    for _ in range(3):
+        prefill_once()
+    torch.cuda.synchronize()
+    reps = 5
+    a, b = events()
+    a.record()
+    for _ in range(reps):
+        prefill_once()
+    b.record()
+    torch.cuda.synchronize()
+    prefill_ms = a.elapsed_time(b) / reps
+    lin, head = linear_params(cfg_dict, layers)
+    dh, nh = cfg.head_dim, cfg.num_attention_heads
+    attn_flops = layers * 4 * nh * dh * (PREFILL_TOKENS * (PREFILL_TOKENS + 1) // 2)
+    prefill_flops = 2 * PREFILL_TOKENS * lin + 2 * head + attn_flops
+    prefill = {"value": round(PREFILL_TOKENS / (prefill_ms / 1e3), 1), "tokens": PREFILL_TOKENS, "ms": round(prefill_ms, 3),
+               "frac": round(prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # ---- decode at a given batch: sequences that already hold PROMPT_LEN tokens each
+    def fill(batch):
+        """Slots with PROMPT_LEN cached tokens.  Up to batch 8 the cache is filled by a real prefill;
+        larger batches get pages of random keys and values (decode timing does not depend on the
+        values, only on how many there are)."""
+        slots = [engine.acquire() for _ in range(batch)]
+        if batch <= 8:
+            engine.step([StepEntry(s, rng.integers(0, V, size=PROMPT_LEN).tolist(), []) for s in slots])
+        else:
+            for s in slots:
+                engine.cache.book.reserve(s, PROMPT_LEN)
+                engine.cache.book.commit(s, PROMPT_LEN)
+            for pool in engine.cache.k_pools + engine.cache.v_pools:
+                pool.normal_(0, 1)
+        return slots
+
+    def decode(batch, steps, warmup):
+        slots = fill(batch)
+        toks = rng.integers(0, V, size=(warmup + steps, batch)).tolist()
+        sampler = Sampler(SamplingParams(top_k=1))
+        for i in range(warmup):
+            sampler.on_device(engine.step([StepEntry(s, [t], [0]) for s, t in zip(slots, toks[i])]), slots, [i] * batch)
+        torch.cuda.synchronize()
+        n0 = kernels.launch_count()
+        a, b = events()
+        with ClockSampler() as clk:
+            a.record()
+            for i in range(warmup, warmup + steps):
+                sampler.on_device(engine.step([StepEntry(s, [t], [0]) for s, t in zip(slots, toks[i])]), slots, [i] * batch)
+            b.record()
+            torch.cuda.synchronize()
+        ms = a.elapsed_time(b) / steps
+        launches = kernels.launch_count() - n0
+        ctx = PROMPT_LEN + warmup + steps // 2            # mean cached length over the timed steps
+        for s in slots:
+            engine.release(s)
+        engine.check()
+        return ms, launches, clk.summary(), ctx
+
+    ms, launches, clocks, ctx_len = decode(args.batch, args.steps, args.warmup)
+    value = args.batch * 1e3 / ms
+    weight_bytes = model.weight_bytes() - model.embedding.weight.numel() * 2 + args.batch * cfg.hidden_size * 2
+    kv_bytes = args.batch * ctx_len * engine.cache.bytes_per_token()
+    achieved = (weight_bytes + kv_bytes) / (ms / 1e3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / pk["hbm_gbs"], 4)}
+
+    points, e2e = {}, None
+    if not args.no_points:
+        for b in (1, 64):
+            m, _, _, _ = decode(b, max(8, args.steps // 2), 3)
+            points[f"decode_b{b}"] = round(b * 1e3 / m, 1)
+        # ---- end to end through the generation loop: host ids in, host ids out
+        prompts = [rng.integers(0, V, size=PROMPT_LEN).tolist() for _ in range(args.batch)]
+        loop = GenerationLoop(engine, Sampler(SamplingParams(top_k=1)), stop_ids=[])
+        n = args.warmup + args.steps
+        loop.run(prompts, max_new_tokens=n + 1)
+        marks = loop.step_marks
+        dt = marks[-1] - marks[-1 - args.steps]
+        meta_ints = 3 * args.batch + (args.batch + 1) + 3 * args.batch + 1 + args.batch * (CONTEXT // 64)
+        e2e = {"value": round(args.batch * args.steps / dt, 1), "unit": "tokens/s",
+               "h2d_bytes_per_step": 4 * meta_ints, "d2h_bytes_per_step": 4 * args.batch}
+
+    out = {
+        "metric": "decode tok/s @ batch 8 (Qwen2-1.5B shape, bf16, 2048-token prompts, context 4096)",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights N(0,0.02), seeded uniform-random token ids",
+        "config": {"model": "Qwen2-1.5B shape (DeepSeek-R1-Distill-Qwen-1.5B config)", "layers": layers,
+                   "layers_of_config": full_layers, "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
+                   "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size,
+                   "vocab": cfg.vocab_size, "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN,
+                   "parallelism": "single GPU", "l2": "no flush: each step streams 3.1 GB of weights, larger than L2",
+                   "peaks": pk_src},
+        "clocks": clocks, "gpu_launches": launches, "prefill": prefill, "roofline": roofline, "points": points,
+    }
+    if e2e:
+        out["e2e"] = e2e
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -14,6 +14,7 @@ The loop needs of its engine only: acquire(), release(slot), step(entries) -> lo
 """
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass, field
 from typing import Callable, List, Optional, Sequence
 
@@ -35,6 +36,7 @@ class GenerationLoop:
         self.max_batch = max_batch
         self.batches_run = 0
         self.steps_run = 0
+        self.step_marks: List[float] = []     # host time after each step's tokens arrived (for measurements)
 
     # ---- admission: how many of the waiting requests start together
     def _room(self, prompt_len: int, max_new: int) -> int:
@@ -87,6 +89,7 @@ class GenerationLoop:
                 logits = eng.step(entries)
                 self.steps_run += 1
                 new = self.sampler(logits, live, [len(results[r].tokens) for r in live])
+                self.step_marks.append(time.perf_counter())
                 still, entries = [], []
                 for r, tok in zip(live, new):
                     g = results[r]

@@ -49,7 +49,18 @@ def _lib_basic():
     return _basic
 
 
-def _check(rc: int, what: str):
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernels of this package launched so far by this process (a captured launch counts once,
+    at capture; replays are counted by whoever replays)."""
+    return _launches
+
+
+def _check(rc: int, what: str, n: int = 1):
+    global _launches
+    _launches += n
     if rc != 0:
         msg = _lib_basic().llb_error_string(rc)
         raise KernelError(f"{what}: CUDA error {rc} ({msg.decode() if msg else '?'})")
@@ -223,7 +234,7 @@ def attention_decode(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_star
         p.n_splits, p.part_o, p.part_ml = n_splits, part_o.data_ptr(), part_ml.data_ptr()
         keep = (part_o, part_ml)
     f = _fn(_attn_lib(dh), "llb_attn_decode", [_AttnParams, c_int, c_int, c_void_p])
-    _check(f(p, _dt(qkv), n_seqs, _stream()), "attention_decode")
+    _check(f(p, _dt(qkv), n_seqs, _stream()), "attention_decode", 2 if n_splits > 1 else 1)
     del keep
     return out
 

@@ -61,6 +61,7 @@ class CausalLM:
         sampler = Sampler(SamplingParams(temperature=temperature, top_k=top_k, top_p=top_p),
                           self.seed if seed is None else seed)
         loop = GenerationLoop(self.engine, sampler, self.stop_token_ids if stop_ids is None else stop_ids, max_batch)
+        self.last_loop = loop
         out = [g.tokens for g in loop.run(prompts, max_new_tokens)]
         self.engine.check()
         return out
