@@ -134,7 +134,7 @@ def load_module(source: str, defines: dict | None = None) -> ctypes.CDLL:
 
 # Every module with the definitions that the tests, the benchmark and the command line use.
 DEFAULT_MODULES = [
-    ("basic.cu", {}), ("gemm_simt.cu", {}), ("sampling.cu", {}),
+    ("basic.cu", {}), ("gemm_simt.cu", {}), ("gemm_tc.cu", {}), ("sampling.cu", {}),
     *[("attention_simt.cu", {"LLB_HEAD_DIM": d}) for d in (16, 24, 32, 48, 64, 128)],
 ]
 

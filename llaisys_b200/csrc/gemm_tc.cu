@@ -1,0 +1,443 @@
+// bfloat16 matrix product on the 5th-generation tensor cores of sm_100a:
+//
+//     Y[T, N] = X[T, K] * W[N, K]^T (+ bias[N]),   float32 accumulation
+//
+// (the linear operator of xsmccc/llaisys, src/ops/linear/cpu/linear_cpu.cpp:21-40, whose model
+// calls it for the q/k/v, output, gate, up, down and head projections).
+//
+// The weight is the M operand: a CTA owns 128 consecutive weight rows (one UMMA of M = 128) and a
+// tile of BN tokens (the UMMA's N), so the same kernel serves prefill (BN up to 256) and decode
+// (BN = 16..64, a handful of tokens against the whole weight) and the weight is read once.
+// Both operands are K-major, which is how X and W lie in memory.
+//
+//   TMA (cp.async.bulk.tensor, 128-byte swizzle) -> shared-memory ring of STAGES k-blocks
+//   -> tcgen05.mma issued by one thread, accumulator in tensor memory
+//   -> tcgen05.ld by all four warps -> bias -> transposed store to Y.
+//
+// With `splits` > 1 the K range is divided over gridDim.z CTAs.  Each writes its float32 partial
+// tile to `scratch`; the CTA that arrives last at the tile's counter adds the partials in split
+// order (so the sum does not depend on arrival order), applies the bias and stores.  Counters
+// return to zero, so the same scratch serves every launch of a stream.
+//
+// With DUAL the CTA multiplies two 128-row weight blocks (rows m and m + dual_offset: the gate
+// and up rows of a fused [2I, K] matrix) into two accumulators and stores
+// up * gate / (1 + exp(-gate))  (src/ops/swiglu/cpu/swiglu_cpu.cpp:13-21) as [T, I].
+//
+// Every wait on an mbarrier is bounded; when a bound is hit the CTA records an error code in
+// *err, stops issuing, waits (bounded) for the copies it has in flight, frees its tensor
+// memory and returns.
+#include "common.cuh"
+
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+namespace {
+
+constexpr int BM = 128;        // weight rows of a tile (UMMA M)
+constexpr int BK = 64;         // k elements of a stage: one 128-byte swizzled row of bf16
+constexpr int UMMA_K = 16;     // k elements of one tcgen05.mma of kind::f16
+constexpr int THREADS = 128;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+constexpr uint64_t HINT_EVICT_FIRST = 0x12F0000000000000ull;
+constexpr uint64_t HINT_EVICT_LAST = 0x14F0000000000000ull;
+
+enum { ERR_TC_WAIT_FULL = 101, ERR_TC_WAIT_EMPTY = 102, ERR_TC_WAIT_ACC = 103 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
+// Bounded wait.  Returns false when the bound is hit or another thread already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y,
+                                            uint64_t hint) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "l"(hint) : "memory");
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, 128-byte swizzled,
+// 8-row groups 1024 bytes apart (what the TMA box {64, rows} with SWIZZLE_128B writes).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);       // start address, bits [0, 14)
+    d |= (uint64_t)1 << 16;                             // leading byte offset (unused for swizzled K-major), bits [16, 30)
+    d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset: 8 rows * 128 B, bits [32, 46)
+    d |= (uint64_t)1 << 46;                             // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                             // layout type: SWIZZLE_128B
+    return d;
+}
+
+// Instruction descriptor of kind::f16: bf16 x bf16 -> f32, both operands K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t umma_idesc(int n) {
+    return (1u << 4)                    // D format: f32
+         | (1u << 7)                    // A format: bf16
+         | (1u << 10)                   // B format: bf16
+         | ((uint32_t)(n >> 3) << 17)   // N / 8
+         | ((uint32_t)(BM >> 4) << 24); // M / 16
+}
+
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+struct GemmArgs {
+    const void* bias;      // [N] or null
+    int bias_dtype;
+    void* Y;               // [T, ldy]
+    int y_dtype;
+    int T, N, K, ldy;
+    int dual_offset;       // DUAL: rows between the gate block and the up block of W
+    int splits;
+    float* scratch;        // [tiles][splits][accs][BN][BM] float32
+    int* counters;         // [tiles], zero between launches
+    int* err;
+};
+
+template <int BN, int STAGES, bool DUAL>
+struct Smem {
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = BN * BK * 2;
+    static constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * A_BYTES + B_BYTES;
+    static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
+    static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16 + 1024;   // + slack to align the base
+};
+
+template <int BN, int STAGES, bool DUAL>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmArgs g) {
+    using S = Smem<BN, STAGES, DUAL>;
+    constexpr int ACCS = DUAL ? 2 : 1;
+    constexpr int TMEM_COLS = (ACCS * BN) <= 32 ? 32 : (ACCS * BN) <= 64 ? 64 : (ACCS * BN) <= 128 ? 128 : (ACCS * BN) <= 256 ? 256 : 512;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t bar_full = base + S::BAR_OFFSET, bar_empty = bar_full + 8 * STAGES, bar_acc = bar_empty + 8 * STAGES;
+    const uint32_t tmem_slot = bar_acc + 8;
+    uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(gen_base + S::BAR_OFFSET + (2 * STAGES + 1) * 8);
+    __shared__ int s_abort, s_last;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN, split = blockIdx.z;
+    const int kblocks = (g.K + BK - 1) / BK;
+    const int chunk = (kblocks + g.splits - 1) / g.splits;
+    const int kb0 = split * chunk, kb1 = min(kblocks, kb0 + chunk);
+
+    if (tid == 0) {
+        s_abort = 0;
+        s_last = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);
+            mbar_init(bar_empty + 8 * s, 1);
+        }
+        mbar_init(bar_acc, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot_ptr;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer: k-blocks kb0..kb1-1 into the ring
+            int issued = 0;
+            for (int kb = kb0; kb < kb1; ++kb, ++issued) {
+                int s = issued % STAGES;
+                uint32_t round = issued / STAGES;
+                if (round > 0 && !mbar_wait(bar_empty + 8 * s, (round - 1) & 1, &s_abort)) {
+                    if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC_WAIT_EMPTY); }
+                    break;
+                }
+                uint32_t dst = base + s * S::STAGE_BYTES;
+                mbar_expect_tx(bar_full + 8 * s, S::STAGE_BYTES);
+                tma_load_2d(dst, &map_w, bar_full + 8 * s, kb * BK, m0, HINT_EVICT_FIRST);
+                if (DUAL) tma_load_2d(dst + S::A_BYTES, &map_w, bar_full + 8 * s, kb * BK, m0 + g.dual_offset, HINT_EVICT_FIRST);
+                tma_load_2d(dst + ACCS * S::A_BYTES, &map_x, bar_full + 8 * s, kb * BK, n0, HINT_EVICT_LAST);
+            }
+            if (s_abort) {
+                // copies in flight must land before this CTA's shared memory is given up
+                int first = issued > STAGES ? issued - STAGES : 0;
+                for (int i = first; i < issued; ++i)
+                    for (uint32_t t = 0; t < WAIT_LIMIT && !mbar_try(bar_full + 8 * (i % STAGES), (i / STAGES) & 1); ++t) {}
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // ---- tensor-core issue
+            const uint32_t idesc = umma_idesc(BN);
+            int done = 0;
+            for (int kb = kb0; kb < kb1; ++kb, ++done) {
+                int s = done % STAGES;
+                if (!mbar_wait(bar_full + 8 * s, (done / STAGES) & 1, &s_abort)) {
+                    if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC_WAIT_FULL); }
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint32_t a = base + s * S::STAGE_BYTES, b = a + ACCS * S::A_BYTES;
+#pragma unroll
+                for (int k = 0; k < BK / UMMA_K; ++k) {
+                    uint32_t acc = (done > 0 || k > 0) ? 1u : 0u;
+                    uint64_t bd = umma_desc(b + k * UMMA_K * 2);
+                    umma(tmem, umma_desc(a + k * UMMA_K * 2), bd, idesc, acc);
+                    if (DUAL) umma(tmem + BN, umma_desc(a + S::A_BYTES + k * UMMA_K * 2), bd, idesc, acc);
+                }
+                umma_commit(bar_empty + 8 * s);      // the stage is free once these MMAs have read it
+            }
+            umma_commit(bar_acc);                    // accumulator complete (arrives even after an early stop)
+        }
+        __syncwarp();
+    }
+
+    // ---- epilogue: all four warps; warp w owns tensor-memory lanes 32w..32w+31 = weight rows m0+32w..
+    bool ok = mbar_wait(bar_acc, 0, &s_abort);
+    if (!ok && !s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC_WAIT_ACC); }
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    __syncthreads();
+    const bool aborted = s_abort != 0;
+    const int m = m0 + tid;                                   // this thread's weight row (output column)
+    const int n_valid = min(BN, g.T - n0);
+    const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+    const int n_out = DUAL ? g.dual_offset : g.N;             // DUAL: the output has I columns
+    const bool row_ok = m < (DUAL ? g.dual_offset : g.N);
+
+    auto finish = [&](float acc0, float acc1, int j) {
+        float v = acc0;
+        if (DUAL) v = acc1 * (acc0 / (1.0f + __expf(-acc0)));
+        if (g.bias) v += g.bias_dtype == LLB_F32 ? ((const float*)g.bias)[m] : to_f32(((const bf16*)g.bias)[m]);
+        size_t o = (size_t)(n0 + j) * g.ldy + m;
+        if (g.y_dtype == LLB_F32) ((float*)g.Y)[o] = v;
+        else ((bf16*)g.Y)[o] = __float2bfloat16_rn(v);
+    };
+    (void)n_out;
+
+    if (!aborted) {
+        if (g.splits == 1) {
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                float v0[16], v1[16];
+                tmem_ld16(lane_addr + c, v0);                 // warp-collective: every lane takes part
+                if (DUAL) tmem_ld16(lane_addr + BN + c, v1);
+                if (row_ok)
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        if (c + j < n_valid) finish(v0[j], DUAL ? v1[j] : 0.f, c + j);
+            }
+        } else {
+            const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+            float* mine = g.scratch + ((size_t)tile * g.splits + split) * (ACCS * BN * BM);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                float v0[16], v1[16];
+                tmem_ld16(lane_addr + c, v0);
+                if (DUAL) tmem_ld16(lane_addr + BN + c, v1);
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (c + j < n_valid) {
+                        mine[(c + j) * BM + tid] = v0[j];
+                        if (DUAL) mine[(BN + c + j) * BM + tid] = v1[j];
+                    }
+            }
+            __threadfence();
+            __syncthreads();
+            if (tid == 0) s_last = (atomicAdd(&g.counters[tile], 1) == g.splits - 1);
+            __syncthreads();
+            if (s_last) {
+                __threadfence();
+                const float* all = g.scratch + (size_t)tile * g.splits * (ACCS * BN * BM);
+                if (row_ok)
+                    for (int j = 0; j < n_valid; ++j) {
+                        float a0 = 0.f, a1 = 0.f;
+                        for (int s = 0; s < g.splits; ++s) {
+                            const float* p = all + (size_t)s * (ACCS * BN * BM);
+                            a0 += __ldcg(p + j * BM + tid);
+                            if (DUAL) a1 += __ldcg(p + (BN + j) * BM + tid);
+                        }
+                        finish(a0, a1, j);
+                    }
+                if (tid == 0) g.counters[tile] = 0;
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+struct MapKey {
+    const void* ptr; int rows, cols, ld, box_rows;
+    bool operator==(const MapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = (size_t)k.ptr;
+        for (int v : {k.rows, k.cols, k.ld, k.box_rows}) h = h * 1000003u ^ (size_t)v;
+        return h;
+    }
+};
+
+// A 2-D map over a row-major bf16 matrix [rows, cols] with row stride ld (elements); boxes of
+// {64 columns, box_rows rows}, 128-byte swizzle, zero fill outside.
+int get_map(const void* ptr, int rows, int cols, int ld, int box_rows, CUtensorMap* out) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    MapKey key{ptr, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
+template <int BN, int STAGES, bool DUAL>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& g, dim3 grid, cudaStream_t stream) {
+    auto k = gemm_tc_kernel<BN, STAGES, DUAL>;
+    constexpr int smem = Smem<BN, STAGES, DUAL>::TOTAL;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    k<<<grid, THREADS, smem, stream>>>(mw, mx, g);
+    return llb_status();
+}
+
+}  // namespace
+
+// Largest number of K splits a launch may use for this shape (every split gets at least one k-block).
+LLB_API int llb_gemm_tc_max_splits(int K) { return (K + BK - 1) / BK; }
+
+// float32 elements of scratch a launch needs (0 when splits == 1).
+LLB_API long long llb_gemm_tc_scratch_elems(int T, int N, int bn, int splits, int dual) {
+    if (splits <= 1) return 0;
+    long long tiles = (long long)((N + BM - 1) / BM) * ((T + bn - 1) / bn);
+    return tiles * splits * (dual ? 2 : 1) * bn * BM;
+}
+
+// X [T, K] bf16 with row stride ldx; W [N, K] bf16 dense ([2 * dual_offset, K] when dual_offset > 0,
+// giving Y [T, dual_offset]); bias bf16/f32 or null; Y bf16 or f32 with row stride ldy.
+// bn: tokens per tile (16, 32, 64, 128, 256).  Requirements: K and ldx multiples of 8, X and W 16-byte
+// aligned.  Returns 0, a cudaError, or cudaErrorInvalidValue for a shape it does not take.
+LLB_API int llb_gemm_tc(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int y_dtype,
+                        int T, int N, int K, int ldx, int ldy, int bn, int splits, int dual_offset,
+                        float* scratch, long long scratch_elems, int* counters, int n_counters, int* err,
+                        cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || ldx % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
+    if (y_dtype != LLB_F32 && y_dtype != LLB_BF16) return (int)cudaErrorInvalidValue;
+    const bool dual = dual_offset > 0;
+    if (dual && (N != 2 * dual_offset || bias)) return (int)cudaErrorInvalidValue;
+    const int rows_out = dual ? dual_offset : N;
+    const int kblocks = (K + BK - 1) / BK;
+    if (splits < 1) splits = 1;
+    if (splits > kblocks) splits = kblocks;
+    {   // no split may be empty
+        int chunk = (kblocks + splits - 1) / splits;
+        splits = (kblocks + chunk - 1) / chunk;
+    }
+    dim3 grid((rows_out + BM - 1) / BM, (T + bn - 1) / bn, splits);
+    if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
+    if (splits > 1) {
+        long long need = llb_gemm_tc_scratch_elems(T, rows_out, bn, splits, dual);
+        if (!scratch || !counters || need > scratch_elems || (long long)grid.x * grid.y > n_counters)
+            return (int)cudaErrorInvalidValue;
+    }
+    CUtensorMap mw, mx;
+    int rc = get_map(W, N, K, K, BM, &mw);
+    if (rc) return rc;
+    rc = get_map(X, T, K, ldx, bn, &mx);
+    if (rc) return rc;
+    GemmArgs g{bias, bias_dtype, Y, y_dtype, T, N, K, ldy, dual_offset, splits, scratch, counters, err};
+#define LLB_TC(BN_, ST_, STD_) \
+    case BN_: return dual ? launch<BN_, STD_, true>(mw, mx, g, grid, stream) : launch<BN_, ST_, false>(mw, mx, g, grid, stream)
+    switch (bn) {
+        LLB_TC(16, 6, 3);       // 108 KB / 102 KB of shared memory: two CTAs per SM
+        LLB_TC(32, 5, 3);       // 100 KB / 108 KB
+        LLB_TC(64, 4, 4);       //  96 KB / 160 KB
+        LLB_TC(128, 6, 4);      // 192 KB / 192 KB
+        LLB_TC(256, 4, 3);      // 192 KB / 192 KB
+        default: return (int)cudaErrorInvalidValue;
+    }
+#undef LLB_TC
+}

@@ -134,6 +134,10 @@ class Engine:
         if ctx is None:
             return
         code = int(ctx.err.item())
+        from ..kernels import tc_error
+        tc = tc_error(self.env.device)
+        if tc:
+            raise StepError(f"a tensor-core kernel gave up a bounded wait (code {tc}); its output is not valid")
         if code:
             what = {1: "a token id outside the embedding table", 2: "a position outside the rotary table"}
             raise StepError(f"device-side check failed in the last step: {what.get(code, code)}")

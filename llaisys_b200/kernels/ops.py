@@ -154,9 +154,74 @@ def rope_append(qkv: torch.Tensor, nh: int, nkvh: int, dh: int, *, cos=None, sin
 
 
 # ------------------------------------------------------------------ matrix products
+_TC_SCRATCH_ELEMS = 16 * 1024 * 1024        # float32 partial tiles of split-K launches (64 MB)
+_TC_COUNTERS = 1 << 16
+_tc_res = {}
+TC_ENABLED = True                            # tests switch the tensor-core path off to compare
+
+
+def _tc_resources(device):
+    """Per device: the scratch of split-K partial tiles, the tile counters (zero between
+    launches) and the error word of the tensor-core kernels.  Allocated once, so launches inside
+    a CUDA graph capture allocate nothing."""
+    r = _tc_res.get(device)
+    if r is None:
+        r = (torch.empty(_TC_SCRATCH_ELEMS, dtype=torch.float32, device=device),
+             torch.zeros(_TC_COUNTERS, dtype=torch.int32, device=device),
+             torch.zeros(1, dtype=torch.int32, device=device))
+        _tc_res[device] = r
+    return r
+
+
+def tc_error(device) -> int:
+    """Error word of the tensor-core kernels on `device` (0: none; 101-103: a bounded wait ran out)."""
+    r = _tc_res.get(torch.device(device))
+    return int(r[2].item()) if r else 0
+
+
+def _sm_count(device) -> int:
+    return torch.cuda.get_device_properties(device).multi_processor_count
+
+
+def tc_plan(T: int, rows_out: int, K: int, sms: int, dual: bool = False):
+    """(tokens per tile, K splits) of a tensor-core launch: the smallest tile that holds the
+    tokens, and enough K splits to give every SM two CTAs when the weight has few row blocks
+    (decode), each split keeping at least four k-blocks of 64."""
+    bn = 16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else 128 if T <= 128 else 256
+    tiles = -(-rows_out // 128) * -(-T // bn)
+    kblocks = -(-K // 64)
+    splits = max(1, min(kblocks // 4, (2 * sms) // tiles))
+    while splits > 1 and tiles * splits * (2 if dual else 1) * bn * 128 > _TC_SCRATCH_ELEMS:
+        splits -= 1
+    if tiles > _TC_COUNTERS:
+        splits = 1
+    return bn, splits
+
+
+def _tc_ok(x, weight, bias) -> bool:
+    return (TC_ENABLED and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def _gemm_tc(x, weight, bias, out, dual_offset=0, plan=None):
+    M, K = x.shape
+    N = weight.shape[0]
+    scratch, counters, err = _tc_resources(x.device)
+    bn, splits = plan or tc_plan(M, dual_offset or N, K, _sm_count(x.device), bool(dual_offset))
+    f = _fn(load_module("gemm_tc.cu"), "llb_gemm_tc",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(x), _ptr(weight), _ptr(bias), _dt(bias) if bias is not None else 0, _ptr(out), _dt(out),
+             M, N, K, x.stride(0), out.stride(0), bn, splits, dual_offset, _ptr(scratch), scratch.numel(),
+             _ptr(counters), counters.numel(), _ptr(err), _stream()), "linear (tensor cores)")
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
-    """x [M, K] (row stride free) times weight [N, K] transposed, plus bias [N]; float32 accumulation."""
+           out_dtype: Optional[torch.dtype] = None, plan=None) -> torch.Tensor:
+    """x [M, K] (row stride free) times weight [N, K] transposed, plus bias [N]; float32 accumulation.
+
+    bfloat16 operands with K a multiple of 8 run on the tensor cores (csrc/gemm_tc.cu); everything
+    else (float32, a 32-bit weight under 16-bit activations, odd K) on the CUDA cores (csrc/gemm_simt.cu)."""
     _need_cuda(x, weight, bias)
     M, K = x.shape
     N, K2 = weight.shape
@@ -164,12 +229,29 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         raise KernelError(f"linear: x has {K} columns but the weight has {K2}")
     assert x.stride(1) == 1 and weight.is_contiguous()
     out = torch.empty((M, N), dtype=out_dtype or x.dtype, device=x.device)
+    if M == 0:
+        return out
+    if _tc_ok(x, weight, bias):
+        _gemm_tc(x, weight, bias, out, plan=plan)
+        return out
     lib = load_module("gemm_simt.cu")
     f = _fn(lib, "llb_gemm_simt", [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int,
                                    c_int, c_int, c_int, c_int, c_int, c_void_p])
     _check(f(_ptr(x), _dt(x), _ptr(weight), _dt(weight), _ptr(bias), _dt(bias) if bias is not None else 0,
              _ptr(out), _dt(out), M, N, K, x.stride(0), out.stride(0), _stream()), "linear")
     return out
+
+
+def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, plan=None) -> torch.Tensor:
+    """up(x) * silu(gate(x)) for the fused [2I, K] matrix (gate rows first): [M, I].  On the
+    tensor cores the two products share one kernel and the [M, 2I] intermediate is never written."""
+    _need_cuda(x, gate_up)
+    I = gate_up.shape[0] // 2
+    if _tc_ok(x, gate_up, None) and x.shape[0] > 0:
+        out = torch.empty((x.shape[0], I), dtype=x.dtype, device=x.device)
+        _gemm_tc(x, gate_up, None, out, dual_offset=I, plan=plan)
+        return out
+    return swiglu(linear(x, gate_up))
 
 
 # ------------------------------------------------------------------ attention

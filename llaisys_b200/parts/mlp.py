@@ -29,5 +29,4 @@ class SwiGLUMLP(FeedForward):
         self.down = tensors["down_proj.weight"].contiguous()
 
     def forward(self, x, ctx):
-        gu = kernels.linear(x, self.gate_up)
-        return kernels.linear(kernels.swiglu(gu), self.down)
+        return kernels.linear(kernels.linear_swiglu(x, self.gate_up), self.down)

@@ -317,3 +317,76 @@ def test_sampling_statistics_and_reproducibility():
     f.restype, f.argtypes = ctypes.c_double, [ctypes.c_ulonglong] * 3
     for s, k, t in [(0, 0, 0), (7, 3, 9), (2 ** 40 + 5, 2 ** 31 - 1, 12345)]:
         assert f(s, k, t) == kernels.uniform(s, k, t)
+
+
+# ----------------------------------------------------------------------------- tensor-core matrix product
+def _tc_case(T, N, K, seed, bias=None):
+    rng = np.random.default_rng(seed)
+    x = torch.from_numpy(rng.normal(size=(T, K))).to(torch.bfloat16).to(DEV)
+    w = torch.from_numpy(rng.normal(size=(N, K)) * 0.05).to(torch.bfloat16).to(DEV)
+    b = None if bias is None else torch.from_numpy(rng.normal(size=N)).to(bias).to(DEV)
+    return x, w, b
+
+
+def _tc_check(got, want, K):
+    got = got.double().cpu().numpy()
+    bound = 5e-4 * math.sqrt(K / 64) + 2e-3 * np.abs(want)
+    err = np.abs(got - want)
+    assert np.isfinite(got).all(), "non-finite output"
+    worst = np.unravel_index(np.argmax(err - bound), err.shape)
+    assert (err <= bound).all(), f"worst at {worst}: got {got[worst]}, want {want[worst]}"
+
+
+@pytest.mark.parametrize("T,N,K", [(1, 128, 64), (8, 2048, 1536), (5, 200, 72), (16, 1536, 8960), (33, 130, 520),
+                                   (64, 256, 128), (100, 384, 1000), (300, 500, 776), (1000, 1536, 256), (17, 151936, 64)])
+def test_linear_tensor_cores(T, N, K):
+    from llaisys_b200 import kernels
+    x, w, b = _tc_case(T, N, K, T + N + K, bias=torch.bfloat16)
+    want = plain.linear(x.double().cpu().numpy(), w.double().cpu().numpy(), b.double().cpu().numpy())
+    _tc_check(kernels.linear(x, w, b, out_dtype=torch.float32), want, K)
+    got = kernels.linear(x, w, b.float())                          # bfloat16 out, float32 bias
+    _close(got, want, torch.bfloat16, atol=5e-3)
+    assert kernels.tc_error(DEV) == 0
+    # the CUDA-core path gives the same numbers up to summation order
+    kernels.ops.TC_ENABLED = False
+    try:
+        ref = kernels.linear(x, w, b, out_dtype=torch.float32)
+    finally:
+        kernels.ops.TC_ENABLED = True
+    _tc_check(ref, want, K)
+
+
+@pytest.mark.parametrize("bn", [16, 32, 64, 128, 256])
+@pytest.mark.parametrize("splits", [1, 2, 5])
+def test_linear_tensor_cores_every_tile_and_split(bn, splits):
+    from llaisys_b200 import kernels
+    T, N, K = bn + 3, 300, 712                  # two token tiles, three row tiles, twelve k-blocks (the last one partial)
+    x, w, _ = _tc_case(T, N, K, bn * splits)
+    want = plain.linear(x.double().cpu().numpy(), w.double().cpu().numpy())
+    for _ in range(2):                          # twice: the tile counters must be back at zero
+        _tc_check(kernels.linear(x, w, out_dtype=torch.float32, plan=(bn, splits)), want, K)
+    wide = torch.zeros((T, K + 16), dtype=torch.bfloat16, device=DEV)
+    wide[:, 8:8 + K] = x
+    _tc_check(kernels.linear(wide[:, 8:8 + K], w, out_dtype=torch.float32, plan=(bn, splits)), want, K)
+    assert kernels.tc_error(DEV) == 0
+
+
+@pytest.mark.parametrize("T,I,K,plan", [(8, 8960, 1536, None), (3, 200, 72, None), (70, 136, 96, None), (300, 264, 200, None),
+                                        (20, 300, 712, (32, 3)), (20, 300, 712, (256, 2)), (130, 300, 712, (128, 4))])
+def test_linear_swiglu_tensor_cores(T, I, K, plan):
+    from llaisys_b200 import kernels
+    x, w, _ = _tc_case(T, 2 * I, K, T + I)
+    w = (w.float() * 4).to(torch.bfloat16)
+    gu = plain.linear(x.double().cpu().numpy(), w.double().cpu().numpy())
+    want = plain.swiglu(gu[:, :I], gu[:, I:])
+    got = kernels.linear_swiglu(x, w, plan=plan)
+    assert got.shape == (T, I)
+    _close(got, want, torch.bfloat16, atol=5e-3)
+    assert kernels.tc_error(DEV) == 0
+
+
+def test_linear_falls_back_where_tensor_cores_do_not_apply():
+    from llaisys_b200 import kernels
+    x, w, _ = _tc_case(5, 40, 36, 1)             # K = 36 is no multiple of 8
+    want = plain.linear(x.double().cpu().numpy(), w.double().cpu().numpy())
+    _tc_check(kernels.linear(x, w, out_dtype=torch.float32), want, 36)
