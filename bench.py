@@ -106,6 +106,41 @@ def linear_params(cfg, layers):
     return per_layer * layers, cfg["vocab_size"] * H
 
 
+def profile_run(args, model, cfg, rng) -> int:
+    """Two uncaptured steps inside a cudaProfilerStart/Stop range, after a warm-up outside it."""
+    import torch
+
+    from llaisys_b200.cache import CacheConfig
+    from llaisys_b200.engine import Engine, StepEntry
+    V = cfg.vocab_size
+    engine = Engine(model, CacheConfig(max_tokens=max(args.batch, 1) * CONTEXT, max_seqs=max(args.batch, 1)), use_graphs=False)
+    if args.profile == "prefill":
+        def once():
+            s = engine.acquire()
+            engine.step([StepEntry(s, rng.integers(0, V, size=PREFILL_TOKENS).tolist(), [PREFILL_TOKENS - 1])])
+            engine.release(s)
+    else:
+        slots = [engine.acquire() for _ in range(args.batch)]
+        for s in slots:
+            engine.cache.book.reserve(s, PROMPT_LEN)
+            engine.cache.book.commit(s, PROMPT_LEN)
+        for pool in engine.cache.k_pools + engine.cache.v_pools:
+            pool.normal_(0, 1)
+
+        def once():
+            engine.step([StepEntry(s, [int(rng.integers(0, V))], [0]) for s in slots])
+    for _ in range(2):
+        once()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.start()
+    for _ in range(2):
+        once()
+    torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
+    engine.check()
+    return 0
+
+
 def reference_arm():
     print(json.dumps({"impl": "reference", "unavailable":
                       "xsmccc/llaisys cannot be installed offline (pip: no setup.py or pyproject.toml at its root; its "
@@ -123,6 +158,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / batch 64 points and the end-to-end run")
+    ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
+                    help="for a profiler: warm up, then run two uncaptured steps of this kind between "
+                         "cudaProfilerStart and cudaProfilerStop, print nothing else")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -159,6 +197,9 @@ def main() -> int:
 
     def events():
         return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+    if args.profile:
+        return profile_run(args, model, cfg, rng)
 
     # ---- prefill: one step over 2,048 tokens
     engine = Engine(model, CacheConfig(max_tokens=max(64, args.batch) * CONTEXT, max_seqs=max(64, args.batch)))

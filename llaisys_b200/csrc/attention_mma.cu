@@ -1,0 +1,521 @@
+// bfloat16 attention over the paged cache on the tensor cores (mma.sync m16n8k16, float32
+// accumulation), for prefill and for decode.  Compiled per head size:
+// -DLLB_HEAD_DIM=<multiple of 16, at most 128>.  Same formula and masks as attention_simt.cu
+// (xsmccc/llaisys src/ops/self_attention/cpu/self_attention_cpu.cpp:28-112, plus the window).
+//
+// Keys and values are walked in tiles of one cache page (64 keys).  A tile's rows are fetched
+// with one cp.async.bulk per row into a ring of shared-memory stages whose rows are padded by 16
+// bytes (so that ldmatrix reads them without bank conflicts); an mbarrier per stage counts the
+// bytes.  A row comes from the cache page of its position or, for positions of the step itself
+// in prefill, from the packed projection output.  Scores, the running maximum, the exponentials
+// and the normaliser are float32; the probabilities are rounded to bfloat16 only as the
+// tensor-core operand of P*V.
+//
+//  * decode: a block owns up to 16 query heads that share one kv head, for one sequence and one
+//    slice of its key range; its four warps take 16 keys each of every tile and are merged at the
+//    end; slices are merged by llb_attn_mma_combine.
+//  * prefill: a block owns 64 consecutive new tokens of one query head; each warp 16 of them.
+//
+// Waits on mbarriers are bounded; when one runs out the block sets *err and returns.
+#include "common.cuh"
+
+#ifndef LLB_HEAD_DIM
+#error "compile with -DLLB_HEAD_DIM=<head size>"
+#endif
+
+namespace {
+
+constexpr int DH = LLB_HEAD_DIM;
+static_assert(DH % 16 == 0 && DH <= 128, "head size must be a multiple of 16, at most 128");
+constexpr int TILE = LLB_PAGE;                 // keys of a tile
+constexpr int ROW_BYTES = DH * 2;
+constexpr int ROW_STRIDE = ROW_BYTES + 16;     // padded shared-memory row
+constexpr int TILE_BYTES = TILE * ROW_STRIDE;
+constexpr int STAGE_BYTES = 2 * TILE_BYTES;    // keys, then values
+constexpr int STAGES = 3;
+constexpr int THREADS = 128;
+constexpr int KSTEPS = DH / 16;
+constexpr int DTILES = DH / 8;
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+enum { ERR_ATTN_WAIT = 111 };
+
+struct MmaAttnParams {
+    const bf16* q;          // packed projections [T, row_stride]; query head h at column h * DH
+    const bf16* k_new;      // the same buffer at its first key column
+    const bf16* v_new;      // the same buffer at its first value column
+    int row_stride;
+    bf16* out;              // [T, nh * DH]
+    const bf16* kpool;      // [pages, nkvh, TILE, DH]
+    const bf16* vpool;
+    const int* page_table;  // [B, table_stride]
+    int table_stride;
+    int ring;
+    const int* seq_start;
+    const int* seq_len_before;
+    int nh, nkvh, window;
+    float scale;
+    int all_from_cache;     // prefill: read the step's own keys from the cache too
+    int n_splits;           // decode
+    float* part_o;          // decode: [B, nh, n_splits, DH]
+    float* part_ml;         // decode: [B, nh, n_splits, 2]
+    int* err;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
+        if (mbar_try(bar, parity)) return true;
+    return false;
+}
+__device__ __forceinline__ void bulk_row(uint32_t dst, const void* src, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"((uint32_t)ROW_BYTES), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// What a block needs to fetch tiles: where each key position of the sequence lives.
+struct Source {
+    const bf16 *kpool, *vpool, *k_new, *v_new;
+    const int* table;
+    int ring, nkvh, kvh, row_stride, tok0, len_before;
+    bool use_new;           // positions >= len_before come from k_new / v_new
+};
+
+// Issues the row copies of tile `tile` (key positions tile*TILE ...) restricted to [key_lo, key_hi]
+// into stage memory at `stage`; executed by all lanes of one warp.
+__device__ __forceinline__ void issue_tile(const Source& s, int tile, int key_lo, int key_hi, uint32_t stage, uint32_t bar,
+                                           int lane) {
+    int p0 = tile * TILE;
+    int j_lo = max(0, key_lo - p0), j_hi = min(TILE, key_hi - p0 + 1);       // valid rows [j_lo, j_hi)
+    if (lane == 0) mbar_expect_tx(bar, (uint32_t)(max(0, j_hi - j_lo) * 2 * ROW_BYTES));
+    __syncwarp();
+    for (int j = j_lo + lane; j < j_hi; j += 32) {
+        int pos = p0 + j;
+        const bf16 *ks, *vs;
+        if (s.use_new && pos >= s.len_before) {
+            size_t off = (size_t)(s.tok0 + pos - s.len_before) * s.row_stride + (size_t)s.kvh * DH;
+            ks = s.k_new + off;
+            vs = s.v_new + off;
+        } else {
+            size_t off = paged_row(s.table, s.ring, pos, s.kvh, s.nkvh, DH);
+            ks = s.kpool + off;
+            vs = s.vpool + off;
+        }
+        bulk_row(stage + j * ROW_STRIDE, ks, bar);
+        bulk_row(stage + TILE_BYTES + j * ROW_STRIDE, vs, bar);
+    }
+}
+
+// Zeroes the value rows of a tile outside [key_lo, key_hi] (they were not fetched; a zero
+// probability must meet a finite value).  All threads of the block; block-uniform condition.
+__device__ __forceinline__ void zero_unfetched(uint8_t* stage_ptr, int tile, int key_lo, int key_hi, int tid) {
+    int p0 = tile * TILE;
+    int j_lo = max(0, key_lo - p0), j_hi = min(TILE, key_hi - p0 + 1);
+    if (j_lo == 0 && j_hi == TILE) return;
+    constexpr int CH = ROW_BYTES / 16;
+    for (int i = tid; i < TILE * CH; i += THREADS) {
+        int j = i / CH, c = i - j * CH;
+        if (j < j_lo || j >= j_hi)
+            *reinterpret_cast<uint4*>(stage_ptr + TILE_BYTES + j * ROW_STRIDE + c * 16) = make_uint4(0, 0, 0, 0);
+    }
+    __syncthreads();
+}
+
+// Query rows as A fragments: q_of(row) gives the pointer to that row's DH elements or nullptr.
+template <typename F>
+__device__ __forceinline__ void load_q(uint32_t (&qf)[KSTEPS][4], F q_of, int lane) {
+    const bf16* r0 = q_of(lane >> 2);
+    const bf16* r1 = q_of((lane >> 2) + 8);
+    int c = (lane & 3) * 2;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+        qf[kk][0] = r0 ? *reinterpret_cast<const uint32_t*>(r0 + kk * 16 + c) : 0u;
+        qf[kk][1] = r1 ? *reinterpret_cast<const uint32_t*>(r1 + kk * 16 + c) : 0u;
+        qf[kk][2] = r0 ? *reinterpret_cast<const uint32_t*>(r0 + kk * 16 + 8 + c) : 0u;
+        qf[kk][3] = r1 ? *reinterpret_cast<const uint32_t*>(r1 + kk * 16 + 8 + c) : 0u;
+    }
+}
+
+// One warp: scores of its 16 rows against NT*8 keys starting at row `key0` of the tile in `stage`,
+// masking, online softmax update, and O += P V.  lo0/hi0 and lo1/hi1: visible key positions of
+// the thread's two rows (lane/4 and lane/4 + 8).
+template <int NT>
+__device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], float (&o)[DTILES][4], float (&m)[2],
+                                          float (&l)[2], uint32_t stage, int key0, int pos0, int lo0, int hi0, int lo1,
+                                          int hi1, float scale_log2, int lane) {
+    float s[NT][4];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+    const int mid = lane >> 3, mr = lane & 7;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+#pragma unroll
+        for (int n2 = 0; n2 < NT / 2; ++n2) {
+            uint32_t b[4];
+            uint32_t addr = stage + (key0 + n2 * 16 + (mid >> 1) * 8 + mr) * ROW_STRIDE + (kk * 16 + (mid & 1) * 8) * 2;
+            ldsm_x4(b, addr);
+            mma16816(s[2 * n2], qf[kk], b[0], b[1]);
+            mma16816(s[2 * n2 + 1], qf[kk], b[2], b[3]);
+        }
+    }
+    // mask and row maxima
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+        int kp = pos0 + key0 + n * 8 + (lane & 3) * 2;
+        s[n][0] = (kp >= lo0 && kp <= hi0) ? s[n][0] * scale_log2 : -INFINITY;
+        s[n][1] = (kp + 1 >= lo0 && kp + 1 <= hi0) ? s[n][1] * scale_log2 : -INFINITY;
+        s[n][2] = (kp >= lo1 && kp <= hi1) ? s[n][2] * scale_log2 : -INFINITY;
+        s[n][3] = (kp + 1 >= lo1 && kp + 1 <= hi1) ? s[n][3] * scale_log2 : -INFINITY;
+        mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
+        mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    float mn0 = fmaxf(m[0], mx0), mn1 = fmaxf(m[1], mx1);
+    // a row that has seen no visible key yet keeps m = -inf; use 0 as the exponent base then so that
+    // exp2(-inf - 0) = 0 and no inf - inf arises
+    float b0 = mn0 == -INFINITY ? 0.f : mn0, b1 = mn1 == -INFINITY ? 0.f : mn1;
+    float a0 = exp2f(m[0] - b0), a1 = exp2f(m[1] - b1);
+    m[0] = mn0;
+    m[1] = mn1;
+    float sum0 = 0.f, sum1 = 0.f;
+    uint32_t pf[NT][2];
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+        float p0 = exp2f(s[n][0] - b0), p1 = exp2f(s[n][1] - b0), p2 = exp2f(s[n][2] - b1), p3 = exp2f(s[n][3] - b1);
+        sum0 += p0 + p1;
+        sum1 += p2 + p3;
+        pf[n][0] = pack_bf16(p0, p1);
+        pf[n][1] = pack_bf16(p2, p3);
+    }
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+    l[0] = l[0] * a0 + sum0;
+    l[1] = l[1] * a1 + sum1;
+#pragma unroll
+    for (int d = 0; d < DTILES; ++d) {
+        o[d][0] *= a0;
+        o[d][1] *= a0;
+        o[d][2] *= a1;
+        o[d][3] *= a1;
+    }
+    // O += P V: 16 keys per k-step
+    const uint32_t vbase = stage + TILE_BYTES;
+#pragma unroll
+    for (int n2 = 0; n2 < NT / 2; ++n2) {
+        uint32_t a[4] = {pf[2 * n2][0], pf[2 * n2][1], pf[2 * n2 + 1][0], pf[2 * n2 + 1][1]};
+#pragma unroll
+        for (int d2 = 0; d2 < DTILES / 2; ++d2) {
+            uint32_t b[4];
+            uint32_t addr = vbase + (key0 + n2 * 16 + (mid & 1) * 8 + mr) * ROW_STRIDE + (d2 * 16 + (mid >> 1) * 8) * 2;
+            ldsm_x4_trans(b, addr);
+            mma16816(o[2 * d2], a, b[0], b[1]);
+            mma16816(o[2 * d2 + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// A wait ran out: record it, and give copies that may still be in flight a bounded time to land
+// before the block's shared memory is released.
+__device__ __forceinline__ void give_up(int* err, int tid) {
+    if (tid == 0) atomicExch(err, ERR_ATTN_WAIT);
+    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    __syncthreads();
+}
+
+struct Ring {
+    uint32_t base, bars;
+    uint8_t* ptr;
+    __device__ uint32_t stage(int i) const { return base + (i % STAGES) * STAGE_BYTES; }
+    __device__ uint8_t* stage_ptr(int i) const { return ptr + (i % STAGES) * STAGE_BYTES; }
+    __device__ uint32_t bar(int i) const { return bars + 8 * (i % STAGES); }
+};
+
+__device__ __forceinline__ Ring make_ring(uint8_t* smem_raw, int tid) {
+    Ring r;
+    uint32_t raw = smem_u32(smem_raw);
+    r.base = (raw + 127u) & ~127u;
+    r.ptr = smem_raw + (r.base - raw);
+    r.bars = r.base + STAGES * STAGE_BYTES;
+    if (tid == 0) {
+        for (int s = 0; s < STAGES; ++s) mbar_init(r.bars + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    return r;
+}
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGES * 8 + 128;
+
+// ------------------------------------------------------------------ decode
+__global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    Ring ring = make_ring(smem_raw, tid);
+
+    const int b = blockIdx.z;
+    const int G = p.nh / p.nkvh;
+    const int chunks = (G + 15) / 16;
+    const int kvh = blockIdx.y / chunks, chunk = blockIdx.y - kvh * chunks;
+    const int head0 = kvh * G + chunk * 16, n_heads = min(16, G - chunk * 16);
+    const int tok = p.seq_start[b];
+    const int pos = p.seq_len_before[b];                 // the new token's position; it is already cached
+    const int key_lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    int tile_lo = key_lo / TILE, tile_hi = pos / TILE + 1;
+    {
+        int n = tile_hi - tile_lo, per = (n + p.n_splits - 1) / p.n_splits;
+        tile_lo += blockIdx.x * per;
+        tile_hi = min(tile_hi, tile_lo + per);
+    }
+    const int n_tiles = max(0, tile_hi - tile_lo);
+
+    Source src{p.kpool, p.vpool, nullptr, nullptr, p.page_table + (size_t)b * p.table_stride,
+               p.ring, p.nkvh, kvh, 0, 0, 0, false};
+    if (warp == 0)
+        for (int i = 0; i < min(STAGES, n_tiles); ++i) issue_tile(src, tile_lo + i, key_lo, pos, ring.stage(i), ring.bar(i), lane);
+
+    uint32_t qf[KSTEPS][4];
+    load_q(qf, [&](int r) -> const bf16* {
+        return r < n_heads ? p.q + (size_t)tok * p.row_stride + (size_t)(head0 + r) * DH : nullptr; }, lane);
+    float o[DTILES][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+#pragma unroll
+    for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+    const float scale_log2 = p.scale * 1.4426950408889634f;
+
+    bool failed = false;
+    for (int i = 0; i < n_tiles; ++i) {
+        bool ok = mbar_wait(ring.bar(i), (i / STAGES) & 1);
+        if (__syncthreads_or(!ok)) { failed = true; break; }       // the whole block leaves together
+        zero_unfetched(ring.stage_ptr(i), tile_lo + i, key_lo, pos, tid);
+        tile_step<2>(qf, o, m, l, ring.stage(i), warp * 16, (tile_lo + i) * TILE, key_lo, pos, key_lo, pos, scale_log2, lane);
+        __syncthreads();                                   // the stage is free
+        if (warp == 0 && i + STAGES < n_tiles) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            issue_tile(src, tile_lo + i + STAGES, key_lo, pos, ring.stage(i + STAGES), ring.bar(i + STAGES), lane);
+        }
+    }
+    if (failed) {
+        give_up(p.err, tid);
+        return;
+    }
+
+    // ---- merge the four warps (each saw a quarter of the keys) through shared memory
+    float* sm_ml = reinterpret_cast<float*>(ring.ptr);               // [4][16][2]
+    float* sm_o = sm_ml + 4 * 16 * 2;                                 // [4][16][DH]
+    {
+        int r0 = lane >> 2, c = (lane & 3) * 2;
+        if ((lane & 3) == 0) {
+            sm_ml[(warp * 16 + r0) * 2] = m[0];
+            sm_ml[(warp * 16 + r0) * 2 + 1] = l[0];
+            sm_ml[(warp * 16 + r0 + 8) * 2] = m[1];
+            sm_ml[(warp * 16 + r0 + 8) * 2 + 1] = l[1];
+        }
+#pragma unroll
+        for (int d = 0; d < DTILES; ++d) {
+            float* w0 = sm_o + (size_t)(warp * 16 + r0) * DH + d * 8 + c;
+            float* w1 = sm_o + (size_t)(warp * 16 + r0 + 8) * DH + d * 8 + c;
+            w0[0] = o[d][0]; w0[1] = o[d][1];
+            w1[0] = o[d][2]; w1[1] = o[d][3];
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < n_heads * DH; i += THREADS) {
+        int r = i / DH, d = i - r * DH;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, sm_ml[(w * 16 + r) * 2]);
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            float mw = sm_ml[(w * 16 + r) * 2];
+            if (mw != -INFINITY) {
+                float f = exp2f(mw - M);
+                L += sm_ml[(w * 16 + r) * 2 + 1] * f;
+                acc += sm_o[(size_t)(w * 16 + r) * DH + d] * f;
+            }
+        }
+        int head = head0 + r;
+        if (p.n_splits == 1) {
+            p.out[(size_t)tok * p.nh * DH + (size_t)head * DH + d] = __float2bfloat16_rn(acc / L);
+        } else {
+            size_t slot = ((size_t)b * p.nh + head) * p.n_splits + blockIdx.x;
+            p.part_o[slot * DH + d] = acc;
+            if (d == 0) {
+                p.part_ml[slot * 2] = M;              // base-2 logarithmic scale
+                p.part_ml[slot * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+__global__ void attn_mma_combine_kernel(bf16* __restrict__ out, const float* __restrict__ part_o,
+                                        const float* __restrict__ part_ml, const int* __restrict__ seq_start, int nh,
+                                        int n_splits) {
+    int head = blockIdx.x, b = blockIdx.y;
+    size_t base = ((size_t)b * nh + head) * n_splits;
+    float M = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+    float L = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        float ms = part_ml[(base + s) * 2];
+        if (ms != -INFINITY) L += part_ml[(base + s) * 2 + 1] * exp2f(ms - M);
+    }
+    int tok = seq_start[b];
+    for (int d = threadIdx.x; d < DH; d += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            float ms = part_ml[(base + s) * 2];
+            if (ms != -INFINITY) acc += part_o[(base + s) * DH + d] * exp2f(ms - M);
+        }
+        out[(size_t)tok * nh * DH + (size_t)head * DH + d] = __float2bfloat16_rn(acc / L);
+    }
+}
+
+// ------------------------------------------------------------------ prefill
+__global__ void __launch_bounds__(THREADS) attn_mma_prefill_kernel(MmaAttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int b = blockIdx.z, head = blockIdx.y;
+    const int tok0 = p.seq_start[b], n_new = p.seq_start[b + 1] - tok0, len_before = p.seq_len_before[b];
+    const int t0 = blockIdx.x * 64;
+    if (t0 >= n_new) return;
+    Ring ring = make_ring(smem_raw, tid);
+    const int kvh = head / (p.nh / p.nkvh);
+    const int n_rows = min(64, n_new - t0);
+    const int first_pos = len_before + t0, last_pos = first_pos + n_rows - 1;
+    const int key_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+    const int tile_lo = key_lo / TILE, n_tiles = last_pos / TILE + 1 - tile_lo;
+
+    Source src{p.kpool, p.vpool, p.k_new, p.v_new, p.page_table + (size_t)b * p.table_stride,
+               p.ring, p.nkvh, kvh, p.row_stride, tok0, len_before, !p.all_from_cache};
+    if (warp == 0)
+        for (int i = 0; i < min(STAGES, n_tiles); ++i)
+            issue_tile(src, tile_lo + i, key_lo, last_pos, ring.stage(i), ring.bar(i), lane);
+
+    // this thread's two query rows
+    const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
+    uint32_t qf[KSTEPS][4];
+    load_q(qf, [&](int r) -> const bf16* {
+        int row = warp * 16 + r;
+        return row < n_rows ? p.q + (size_t)(tok0 + t0 + row) * p.row_stride + (size_t)head * DH : nullptr; }, lane);
+    const int hi0 = first_pos + r0, hi1 = first_pos + r1;          // causal: keys up to the row's own position
+    const int lo0 = p.window > 0 ? max(0, hi0 - p.window + 1) : 0, lo1 = p.window > 0 ? max(0, hi1 - p.window + 1) : 0;
+    const int warp_hi = first_pos + warp * 16 + 15;                  // last position any row of this warp sees
+    const int warp_lo = p.window > 0 ? max(0, first_pos + warp * 16 - p.window + 1) : 0;
+    float o[DTILES][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+#pragma unroll
+    for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
+    const float scale_log2 = p.scale * 1.4426950408889634f;
+
+    bool failed = false;
+    for (int i = 0; i < n_tiles; ++i) {
+        bool ok = mbar_wait(ring.bar(i), (i / STAGES) & 1);
+        if (__syncthreads_or(!ok)) { failed = true; break; }
+        zero_unfetched(ring.stage_ptr(i), tile_lo + i, key_lo, last_pos, tid);
+        int p0 = (tile_lo + i) * TILE;
+        if (p0 <= warp_hi && p0 + TILE - 1 >= warp_lo)               // the tile holds a key some row of the warp sees
+            tile_step<8>(qf, o, m, l, ring.stage(i), 0, p0, lo0, hi0, lo1, hi1, scale_log2, lane);
+        __syncthreads();
+        if (warp == 0 && i + STAGES < n_tiles) {
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            issue_tile(src, tile_lo + i + STAGES, key_lo, last_pos, ring.stage(i + STAGES), ring.bar(i + STAGES), lane);
+        }
+    }
+    if (failed) {
+        give_up(p.err, tid);
+        return;
+    }
+    const int c = (lane & 3) * 2;
+    if (r0 < n_rows) {
+        float inv = 1.0f / l[0];
+        bf16* dst = p.out + (size_t)(tok0 + t0 + r0) * p.nh * DH + (size_t)head * DH + c;
+#pragma unroll
+        for (int d = 0; d < DTILES; ++d) *reinterpret_cast<uint32_t*>(dst + d * 8) = pack_bf16(o[d][0] * inv, o[d][1] * inv);
+    }
+    if (r1 < n_rows) {
+        float inv = 1.0f / l[1];
+        bf16* dst = p.out + (size_t)(tok0 + t0 + r1) * p.nh * DH + (size_t)head * DH + c;
+#pragma unroll
+        for (int d = 0; d < DTILES; ++d) *reinterpret_cast<uint32_t*>(dst + d * 8) = pack_bf16(o[d][2] * inv, o[d][3] * inv);
+    }
+}
+
+template <int WHICH, typename K>       // WHICH tells the kernels apart: they share one function type
+int configure(K kernel) {
+    static bool done = false;
+    if (!done && SMEM_BYTES > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+    }
+    done = true;
+    return 0;
+}
+
+bool aligned_ok(const MmaAttnParams& p) {
+    return !(((uintptr_t)p.q | (uintptr_t)p.kpool | (uintptr_t)p.vpool | (uintptr_t)p.out) & 15) && p.row_stride % 8 == 0 &&
+           p.nkvh > 0 && p.nh % p.nkvh == 0;
+}
+
+}  // namespace
+
+LLB_API int llb_attn_mma_head_dim() { return DH; }
+
+LLB_API int llb_attn_mma_prefill(MmaAttnParams p, int B, int max_new, cudaStream_t stream) {
+    if (B == 0 || max_new == 0) return 0;
+    if (!aligned_ok(p)) return (int)cudaErrorInvalidValue;
+    dim3 grid((max_new + 63) / 64, p.nh, B);
+    if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
+    int rc = configure<0>(attn_mma_prefill_kernel);
+    if (rc) return rc;
+    attn_mma_prefill_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(p);
+    return llb_status();
+}
+
+LLB_API int llb_attn_mma_decode(MmaAttnParams p, int B, cudaStream_t stream) {
+    if (B == 0) return 0;
+    if (!aligned_ok(p) || p.n_splits < 1) return (int)cudaErrorInvalidValue;
+    int G = p.nh / p.nkvh;
+    dim3 grid(p.n_splits, p.nkvh * ((G + 15) / 16), B);
+    if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
+    int rc = configure<1>(attn_mma_decode_kernel);
+    if (rc) return rc;
+    attn_mma_decode_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(p);
+    rc = llb_status();
+    if (rc == 0 && p.n_splits > 1) {
+        attn_mma_combine_kernel<<<dim3(p.nh, B), 128, 0, stream>>>(p.out, p.part_o, p.part_ml, p.seq_start, p.nh, p.n_splits);
+        rc = llb_status();
+    }
+    return rc;
+}

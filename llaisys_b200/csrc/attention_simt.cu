@@ -245,10 +245,12 @@ template <typename T, bool DECODE>
 static int launch_attn(const AttnParams& p, dim3 grid, cudaStream_t stream) {
     auto k = attn_kernel<T, DECODE>;
     size_t smem = attn_smem_bytes();
-    if (smem > 48 * 1024) {
+    static bool configured = false;          // once per instantiation: not repeated inside a graph capture
+    if (!configured && smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
+    configured = true;
     k<<<grid, WARPS * 32, smem, stream>>>(p);
     return llb_status();
 }

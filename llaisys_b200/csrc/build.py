@@ -23,7 +23,7 @@ from pathlib import Path
 SRC_DIR = Path(__file__).resolve().parent
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC",
-              "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr"]
+              "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr", "--extended-lambda"]
 
 _lock = threading.RLock()
 _loaded: dict[str, ctypes.CDLL] = {}
@@ -136,6 +136,7 @@ def load_module(source: str, defines: dict | None = None) -> ctypes.CDLL:
 DEFAULT_MODULES = [
     ("basic.cu", {}), ("gemm_simt.cu", {}), ("gemm_tc.cu", {}), ("sampling.cu", {}),
     *[("attention_simt.cu", {"LLB_HEAD_DIM": d}) for d in (16, 24, 32, 48, 64, 128)],
+    *[("attention_mma.cu", {"LLB_HEAD_DIM": d}) for d in (16, 32, 48, 64, 128)],
 ]
 
 

@@ -41,15 +41,32 @@ class Engine:
     step() runs exactly the tokens it is given, as one packed batch, against what earlier
     steps left in the cache, and returns the logits at the wanted places.  Sequences are
     identified by slots from acquire(); release() gives a slot and its pages back.
+
+    A step in which every sequence brings one token (decode) has the same launches whenever its
+    shape (sequences, wanted rows, page-table widths) is the same, so its launches are captured
+    in a CUDA graph the first time the shape is met and replayed afterwards; the step's
+    description is copied into the same device buffer each time.  This only removes launch
+    overhead: the kernels, the cache and the results are those of the uncaptured step.
+    Models with parts that are not `capturable` always run uncaptured.
     """
 
-    def __init__(self, model: DecoderModel, cache_config: CacheConfig):
+    MAX_GRAPHS = 64
+    STAGES = 8
+
+    def __init__(self, model: DecoderModel, cache_config: CacheConfig, use_graphs: bool = True):
         self.model, self.spec, self.env = model, model.spec, model.env
         _require_cuda(self.env.device)
         self.cache = PagedCache(model.kv_needs(), model.cache_of(), model.state_sizes(), cache_config,
                                 self.env.dtype, self.env.device)
         self.sm_count = torch.cuda.get_device_properties(self.env.device).multi_processor_count
+        self.err = torch.zeros(1, dtype=torch.int32, device=self.env.device)
+        self.use_graphs = use_graphs and model.capturable()
+        model.prepare(min(self.spec.max_positions, self.cache.n_pages * self.page))
+        self._graphs = {}                      # shape -> [context, graph or None, logits]
+        self._stages = [[None, None] for _ in range(self.STAGES)]
+        self._stage_i = 0
         self.steps_run = 0
+        self.graph_replays = 0
 
     # ---- limits the generation loop plans with
     @property
@@ -80,9 +97,23 @@ class Engine:
         return self.cache.length(slot)
 
     # ---- the step
+    def _staging(self, n: int):
+        """A pinned host buffer of the ring, free again (its last copy has run)."""
+        i = self._stage_i % self.STAGES
+        self._stage_i += 1
+        buf, ev = self._stages[i]
+        if ev is not None:
+            ev.synchronize()
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(max(n, 1024), dtype=torch.int32).pin_memory()
+        if ev is None:
+            ev = torch.cuda.Event()
+        self._stages[i] = [buf, ev]
+        return buf, ev
+
     def step(self, entries: List[StepEntry]) -> Optional[torch.Tensor]:
         """Returns float32 logits [sum(len(e.want)), vocab] in the order of the entries and of
-        their `want` lists (None if nothing is wanted)."""
+        their `want` lists (None if nothing is wanted).  The tensor is valid until the next step."""
         if not entries:
             return None
         slots = [e.slot for e in entries]
@@ -120,34 +151,68 @@ class Engine:
                     book.seqs[s].pages[g] = old
             raise
         with torch.cuda.device(self.env.device):
-            ctx = StepContext(self.cache, slots, n_new, tokens, out_rows, self.env.device, self.sm_count)
-            logits = self.model.forward(ctx)
+            graphed = self.use_graphs and max(n_new) == 1
+            shape = StepContext.shape_of(self.cache, slots, n_new, out_rows, bucket=graphed)
+            if graphed:
+                logits = self._graphed_step(shape, slots, n_new, tokens, out_rows)
+            else:
+                ctx = StepContext(self.cache, self.env.device, *shape, self.err, self.sm_count)
+                buf, ev = self._staging(ctx.meta.numel())
+                ctx.load(slots, n_new, tokens, out_rows, buf)
+                ev.record()
+                logits = self.model.forward(ctx)
             for s, n in zip(slots, n_new):
                 book.commit(s, n)
             self.steps_run += 1
-            self._last_ctx = ctx
         return logits
 
+    def _graphed_step(self, shape, slots, n_new, tokens, out_rows):
+        entry = self._graphs.get(shape)
+        if entry is None:
+            if len(self._graphs) >= self.MAX_GRAPHS:
+                self._graphs.pop(next(iter(self._graphs)))
+            entry = [StepContext(self.cache, self.env.device, *shape, self.err, self.sm_count), None, None]
+            self._graphs[shape] = entry
+        ctx = entry[0]
+        buf, ev = self._staging(ctx.meta.numel())
+        ctx.load(slots, n_new, tokens, out_rows, buf)
+        ev.record()
+        if entry[1] is None:
+            logits = self.model.forward(ctx)          # the real step, uncaptured; this also loads every kernel
+            from ..kernels import ops
+            graph = torch.cuda.CUDAGraph()
+            n0 = ops.launch_count()
+            with torch.cuda.graph(graph):
+                captured = self.model.forward(ctx)    # recorded, not run
+            entry[1], entry[2] = graph, captured
+            entry.append(ops.launch_count() - n0)     # kernels a replay launches
+            ops._launches = n0                        # the capture itself launched nothing
+            return logits
+        entry[1].replay()
+        from ..kernels import ops
+        ops._launches += entry[3]
+        self.graph_replays += 1
+        return entry[2]
+
     def check(self) -> None:
-        """Waits for the device and raises if a kernel of the last step flagged an error."""
-        ctx = getattr(self, "_last_ctx", None)
-        if ctx is None:
-            return
-        code = int(ctx.err.item())
+        """Waits for the device and raises if a kernel flagged an error since the last check."""
         from ..kernels import tc_error
+        code = int(self.err.item())
         tc = tc_error(self.env.device)
         if tc:
             raise StepError(f"a tensor-core kernel gave up a bounded wait (code {tc}); its output is not valid")
         if code:
+            self.err.zero_()
             what = {1: "a token id outside the embedding table", 2: "a position outside the rotary table"}
-            raise StepError(f"device-side check failed in the last step: {what.get(code, code)}")
+            raise StepError(f"device-side check failed: {what.get(code, code)}")
 
 
-def build_engine(spec: ModelSpec, dtype: torch.dtype, device, cache_config: CacheConfig, source) -> Engine:
+def build_engine(spec: ModelSpec, dtype: torch.dtype, device, cache_config: CacheConfig, source,
+                 use_graphs: bool = True) -> Engine:
     """Builds the model of `spec`, binds its weights from `source` (see weights.loader) and
     wraps it with a cache."""
     from ..weights.loader import load_weights
     device = torch.device(device)
     model = DecoderModel(spec, BuildEnv(dtype=dtype, device=device))
     load_weights(model, source)
-    return Engine(model, cache_config)
+    return Engine(model, cache_config, use_graphs=use_graphs)

@@ -36,6 +36,16 @@ class DecoderModel:
     def state_sizes(self) -> List[int]:
         return [self.blocks[c.layer].mixer.state_size() for c in self.spec.order]
 
+    def capturable(self) -> bool:
+        """True when every part's forward only enqueues device work (no host read-back), so that
+        a decode step can be captured in a CUDA graph."""
+        return all(getattr(p, "capturable", False) for p in self.parts())
+
+    def prepare(self, max_positions: int) -> None:
+        """Lets parts size what depends on the longest sequence the cache can hold."""
+        for p in self.parts():
+            p.prepare(max_positions)
+
     # ---- weights
     def parts(self) -> List[Part]:
         ps: List[Part] = [self.embedding]

@@ -263,6 +263,26 @@ class _AttnParams(ctypes.Structure):
                 ("scale", c_float), ("all_from_cache", c_int), ("n_splits", c_int), ("part_o", c_void_p), ("part_ml", c_void_p)]
 
 
+class _MmaAttnParams(ctypes.Structure):
+    _fields_ = [("q", c_void_p), ("k_new", c_void_p), ("v_new", c_void_p), ("row_stride", c_int),
+                ("out", c_void_p), ("kpool", c_void_p), ("vpool", c_void_p), ("page_table", c_void_p),
+                ("table_stride", c_int), ("ring", c_int), ("seq_start", c_void_p),
+                ("seq_len_before", c_void_p), ("nh", c_int), ("nkvh", c_int), ("window", c_int),
+                ("scale", c_float), ("all_from_cache", c_int), ("n_splits", c_int), ("part_o", c_void_p),
+                ("part_ml", c_void_p), ("err", c_void_p)]
+
+
+MMA_ATTENTION = True                         # tests switch the tensor-core attention off to compare
+
+
+def _mma_ok(qkv, dh) -> bool:
+    return MMA_ATTENTION and qkv.dtype == torch.bfloat16 and dh % 16 == 0 and dh <= 128 and qkv.stride(0) % 8 == 0
+
+
+def _mma_lib(dh: int):
+    return load_module("attention_mma.cu", {"LLB_HEAD_DIM": dh})
+
+
 def _attn_lib(dh: int):
     if dh % 2 or dh > 256:
         raise KernelError(f"attention: head size {dh} is not supported (even, at most 256)")
@@ -270,9 +290,9 @@ def _attn_lib(dh: int):
 
 
 def _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before,
-                 window, scale):
+                 window, scale, cls=None):
     es = qkv.element_size()
-    p = _AttnParams()
+    p = (cls or _AttnParams)()
     p.q = qkv.data_ptr()
     p.k_new = qkv.data_ptr() + nh * dh * es
     p.v_new = qkv.data_ptr() + (nh + nkvh) * dh * es
@@ -295,6 +315,13 @@ def attention_prefill(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_sta
     _need_cuda(qkv, kpool, vpool, page_table)
     assert qkv.dtype == kpool.dtype == vpool.dtype
     out = torch.empty((qkv.shape[0], nh * dh), dtype=qkv.dtype, device=qkv.device)
+    if _mma_ok(qkv, dh):
+        p = _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before, window,
+                         scale, _MmaAttnParams)
+        p.all_from_cache, p.err = int(all_from_cache), _tc_resources(qkv.device)[2].data_ptr()
+        f = _fn(_mma_lib(dh), "llb_attn_mma_prefill", [_MmaAttnParams, c_int, c_int, c_void_p])
+        _check(f(p, n_seqs, max_new, _stream()), "attention_prefill (tensor cores)")
+        return out
     p = _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before, window, scale)
     p.all_from_cache = int(all_from_cache)
     f = _fn(_attn_lib(dh), "llb_attn_prefill", [_AttnParams, c_int, c_int, c_int, c_void_p])
@@ -308,15 +335,22 @@ def attention_decode(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_star
     _need_cuda(qkv, kpool, vpool, page_table)
     assert qkv.dtype == kpool.dtype == vpool.dtype
     out = torch.empty((qkv.shape[0], nh * dh), dtype=qkv.dtype, device=qkv.device)
-    p = _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before, window, scale)
+    mma = _mma_ok(qkv, dh)
+    p = _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before, window, scale,
+                     _MmaAttnParams if mma else None)
     keep = None
     if n_splits > 1:
         part_o = torch.empty((n_seqs, nh, n_splits, dh), dtype=torch.float32, device=qkv.device)
         part_ml = torch.empty((n_seqs, nh, n_splits, 2), dtype=torch.float32, device=qkv.device)
         p.n_splits, p.part_o, p.part_ml = n_splits, part_o.data_ptr(), part_ml.data_ptr()
         keep = (part_o, part_ml)
-    f = _fn(_attn_lib(dh), "llb_attn_decode", [_AttnParams, c_int, c_int, c_void_p])
-    _check(f(p, _dt(qkv), n_seqs, _stream()), "attention_decode", 2 if n_splits > 1 else 1)
+    if mma:
+        p.err = _tc_resources(qkv.device)[2].data_ptr()
+        f = _fn(_mma_lib(dh), "llb_attn_mma_decode", [_MmaAttnParams, c_int, c_void_p])
+        _check(f(p, n_seqs, _stream()), "attention_decode (tensor cores)", 2 if n_splits > 1 else 1)
+    else:
+        f = _fn(_attn_lib(dh), "llb_attn_decode", [_AttnParams, c_int, c_int, c_void_p])
+        _check(f(p, _dt(qkv), n_seqs, _stream()), "attention_decode", 2 if n_splits > 1 else 1)
     del keep
     return out
 

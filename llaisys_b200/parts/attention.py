@@ -38,6 +38,14 @@ class GQAttention(Mixer):
         self.position = build_part("position", p["position"], env) if p.get("position") else None
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
 
+    @property
+    def capturable(self):
+        return self.position is None or self.position.capturable
+
+    def prepare(self, max_positions):
+        if self.position is not None:
+            self.position.prepare(max_positions)
+
     def kv_need(self):
         return KVNeed(self.nkvh, self.dh, self.window)
 

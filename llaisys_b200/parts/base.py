@@ -82,9 +82,13 @@ class KVNeed:
 class Part:
     """Base of all parts."""
     category = kind = "?"
+    capturable = False      # True: forward() only enqueues device work and may be captured in a CUDA graph
 
     def __init__(self, spec: PartSpec, env: BuildEnv):
         self.spec, self.env = spec, env
+
+    def prepare(self, max_positions: int) -> None:
+        """Called once before the first step with the longest sequence the cache can hold."""
 
     def tensors(self) -> Dict[str, TensorDecl]:
         """local tensor name -> declaration; the file's name is spec.prefix + "." + local name."""
@@ -136,6 +140,7 @@ class Block(Part):
 
     def __init__(self, mixer: Mixer, mixer_norm: Norm, ffn: FeedForward, ffn_norm: Norm, env: BuildEnv):
         self.mixer, self.mixer_norm, self.ffn, self.ffn_norm, self.env = mixer, mixer_norm, ffn, ffn_norm, env
+        self.spec = None
 
     def forward(self, residual: torch.Tensor, pending: Optional[torch.Tensor], ctx, call: int):
         """residual: float32 [T, H]; pending: a delta not yet added to it (or None).

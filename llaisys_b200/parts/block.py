@@ -8,6 +8,8 @@ class PreNormResidual(Block):
     """x -> norm -> mixer -> +x -> norm -> feed-forward -> +   (xsmccc/llaisys
     src/models/qwen2/layer.hpp:47-84).  Each residual add is done by the norm that follows it,
     so the block hands its last delta on to the next block (or to the final norm)."""
+    capturable = True
+
 
     def forward(self, residual, pending, ctx, call):
         h = self.mixer_norm.forward(residual, pending)

@@ -9,6 +9,8 @@ class TokenEmbedding(Part):
     """x[t] = E[id[t]] (xsmccc/llaisys src/ops/embedding/cpu/embedding_cpu.cpp:16-22), written
     as the float32 residual stream.  An id outside the table is reported through ctx.err.
     params: vocab_size, hidden_size."""
+    capturable = True
+
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -30,6 +32,8 @@ class LMHead(Part):
     """logits = h W^T in float32, no bias (xsmccc/llaisys src/models/qwen2/qwen2.cpp:76-77).
     With params["tied_to"] set, W is the tensor of that name (the embedding table) and the part
     declares no tensor of its own.  params: vocab_size, hidden_size, tied_to."""
+    capturable = True
+
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

@@ -11,6 +11,8 @@ class SwiGLUMLP(FeedForward):
     """down(up(x) * silu(gate(x))), no biases (xsmccc/llaisys src/models/qwen2/mlp.hpp:18-39,
     src/ops/swiglu/cpu/swiglu_cpu.cpp:13-21).  The gate and up matrices are kept as one
     [2I, H] matrix so that one product serves both.  params: hidden_size, intermediate_size."""
+    capturable = True
+
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

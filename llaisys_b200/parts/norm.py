@@ -9,6 +9,8 @@ class RMSNorm(Norm):
     """y = x * w / sqrt(mean(x^2) + eps): eps inside the root, plain weight
     (xsmccc/llaisys src/ops/rms_norm/cpu/rms_norm_cpu.cpp:15-34), fused with the residual add
     that precedes it (src/models/qwen2/layer.hpp:60-71).  params: size, eps."""
+    capturable = True
+
 
     def __init__(self, spec, env):
         super().__init__(spec, env)

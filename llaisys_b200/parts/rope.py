@@ -13,6 +13,8 @@ class RotaryHalfSplit(PositionEncoding):
     (xsmccc/llaisys src/ops/rope/cpu/rope_cpu.cpp:16-46, which computes the angle in double
     precision from theta held as a C float).  The cos/sin table is built once in float64 on the
     host, kept in float32, and grows with the longest position asked for.  params: head_dim, theta."""
+    capturable = True
+
 
     def __init__(self, spec, env):
         super().__init__(spec, env)
@@ -32,6 +34,9 @@ class RotaryHalfSplit(PositionEncoding):
             self._cos = torch.cos(ang).to(torch.float32).to(self.env.device)
             self._sin = torch.sin(ang).to(torch.float32).to(self.env.device)
         return self._cos, self._sin
+
+    def prepare(self, max_positions):
+        self.table(max_positions)          # full size once: a captured step must not see the table move
 
     def apply(self, qkv, num_heads, num_kv_heads, ctx, append=None):
         cos, sin = self.table(ctx.max_position + 1)

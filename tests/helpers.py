@@ -88,13 +88,14 @@ def tolerance(dtype: torch.dtype, config: dict, ref: np.ndarray) -> float:
     return 8 * u * math.sqrt(6 * L + 2) * float(np.sqrt(np.mean(ref ** 2)))
 
 
-def build_engine(folder, dtype: torch.dtype, max_tokens: int, max_seqs=None):
+def build_engine(folder, dtype: torch.dtype, max_tokens: int, max_seqs=None, use_graphs=True):
     from llaisys_b200.cache import CacheConfig
     from llaisys_b200.config import load_config
     from llaisys_b200.engine import build_engine as be
     from llaisys_b200.weights import FolderSource
     cfg = load_config(folder)
-    return be(cfg.to_spec(), dtype, "cuda:0", CacheConfig(max_tokens=max_tokens, max_seqs=max_seqs), FolderSource(folder))
+    return be(cfg.to_spec(), dtype, "cuda:0", CacheConfig(max_tokens=max_tokens, max_seqs=max_seqs), FolderSource(folder),
+              use_graphs=use_graphs)
 
 
 # ----------------------------------------------------------------------------- schedules

@@ -108,6 +108,26 @@ def test_first_tokens(model, dtype):
     compare(got, oracle, reqs, dtype, cfg, f"{name} first tokens")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_captured_decode_steps_equal_uncaptured_ones(model, dtype):
+    """Decode steps are replayed from a CUDA graph once their shape has been seen; that must
+    change nothing but rounding (the key range is sliced differently)."""
+    name = model.name
+    folder, oracle = model.at(dtype)
+    cfg = CONFIGS[name]
+    reqs = random_requests(cfg, [150, 9, 70], seed=17)
+    outs = []
+    for graphs in (True, False):
+        engine = build_engine(folder, dtype, max_tokens=64 * 5, use_graphs=graphs)
+        outs.append(run_batches(engine, reqs, [[0, 1, 2]], [20, 2, 5]))
+        assert (engine.graph_replays > 100) == graphs
+    compare(outs[0], oracle, reqs, dtype, cfg, f"{name} captured")
+    bound = 2e-5 if dtype == torch.float32 else None
+    for key, row in outs[1].items():
+        if bound:
+            assert np.abs(row - outs[0][key]).max() < bound, key
+
+
 def test_padding_and_company_change_nothing(model):
     """float32: a request's logits are the same alone and in a batch, up to rounding."""
     name, folder, oracle, requests = model

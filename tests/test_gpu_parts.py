@@ -23,7 +23,10 @@ def _ctx(cache, slots, n_new, tokens=None, want=()):
     for s, n in zip(slots, n_new):
         cache.book.reserve(s, n)
     tokens = tokens if tokens is not None else [0] * sum(n_new)
-    return StepContext(cache, slots, n_new, tokens, list(want), DEV)
+    shape = StepContext.shape_of(cache, slots, n_new, list(want), bucket=False)
+    ctx = StepContext(cache, DEV, *shape, torch.zeros(1, dtype=torch.int32, device=DEV))
+    ctx.load(slots, n_new, tokens, list(want))
+    return ctx
 
 
 def _commit(cache, slots, n_new):
@@ -215,6 +218,7 @@ def test_toy_parts_register_build_and_step():
     engine = Engine(model, CacheConfig(max_tokens=256, max_seqs=3))
     assert len(engine.cache.k_pools) == 1 and engine.cache.k_pools[0].shape[0] == 1        # one cache for both attention calls
     assert set(engine.cache.state) == {0, 2}
+    assert not engine.use_graphs                     # the toy parts read back from the device: never captured
     toks = np.random.default_rng(0).integers(0, 50, size=90).tolist()
     a = engine.acquire()
     whole = engine.step([StepEntry(a, toks, list(range(90)))])
