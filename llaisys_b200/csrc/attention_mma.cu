@@ -4,19 +4,20 @@
 // (xsmccc/llaisys src/ops/self_attention/cpu/self_attention_cpu.cpp:28-112, plus the window).
 //
 // Keys and values are walked in tiles of one cache page (64 keys).  A tile's rows are fetched
-// with one cp.async.bulk per row into a ring of shared-memory stages whose rows are padded by 16
-// bytes (so that ldmatrix reads them without bank conflicts); an mbarrier per stage counts the
-// bytes.  A row comes from the cache page of its position or, for positions of the step itself
-// in prefill, from the packed projection output.  Scores, the running maximum, the exponentials
-// and the normaliser are float32; the probabilities are rounded to bfloat16 only as the
-// tensor-core operand of P*V.
+// with 16-byte cp.async copies by all threads into a ring of shared-memory stages whose rows are
+// padded by 16 bytes (so that ldmatrix reads them without bank conflicts).  (One bulk copy per
+// row was measured first: the copy engine takes them one after another, about 36 ns each, which
+// made a tile cost 4.6 us.)  A row comes from the cache page of its position or, for positions
+// of the step itself in prefill, from the packed projection output.  Scores, the running
+// maximum, the exponentials and the normaliser are float32; the probabilities are rounded to
+// bfloat16 only as the tensor-core operand of P*V.
 //
 //  * decode: a block owns up to 16 query heads that share one kv head, for one sequence and one
 //    slice of its key range; its four warps take 16 keys each of every tile and are merged at the
 //    end; slices are merged by llb_attn_mma_combine.
 //  * prefill: a block owns 64 consecutive new tokens of one query head; each warp 16 of them.
 //
-// Waits on mbarriers are bounded; when one runs out the block sets *err and returns.
+// The only waits are cp.async.wait_group and __syncthreads, which cannot outlast the copies.
 #include "common.cuh"
 
 #ifndef LLB_HEAD_DIM
@@ -36,8 +37,6 @@ constexpr int STAGES = 3;
 constexpr int THREADS = 128;
 constexpr int KSTEPS = DH / 16;
 constexpr int DTILES = DH / 8;
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
-enum { ERR_ATTN_WAIT = 111 };
 
 struct MmaAttnParams {
     const bf16* q;          // packed projections [T, row_stride]; query head h at column h * DH
@@ -58,31 +57,15 @@ struct MmaAttnParams {
     int n_splits;           // decode
     float* part_o;          // decode: [B, nh, n_splits, DH]
     float* part_ml;         // decode: [B, nh, n_splits, 2]
-    int* err;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
 }
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-    uint32_t done;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-    return done != 0;
-}
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (uint32_t i = 0; i < WAIT_LIMIT; ++i)
-        if (mbar_try(bar, parity)) return true;
-    return false;
-}
-__device__ __forceinline__ void bulk_row(uint32_t dst, const void* src, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(dst), "l"(src), "r"((uint32_t)ROW_BYTES), "r"(bar) : "memory");
-}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 __device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
@@ -109,15 +92,16 @@ struct Source {
     bool use_new;           // positions >= len_before come from k_new / v_new
 };
 
-// Issues the row copies of tile `tile` (key positions tile*TILE ...) restricted to [key_lo, key_hi]
-// into stage memory at `stage`; executed by all lanes of one warp.
-__device__ __forceinline__ void issue_tile(const Source& s, int tile, int key_lo, int key_hi, uint32_t stage, uint32_t bar,
-                                           int lane) {
-    int p0 = tile * TILE;
-    int j_lo = max(0, key_lo - p0), j_hi = min(TILE, key_hi - p0 + 1);       // valid rows [j_lo, j_hi)
-    if (lane == 0) mbar_expect_tx(bar, (uint32_t)(max(0, j_hi - j_lo) * 2 * ROW_BYTES));
-    __syncwarp();
-    for (int j = j_lo + lane; j < j_hi; j += 32) {
+// Starts the copies of tile `tile` (key positions tile*TILE ...) restricted to [key_lo, key_hi] into
+// stage memory at `stage`; all threads of the block take part.  The caller commits the group.
+__device__ __forceinline__ void issue_tile(const Source& s, int tile, int key_lo, int key_hi, uint32_t stage, int tid) {
+    constexpr int CH = ROW_BYTES / 16;                     // 16-byte chunks of a row
+    const int p0 = tile * TILE;
+    const int j_lo = max(0, key_lo - p0), j_hi = min(TILE, key_hi - p0 + 1);       // valid rows [j_lo, j_hi)
+    const size_t page_off = paged_row(s.table, s.ring, p0, s.kvh, s.nkvh, DH);      // one page per tile
+    for (int i = tid; i < TILE * CH; i += THREADS) {
+        int j = i / CH, c = i - j * CH;
+        if (j < j_lo || j >= j_hi) continue;
         int pos = p0 + j;
         const bf16 *ks, *vs;
         if (s.use_new && pos >= s.len_before) {
@@ -125,12 +109,13 @@ __device__ __forceinline__ void issue_tile(const Source& s, int tile, int key_lo
             ks = s.k_new + off;
             vs = s.v_new + off;
         } else {
-            size_t off = paged_row(s.table, s.ring, pos, s.kvh, s.nkvh, DH);
+            size_t off = page_off + (size_t)j * DH;
             ks = s.kpool + off;
             vs = s.vpool + off;
         }
-        bulk_row(stage + j * ROW_STRIDE, ks, bar);
-        bulk_row(stage + TILE_BYTES + j * ROW_STRIDE, vs, bar);
+        uint32_t d = stage + j * ROW_STRIDE + c * 16;
+        cp_async16(d, ks + c * 8);
+        cp_async16(d + TILE_BYTES, vs + c * 8);
     }
 }
 
@@ -248,42 +233,28 @@ __device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], float
     }
 }
 
-// A wait ran out: record it, and give copies that may still be in flight a bounded time to land
-// before the block's shared memory is released.
-__device__ __forceinline__ void give_up(int* err, int tid) {
-    if (tid == 0) atomicExch(err, ERR_ATTN_WAIT);
-    for (int i = 0; i < 1000; ++i) __nanosleep(1000);
-    __syncthreads();
-}
-
 struct Ring {
-    uint32_t base, bars;
+    uint32_t base;
     uint8_t* ptr;
     __device__ uint32_t stage(int i) const { return base + (i % STAGES) * STAGE_BYTES; }
     __device__ uint8_t* stage_ptr(int i) const { return ptr + (i % STAGES) * STAGE_BYTES; }
-    __device__ uint32_t bar(int i) const { return bars + 8 * (i % STAGES); }
 };
 
-__device__ __forceinline__ Ring make_ring(uint8_t* smem_raw, int tid) {
+__device__ __forceinline__ Ring make_ring(uint8_t* smem_raw) {
     Ring r;
     uint32_t raw = smem_u32(smem_raw);
     r.base = (raw + 127u) & ~127u;
     r.ptr = smem_raw + (r.base - raw);
-    r.bars = r.base + STAGES * STAGE_BYTES;
-    if (tid == 0) {
-        for (int s = 0; s < STAGES; ++s) mbar_init(r.bars + 8 * s, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
     return r;
 }
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + STAGES * 8 + 128;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 128;
 
 // ------------------------------------------------------------------ decode
 __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    Ring ring = make_ring(smem_raw, tid);
+    Ring ring = make_ring(smem_raw);
+    llb_grid_dependency_sync();
 
     const int b = blockIdx.z;
     const int G = p.nh / p.nkvh;
@@ -303,8 +274,10 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
 
     Source src{p.kpool, p.vpool, nullptr, nullptr, p.page_table + (size_t)b * p.table_stride,
                p.ring, p.nkvh, kvh, 0, 0, 0, false};
-    if (warp == 0)
-        for (int i = 0; i < min(STAGES, n_tiles); ++i) issue_tile(src, tile_lo + i, key_lo, pos, ring.stage(i), ring.bar(i), lane);
+    for (int i = 0; i < STAGES; ++i) {
+        if (i < n_tiles) issue_tile(src, tile_lo + i, key_lo, pos, ring.stage(i), tid);
+        cp_async_commit();                                 // one group per stage, empty or not
+    }
 
     uint32_t qf[KSTEPS][4];
     load_q(qf, [&](int r) -> const bf16* {
@@ -314,22 +287,17 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
     for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
     const float scale_log2 = p.scale * 1.4426950408889634f;
 
-    bool failed = false;
     for (int i = 0; i < n_tiles; ++i) {
-        bool ok = mbar_wait(ring.bar(i), (i / STAGES) & 1);
-        if (__syncthreads_or(!ok)) { failed = true; break; }       // the whole block leaves together
+        cp_async_wait<STAGES - 1>();                       // this thread's copies of tile i have landed
+        __syncthreads();                                   // ... and everyone else's
         zero_unfetched(ring.stage_ptr(i), tile_lo + i, key_lo, pos, tid);
         tile_step<2>(qf, o, m, l, ring.stage(i), warp * 16, (tile_lo + i) * TILE, key_lo, pos, key_lo, pos, scale_log2, lane);
         __syncthreads();                                   // the stage is free
-        if (warp == 0 && i + STAGES < n_tiles) {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            issue_tile(src, tile_lo + i + STAGES, key_lo, pos, ring.stage(i + STAGES), ring.bar(i + STAGES), lane);
-        }
+        if (i + STAGES < n_tiles) issue_tile(src, tile_lo + i + STAGES, key_lo, pos, ring.stage(i + STAGES), tid);
+        cp_async_commit();
     }
-    if (failed) {
-        give_up(p.err, tid);
-        return;
-    }
+    cp_async_wait<0>();
+    __syncthreads();
 
     // ---- merge the four warps (each saw a quarter of the keys) through shared memory
     float* sm_ml = reinterpret_cast<float*>(ring.ptr);               // [4][16][2]
@@ -383,6 +351,7 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
 __global__ void attn_mma_combine_kernel(bf16* __restrict__ out, const float* __restrict__ part_o,
                                         const float* __restrict__ part_ml, const int* __restrict__ seq_start, int nh,
                                         int n_splits) {
+    llb_grid_dependency_sync();
     int head = blockIdx.x, b = blockIdx.y;
     size_t base = ((size_t)b * nh + head) * n_splits;
     float M = -INFINITY;
@@ -408,10 +377,11 @@ __global__ void __launch_bounds__(THREADS) attn_mma_prefill_kernel(MmaAttnParams
     extern __shared__ uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.z, head = blockIdx.y;
+    llb_grid_dependency_sync();
     const int tok0 = p.seq_start[b], n_new = p.seq_start[b + 1] - tok0, len_before = p.seq_len_before[b];
     const int t0 = blockIdx.x * 64;
     if (t0 >= n_new) return;
-    Ring ring = make_ring(smem_raw, tid);
+    Ring ring = make_ring(smem_raw);
     const int kvh = head / (p.nh / p.nkvh);
     const int n_rows = min(64, n_new - t0);
     const int first_pos = len_before + t0, last_pos = first_pos + n_rows - 1;
@@ -420,9 +390,10 @@ __global__ void __launch_bounds__(THREADS) attn_mma_prefill_kernel(MmaAttnParams
 
     Source src{p.kpool, p.vpool, p.k_new, p.v_new, p.page_table + (size_t)b * p.table_stride,
                p.ring, p.nkvh, kvh, p.row_stride, tok0, len_before, !p.all_from_cache};
-    if (warp == 0)
-        for (int i = 0; i < min(STAGES, n_tiles); ++i)
-            issue_tile(src, tile_lo + i, key_lo, last_pos, ring.stage(i), ring.bar(i), lane);
+    for (int i = 0; i < STAGES; ++i) {
+        if (i < n_tiles) issue_tile(src, tile_lo + i, key_lo, last_pos, ring.stage(i), tid);
+        cp_async_commit();
+    }
 
     // this thread's two query rows
     const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;
@@ -439,24 +410,18 @@ __global__ void __launch_bounds__(THREADS) attn_mma_prefill_kernel(MmaAttnParams
     for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
     const float scale_log2 = p.scale * 1.4426950408889634f;
 
-    bool failed = false;
     for (int i = 0; i < n_tiles; ++i) {
-        bool ok = mbar_wait(ring.bar(i), (i / STAGES) & 1);
-        if (__syncthreads_or(!ok)) { failed = true; break; }
+        cp_async_wait<STAGES - 1>();
+        __syncthreads();
         zero_unfetched(ring.stage_ptr(i), tile_lo + i, key_lo, last_pos, tid);
         int p0 = (tile_lo + i) * TILE;
         if (p0 <= warp_hi && p0 + TILE - 1 >= warp_lo)               // the tile holds a key some row of the warp sees
             tile_step<8>(qf, o, m, l, ring.stage(i), 0, p0, lo0, hi0, lo1, hi1, scale_log2, lane);
         __syncthreads();
-        if (warp == 0 && i + STAGES < n_tiles) {
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            issue_tile(src, tile_lo + i + STAGES, key_lo, last_pos, ring.stage(i + STAGES), ring.bar(i + STAGES), lane);
-        }
+        if (i + STAGES < n_tiles) issue_tile(src, tile_lo + i + STAGES, key_lo, last_pos, ring.stage(i + STAGES), tid);
+        cp_async_commit();
     }
-    if (failed) {
-        give_up(p.err, tid);
-        return;
-    }
+    cp_async_wait<0>();
     const int c = (lane & 3) * 2;
     if (r0 < n_rows) {
         float inv = 1.0f / l[0];
@@ -499,7 +464,7 @@ LLB_API int llb_attn_mma_prefill(MmaAttnParams p, int B, int max_new, cudaStream
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
     int rc = configure<0>(attn_mma_prefill_kernel);
     if (rc) return rc;
-    attn_mma_prefill_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(p);
+    llb_launch(attn_mma_prefill_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, p);
     return llb_status();
 }
 
@@ -511,10 +476,10 @@ LLB_API int llb_attn_mma_decode(MmaAttnParams p, int B, cudaStream_t stream) {
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
     int rc = configure<1>(attn_mma_decode_kernel);
     if (rc) return rc;
-    attn_mma_decode_kernel<<<grid, THREADS, SMEM_BYTES, stream>>>(p);
+    llb_launch(attn_mma_decode_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, p);
     rc = llb_status();
     if (rc == 0 && p.n_splits > 1) {
-        attn_mma_combine_kernel<<<dim3(p.nh, B), 128, 0, stream>>>(p.out, p.part_o, p.part_ml, p.seq_start, p.nh, p.n_splits);
+        llb_launch(attn_mma_combine_kernel, dim3(p.nh, B), dim3(128), 0, stream, p.out, p.part_o, p.part_ml, p.seq_start, p.nh, p.n_splits);
         rc = llb_status();
     }
     return rc;

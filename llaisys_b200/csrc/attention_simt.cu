@@ -60,6 +60,7 @@ __global__ void __launch_bounds__(WARPS * 32) attn_kernel(AttnParams p) {
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.z;
+    llb_grid_dependency_sync();
     const int tok0 = p.seq_start[b];
     const int n_new = p.seq_start[b + 1] - tok0;
     const int len_before = p.seq_len_before[b];
@@ -217,6 +218,7 @@ template <typename T>
 __global__ void attn_combine_kernel(T* __restrict__ out, const float* __restrict__ part_o,
                                     const float* __restrict__ part_ml, const int* __restrict__ seq_start,
                                     int nh, int n_splits) {
+    llb_grid_dependency_sync();
     int head = blockIdx.x, b = blockIdx.y;
     size_t base = ((size_t)b * nh + head) * n_splits;
     float M = -INFINITY;
@@ -251,7 +253,7 @@ static int launch_attn(const AttnParams& p, dim3 grid, cudaStream_t stream) {
         if (e != cudaSuccess) return (int)e;
     }
     configured = true;
-    k<<<grid, WARPS * 32, smem, stream>>>(p);
+    llb_launch(k, grid, dim3(WARPS * 32), smem, stream, p);
     return llb_status();
 }
 
@@ -279,8 +281,8 @@ LLB_API int llb_attn_decode(AttnParams p, int dtype, int B, cudaStream_t stream)
     LLB_DISPATCH_DTYPE(dtype, T, {
         rc = launch_attn<T, true>(p, grid, stream);
         if (rc == 0 && p.n_splits > 1) {
-            attn_combine_kernel<T><<<dim3(p.nh, B), 128, 0, stream>>>(
-                (T*)p.out, p.part_o, p.part_ml, p.seq_start, p.nh, p.n_splits);
+            llb_launch(attn_combine_kernel<T>, dim3(p.nh, B), dim3(128), 0, stream,
+                       (T*)p.out, (const float*)p.part_o, (const float*)p.part_ml, p.seq_start, p.nh, p.n_splits);
             rc = llb_status();
         }
         return rc;

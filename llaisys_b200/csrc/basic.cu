@@ -12,6 +12,7 @@
 template <typename TW>
 __global__ void embedding_kernel(float* __restrict__ out, const TW* __restrict__ table,
                                  const int* __restrict__ ids, int H, int V, int* err) {
+    llb_grid_dependency_sync();
     int t = blockIdx.x;
     int id = ids[t];
     bool ok = id >= 0 && id < V;
@@ -25,7 +26,7 @@ LLB_API int llb_embedding(float* out, const void* table, int table_dtype, const 
                           int H, int V, int* err, cudaStream_t stream) {
     if (T == 0) return 0;
     LLB_DISPATCH_DTYPE(table_dtype, TW,
-        embedding_kernel<TW><<<T, 256, 0, stream>>>(out, (const TW*)table, ids, H, V, err));
+        llb_launch(embedding_kernel<TW>, dim3(T), dim3(256), 0, stream, out, (const TW*)table, ids, H, V, err));
     return llb_status();
 }
 
@@ -39,6 +40,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __res
                                    float eps, int write_back) {
     extern __shared__ float rowbuf[];          // H floats
     __shared__ float red[32];
+    llb_grid_dependency_sync();
     int r = blockIdx.x;
     size_t src = rows ? (size_t)rows[r] : (size_t)r;
     float* res = residual + src * H;
@@ -78,8 +80,8 @@ static int add_rmsnorm_out(float* residual, const void* delta, int n_part, size_
     LLB_DISPATCH_DTYPE(out_dtype, TO, {
         auto k = add_rmsnorm_kernel<TD, TW, TO>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        k<<<R, 256, smem, stream>>>(residual, (const TD*)delta, n_part, part_stride,
-                                    (const TW*)weight, (TO*)out, rows, H, eps, write_back);
+        llb_launch(k, dim3(R), dim3(256), smem, stream, residual, (const TD*)delta, n_part, part_stride,
+                   (const TW*)weight, (TO*)out, rows, H, eps, write_back);
     });
     return llb_status();
 }
@@ -106,6 +108,7 @@ LLB_API int llb_add_rmsnorm(float* residual, const void* delta, int delta_dtype,
 template <typename TD>
 __global__ void add_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_part,
                            size_t part_stride, size_t n) {
+    llb_grid_dependency_sync();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     float d = 0.f;
@@ -117,8 +120,8 @@ LLB_API int llb_residual_add(float* residual, const void* delta, int delta_dtype
                              long long part_stride, long long n, cudaStream_t stream) {
     if (n == 0) return 0;
     LLB_DISPATCH_DTYPE(delta_dtype, TD,
-        add_kernel<TD><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(
-            residual, (const TD*)delta, n_part, (size_t)part_stride, (size_t)n));
+        llb_launch(add_kernel<TD>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream,
+                   residual, (const TD*)delta, n_part, (size_t)part_stride, (size_t)n));
     return llb_status();
 }
 
@@ -138,6 +141,7 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int row_stride, int nh, 
                                    T* __restrict__ kpool, T* __restrict__ vpool,
                                    const int* __restrict__ page_table, int table_stride, int ring,
                                    int* err) {
+    llb_grid_dependency_sync();
     int t = blockIdx.x;
     int pos = tok_pos[t];
     T* row = qkv + (size_t)t * row_stride;
@@ -192,7 +196,7 @@ static void launch_rope_append(TT* qkv, int T, int row_stride, int nh, int nkvh,
                                const int* page_table, int table_stride, int ring, int* err,
                                cudaStream_t stream) {
 #define LLB_RA(R, A)                                                                          \
-    rope_append_kernel<TT, R, A><<<T, 128, 0, stream>>>(                                      \
+    llb_launch(rope_append_kernel<TT, R, A>, dim3(T), dim3(128), 0, stream,                   \
         qkv, row_stride, nh, nkvh, dh, cos_t, sin_t, table_rows, tok_pos, tok_seq, seq_start, \
         seq_len_before, kpool, vpool, page_table, table_stride, ring, err)
     if (do_rope && do_append) LLB_RA(true, true);
@@ -220,6 +224,7 @@ LLB_API int llb_rope_append(void* qkv, int dtype, int T, int row_stride, int nh,
 // gate_up is [T, 2I] with the gate columns first; out[t, i] = up * gate / (1 + exp(-gate)).
 template <typename T>
 __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int I, size_t n) {
+    llb_grid_dependency_sync();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     size_t t = i / I;
@@ -233,7 +238,7 @@ LLB_API int llb_swiglu(void* out, const void* gate_up, int dtype, int T, int I, 
     size_t n = (size_t)T * I;
     if (n == 0) return 0;
     LLB_DISPATCH_DTYPE(dtype, TT,
-        swiglu_kernel<TT><<<(unsigned)((n + 255) / 256), 256, 0, stream>>>((TT*)out, (const TT*)gate_up, I, n));
+        llb_launch(swiglu_kernel<TT>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (TT*)out, (const TT*)gate_up, I, n));
     return llb_status();
 }
 

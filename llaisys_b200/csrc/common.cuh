@@ -47,6 +47,44 @@ __device__ __forceinline__ size_t paged_row(const int* table, int ring, int pos,
 
 static inline int llb_status() { return (int)cudaGetLastError(); }
 
+// ---- programmatic dependent launch
+// Kernels of a step follow one another on one stream, each a few microseconds long, so the gap
+// between them matters.  Every kernel is launched with programmatic stream serialization: it may
+// start (be scheduled, set up its shared memory, barriers and tensor memory) while its
+// predecessor is still running, and calls llb_grid_dependency_sync() before it first touches
+// global memory; that call returns when the predecessor has completed and its writes are
+// visible.  The same call lets this kernel's successor start early in turn.  LLAISYS_PDL=0 in
+// the environment launches the plain way (the device-side call is then a no-op).
+__device__ __forceinline__ void llb_grid_dependency_sync() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+#include <stdlib.h>
+static inline bool llb_pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("LLAISYS_PDL");
+        v = (e && e[0] == '0') ? 0 : 1;
+    }
+    return v != 0;
+}
+
+template <typename... P, typename... A>
+static inline void llb_launch(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = llb_pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<P>(args)...);
+}
+
 #define LLB_DISPATCH_DTYPE(code, T, ...)                                   \
     do {                                                                   \
         if ((code) == LLB_F32) { typedef float T; __VA_ARGS__; }           \

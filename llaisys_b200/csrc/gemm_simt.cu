@@ -14,6 +14,7 @@ gemm_tile_kernel(const TX* __restrict__ X, const TW* __restrict__ W, const void*
     constexpr int BM = 64, BN = 64, BK = 16;
     __shared__ float Xs[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
+    llb_grid_dependency_sync();
     int tid = threadIdx.x;
     int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     int ty = tid / 16, tx = tid % 16;
@@ -66,6 +67,7 @@ template <typename TX, typename TW, typename TO, int MR>
 __global__ void __launch_bounds__(256)
 gemm_rows_kernel(const TX* __restrict__ X, const TW* __restrict__ W, const void* __restrict__ bias,
                  int bias_dtype, TO* __restrict__ Y, int M, int N, int K, int ldx, int ldy) {
+    llb_grid_dependency_sync();
     int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= N) return;
     const TW* w = W + (size_t)warp * K;
@@ -96,12 +98,12 @@ static void launch(const void* X, const void* W, const void* bias, int bias_dtyp
     if (M <= 8) {
         int warps_per_block = 8;
         dim3 grid((N + warps_per_block - 1) / warps_per_block);
-        gemm_rows_kernel<TX, TW, TO, 8><<<grid, 256, 0, stream>>>(
-            (const TX*)X, (const TW*)W, bias, bias_dtype, (TO*)Y, M, N, K, ldx, ldy);
+        llb_launch(gemm_rows_kernel<TX, TW, TO, 8>, grid, dim3(256), 0, stream,
+                   (const TX*)X, (const TW*)W, bias, bias_dtype, (TO*)Y, M, N, K, ldx, ldy);
     } else {
         dim3 grid((N + 63) / 64, (M + 63) / 64);
-        gemm_tile_kernel<TX, TW, TO><<<grid, 256, 0, stream>>>(
-            (const TX*)X, (const TW*)W, bias, bias_dtype, (TO*)Y, M, N, K, ldx, ldy);
+        llb_launch(gemm_tile_kernel<TX, TW, TO>, grid, dim3(256), 0, stream,
+                   (const TX*)X, (const TW*)W, bias, bias_dtype, (TO*)Y, M, N, K, ldx, ldy);
     }
 }
 

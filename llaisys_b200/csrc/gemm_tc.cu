@@ -184,14 +184,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot_ptr;
 
+    // The weight does not depend on any earlier kernel of the step, so its first STAGES k-blocks are
+    // requested before the grid dependency resolves: while the predecessor is still running, this
+    // CTA's share of the weight is already on its way into shared memory.
+    const int prefetched = min(STAGES, kb1 - kb0);
+    if (warp == 0 && lane == 0) {
+        for (int i = 0; i < prefetched; ++i) {
+            uint32_t dst = base + i * S::STAGE_BYTES;
+            mbar_expect_tx(bar_full + 8 * i, S::STAGE_BYTES);
+            tma_load_2d(dst, &map_w, bar_full + 8 * i, (kb0 + i) * BK, m0, HINT_EVICT_FIRST);
+            if (DUAL) tma_load_2d(dst + S::A_BYTES, &map_w, bar_full + 8 * i, (kb0 + i) * BK, m0 + g.dual_offset, HINT_EVICT_FIRST);
+        }
+    }
+    llb_grid_dependency_sync();      // from here on memory written by earlier kernels is touched
+
     if (warp == 0) {
         if (lane == 0) {
-            // ---- producer: k-blocks kb0..kb1-1 into the ring
-            int issued = 0;
-            for (int kb = kb0; kb < kb1; ++kb, ++issued) {
+            // ---- producer: the activations of the prefetched k-blocks, then whole k-blocks into the ring
+            for (int i = 0; i < prefetched; ++i)
+                tma_load_2d(base + i * S::STAGE_BYTES + ACCS * S::A_BYTES, &map_x, bar_full + 8 * i, (kb0 + i) * BK, n0,
+                            HINT_EVICT_LAST);
+            int issued = prefetched;
+            for (int kb = kb0 + prefetched; kb < kb1; ++kb, ++issued) {
                 int s = issued % STAGES;
                 uint32_t round = issued / STAGES;
-                if (round > 0 && !mbar_wait(bar_empty + 8 * s, (round - 1) & 1, &s_abort)) {
+                if (!mbar_wait(bar_empty + 8 * s, (round - 1) & 1, &s_abort)) {
                     if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC_WAIT_EMPTY); }
                     break;
                 }
@@ -292,15 +309,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             if (s_last) {
                 __threadfence();
                 const float* all = g.scratch + (size_t)tile * g.splits * (ACCS * BN * BM);
+                // eight tokens at a time and four splits ahead, so that the loads overlap instead of
+                // each waiting for the one before; the sums still run in split order
                 if (row_ok)
-                    for (int j = 0; j < n_valid; ++j) {
-                        float a0 = 0.f, a1 = 0.f;
+                    for (int j0 = 0; j0 < n_valid; j0 += 8) {
+                        float a0[8], a1[8];
+#pragma unroll
+                        for (int jj = 0; jj < 8; ++jj) a0[jj] = a1[jj] = 0.f;
+#pragma unroll 4
                         for (int s = 0; s < g.splits; ++s) {
                             const float* p = all + (size_t)s * (ACCS * BN * BM);
-                            a0 += __ldcg(p + j * BM + tid);
-                            if (DUAL) a1 += __ldcg(p + (BN + j) * BM + tid);
+                            float v0[8], v1[8];
+#pragma unroll
+                            for (int jj = 0; jj < 8; ++jj) {
+                                bool in = j0 + jj < n_valid;
+                                v0[jj] = in ? __ldcg(p + (j0 + jj) * BM + tid) : 0.f;
+                                v1[jj] = (DUAL && in) ? __ldcg(p + (BN + j0 + jj) * BM + tid) : 0.f;
+                            }
+#pragma unroll
+                            for (int jj = 0; jj < 8; ++jj) {
+                                a0[jj] += v0[jj];
+                                a1[jj] += v1[jj];
+                            }
                         }
-                        finish(a0, a1, j);
+#pragma unroll
+                        for (int jj = 0; jj < 8; ++jj)
+                            if (j0 + jj < n_valid) finish(a0[jj], a1[jj], j0 + jj);
                     }
                 if (tid == 0) g.counters[tile] = 0;
             }
@@ -363,7 +397,7 @@ int get_map(const void* ptr, int rows, int cols, int ld, int box_rows, CUtensorM
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return (int)cudaErrorInvalidValue;
+    if (r != CUDA_SUCCESS) return -1000 - (int)r;          // tensor-map encoding refused: -(1000 + CUresult)
     if (cache.size() > 4096) cache.clear();
     cache.emplace(key, *out);
     return 0;
@@ -376,10 +410,10 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& g, dim3
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
+        if (e != cudaSuccess) return -2000 - (int)e;       // shared-memory opt-in refused: -(2000 + cudaError)
         configured = true;
     }
-    k<<<grid, THREADS, smem, stream>>>(mw, mx, g);
+    llb_launch(k, grid, dim3(THREADS), smem, stream, mw, mx, g);
     return llb_status();
 }
 

@@ -74,6 +74,7 @@ __device__ ArgMax block_argmax(const float* row, int V, ArgMax* red) {
 __global__ void __launch_bounds__(SB) argmax_kernel(const float* __restrict__ logits, long long ld,
                                                     int V, int* __restrict__ out) {
     __shared__ ArgMax red[32];
+    llb_grid_dependency_sync();
     ArgMax b = block_argmax(logits + (size_t)blockIdx.x * ld, V, red);
     if (threadIdx.x == 0) out[blockIdx.x] = b.i;
 }
@@ -81,7 +82,7 @@ __global__ void __launch_bounds__(SB) argmax_kernel(const float* __restrict__ lo
 LLB_API int llb_argmax(const float* logits, long long ld, int R, int V, int* out, cudaStream_t stream) {
     if (R == 0) return 0;
     if (V <= 0) return (int)cudaErrorInvalidValue;
-    argmax_kernel<<<R, SB, 0, stream>>>(logits, ld, V, out);
+    llb_launch(argmax_kernel, dim3(R), dim3(SB), 0, stream, logits, ld, V, out);
     return llb_status();
 }
 
@@ -132,6 +133,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, int V, int* __rest
     __shared__ unsigned long long sh_acc;
     const float* row = logits + (size_t)blockIdx.x * ld;
     const int tid = threadIdx.x;
+    llb_grid_dependency_sync();
 
     ArgMax top = block_argmax(row, V, red);
     if (top_k == 1 || temperature == 0.f) {
@@ -286,7 +288,7 @@ LLB_API int llb_sample(const float* logits, long long ld, int R, int V, int* out
                        const int* steps, cudaStream_t stream) {
     if (R == 0) return 0;
     if (V <= 0 || temperature < 0.f || !(top_p > 0.f)) return (int)cudaErrorInvalidValue;
-    sample_kernel<<<R, SB, 0, stream>>>(logits, ld, V, out, temperature, top_k, top_p, seed, keys, steps);
+    llb_launch(sample_kernel, dim3(R), dim3(SB), 0, stream, logits, ld, V, out, temperature, top_k, top_p, seed, keys, steps);
     return llb_status();
 }
 

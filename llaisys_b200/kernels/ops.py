@@ -61,6 +61,10 @@ def launch_count() -> int:
 def _check(rc: int, what: str, n: int = 1):
     global _launches
     _launches += n
+    if rc <= -2000:
+        raise KernelError(f"{what}: the kernel's shared-memory size was refused (CUDA error {-rc - 2000})")
+    if rc <= -1000:
+        raise KernelError(f"{what}: a tensor map could not be encoded (driver error {-rc - 1000})")
     if rc != 0:
         msg = _lib_basic().llb_error_string(rc)
         raise KernelError(f"{what}: CUDA error {rc} ({msg.decode() if msg else '?'})")
@@ -184,18 +188,28 @@ def _sm_count(device) -> int:
 
 
 def tc_plan(T: int, rows_out: int, K: int, sms: int, dual: bool = False):
-    """(tokens per tile, K splits) of a tensor-core launch: the smallest tile that holds the
-    tokens, and enough K splits to give every SM two CTAs when the weight has few row blocks
-    (decode), each split keeping at least four k-blocks of 64."""
+    """(tokens per tile, K splits) of a tensor-core launch.
+
+    The tile is the smallest that holds the tokens.  When the weight has fewer row blocks than
+    the device has SMs (decode), K is split so that more CTAs stream it; the number of splits
+    minimises a cost fitted to measurements on a B200 (microseconds):
+        k-blocks per CTA * 0.28  +  (2 + 0.025 * tile tokens * accumulators * splits  if split)
+    the first term being one CTA's streaming time, the second the fix-up of the partial tiles."""
     bn = 16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else 128 if T <= 128 else 256
     tiles = -(-rows_out // 128) * -(-T // bn)
     kblocks = -(-K // 64)
-    splits = max(1, min(kblocks // 4, (2 * sms) // tiles))
-    while splits > 1 and tiles * splits * (2 if dual else 1) * bn * 128 > _TC_SCRATCH_ELEMS:
-        splits -= 1
+    accs = 2 if dual else 1
+    best, best_cost = 1, kblocks * 0.28
+    if tiles < sms:
+        for s in range(2, max(2, kblocks // 2) + 1):
+            if tiles * s > 2 * sms or tiles * s * accs * bn * 128 > _TC_SCRATCH_ELEMS:
+                break
+            cost = -(-kblocks // s) * 0.28 + 2 + 0.025 * bn * accs * s
+            if cost < best_cost:
+                best, best_cost = s, cost
     if tiles > _TC_COUNTERS:
-        splits = 1
-    return bn, splits
+        best = 1
+    return bn, best
 
 
 def _tc_ok(x, weight, bias) -> bool:
@@ -269,7 +283,7 @@ class _MmaAttnParams(ctypes.Structure):
                 ("table_stride", c_int), ("ring", c_int), ("seq_start", c_void_p),
                 ("seq_len_before", c_void_p), ("nh", c_int), ("nkvh", c_int), ("window", c_int),
                 ("scale", c_float), ("all_from_cache", c_int), ("n_splits", c_int), ("part_o", c_void_p),
-                ("part_ml", c_void_p), ("err", c_void_p)]
+                ("part_ml", c_void_p)]
 
 
 MMA_ATTENTION = True                         # tests switch the tensor-core attention off to compare
@@ -318,7 +332,7 @@ def attention_prefill(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_sta
     if _mma_ok(qkv, dh):
         p = _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before, window,
                          scale, _MmaAttnParams)
-        p.all_from_cache, p.err = int(all_from_cache), _tc_resources(qkv.device)[2].data_ptr()
+        p.all_from_cache = int(all_from_cache)
         f = _fn(_mma_lib(dh), "llb_attn_mma_prefill", [_MmaAttnParams, c_int, c_int, c_void_p])
         _check(f(p, n_seqs, max_new, _stream()), "attention_prefill (tensor cores)")
         return out
@@ -345,7 +359,6 @@ def attention_decode(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_star
         p.n_splits, p.part_o, p.part_ml = n_splits, part_o.data_ptr(), part_ml.data_ptr()
         keep = (part_o, part_ml)
     if mma:
-        p.err = _tc_resources(qkv.device)[2].data_ptr()
         f = _fn(_mma_lib(dh), "llb_attn_mma_decode", [_MmaAttnParams, c_int, c_void_p])
         _check(f(p, n_seqs, _stream()), "attention_decode (tensor cores)", 2 if n_splits > 1 else 1)
     else:
