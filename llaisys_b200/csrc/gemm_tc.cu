@@ -475,3 +475,94 @@ LLB_API int llb_gemm_tc(const void* X, const void* W, const void* bias, int bias
     }
 #undef LLB_TC
 }
+
+// ------------------------------------------------------------------ allocation-free entry point
+// See gemm_tc_noalloc.h.  The scratch of the split launches lives in the device image.  In host
+// code the names below are host-side stand-ins, not device addresses, so the addresses are
+// looked up once per device with cudaGetSymbolAddress and passed to the kernel.
+#include "gemm_tc_noalloc.h"
+
+static __device__ __align__(256) float g_noalloc_scratch[LLB_NOALLOC_SCRATCH_FLOATS];
+static __device__ __align__(256) int g_noalloc_counters[LLB_NOALLOC_TILES];
+static __device__ __align__(256) int g_noalloc_err[64];
+
+namespace {
+
+struct NoAllocPtrs { float* scratch; int* counters; int* err; bool ready; };
+constexpr int NOALLOC_MAX_DEVICES = 64;
+NoAllocPtrs g_noalloc_ptrs[NOALLOC_MAX_DEVICES];
+std::mutex g_noalloc_mutex;
+
+// Device addresses of the built-in arrays on the current device; looked up on the first call there.
+int noalloc_setup(NoAllocPtrs* out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= NOALLOC_MAX_DEVICES) return LLB_NOALLOC_SETUP_FAILED;
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    NoAllocPtrs& p = g_noalloc_ptrs[dev];
+    if (!p.ready) {
+        void *s = nullptr, *c = nullptr, *e = nullptr;
+        if (cudaGetSymbolAddress(&s, g_noalloc_scratch) != cudaSuccess || cudaGetSymbolAddress(&c, g_noalloc_counters) != cudaSuccess ||
+            cudaGetSymbolAddress(&e, g_noalloc_err) != cudaSuccess || !s || !c || !e) {
+            cudaGetLastError();
+            return LLB_NOALLOC_SETUP_FAILED;
+        }
+        p.scratch = (float*)s;
+        p.counters = (int*)c;
+        p.err = (int*)e;
+        p.ready = true;
+    }
+    *out = p;
+    return 0;
+}
+
+// Like get_map, but encodes into caller storage every time: no cache, no heap.
+int encode_map_uncached(const void* ptr, int rows, int cols, int ld, int box_rows, CUtensorMap* out) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -1000 - (int)r;
+}
+
+}  // namespace
+
+int llb_gemm_tc_noalloc(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int y_dtype,
+                        int T, int N, int K, int ldx, int ldy, int bn, int splits, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || ldx % 8 || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return (int)cudaErrorInvalidValue;
+    if (y_dtype != LLB_F32 && y_dtype != LLB_BF16) return (int)cudaErrorInvalidValue;
+    if (bn != 16 && bn != 32 && bn != 64 && bn != 128 && bn != 256) return (int)cudaErrorInvalidValue;
+    const int kblocks = (K + BK - 1) / BK;
+    if (splits < 1) splits = 1;
+    if (splits > kblocks) splits = kblocks;
+    {
+        int chunk = (kblocks + splits - 1) / splits;
+        splits = (kblocks + chunk - 1) / chunk;
+    }
+    dim3 grid((N + BM - 1) / BM, (T + bn - 1) / bn, splits);
+    if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
+    const long long tiles = (long long)grid.x * grid.y;
+    if (splits > 1 && (tiles * splits * bn * BM > (long long)LLB_NOALLOC_SCRATCH_FLOATS || tiles > LLB_NOALLOC_TILES))
+        return LLB_NOALLOC_TOO_LARGE;
+    NoAllocPtrs ptrs;
+    int rc = noalloc_setup(&ptrs);
+    if (rc) return rc;
+    CUtensorMap mw, mx;
+    rc = encode_map_uncached(W, N, K, K, BM, &mw);
+    if (rc) return rc;
+    rc = encode_map_uncached(X, T, K, ldx, bn, &mx);
+    if (rc) return rc;
+    GemmArgs g{bias, bias_dtype, Y, y_dtype, T, N, K, ldy, 0, splits, ptrs.scratch, ptrs.counters, ptrs.err};
+    switch (bn) {
+        case 16: return launch<16, 6, false>(mw, mx, g, grid, stream);
+        case 32: return launch<32, 5, false>(mw, mx, g, grid, stream);
+        case 64: return launch<64, 4, false>(mw, mx, g, grid, stream);
+        case 128: return launch<128, 6, false>(mw, mx, g, grid, stream);
+        default: return launch<256, 4, false>(mw, mx, g, grid, stream);
+    }
+}
