@@ -14,7 +14,10 @@
 //
 //  * decode: a block owns up to 16 query heads that share one kv head, for one sequence and one
 //    slice of its key range; its four warps take 16 keys each of every tile and are merged at the
-//    end; slices are merged by llb_attn_mma_combine.
+//    end.  Up to eight slices form a thread-block cluster and are merged through distributed
+//    shared memory; more slices go through global memory and a second kernel.  The kernel can
+//    also do what would otherwise take a kernel before it: rotate the query heads and the new key
+//    (half-split rotary encoding) and append the new key and value to the cache.
 //  * prefill: a block owns 64 consecutive new tokens of one query head; each warp 16 of them.
 //
 // The only waits are cp.async.wait_group and __syncthreads, which cannot outlast the copies.
@@ -57,6 +60,14 @@ struct MmaAttnParams {
     int n_splits;           // decode
     float* part_o;          // decode: [B, nh, n_splits, DH]
     float* part_ml;         // decode: [B, nh, n_splits, 2]
+    // decode, optional fusions (null / 0 when not used)
+    const float* rope_cos;  // [rope_rows, DH/2]: rotate the query heads and the new key here (half-split pairs) and
+    const float* rope_sin;  //   append the new key and value to the cache, instead of in a kernel before this one
+    int rope_rows;
+    int append_new;         // the new token's key/value are not in the cache yet: take them from the packed projections
+                            // (rotating the key when rope_cos is set), use them, and write them to the cache
+    int cluster;            // the n_splits (<= 8) blocks of a (sequence, head group) are a thread-block cluster and merge
+                            // their key slices through distributed shared memory; part_o / part_ml are not used
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -134,18 +145,40 @@ __device__ __forceinline__ void zero_unfetched(uint8_t* stage_ptr, int tile, int
     __syncthreads();
 }
 
+// Elements d, d+1 of a head's vector after the half-split rotation by the angles of one position
+// (cs, sn: that position's DH/2 cosines and sines), rounded to bfloat16 like the separate kernel does.
+__device__ __forceinline__ uint32_t rotated_pair(const bf16* x, int d, const float* cs, const float* sn) {
+    constexpr int HALF = DH / 2;
+    float r[2];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        int i = d + e;
+        if (i < HALF) r[e] = to_f32(x[i]) * cs[i] - to_f32(x[i + HALF]) * sn[i];
+        else r[e] = to_f32(x[i]) * cs[i - HALF] + to_f32(x[i - HALF]) * sn[i - HALF];
+    }
+    return pack_bf16(r[0], r[1]);
+}
+
 // Query rows as A fragments: q_of(row) gives the pointer to that row's DH elements or nullptr.
 template <typename F>
-__device__ __forceinline__ void load_q(uint32_t (&qf)[KSTEPS][4], F q_of, int lane) {
+__device__ __forceinline__ void load_q(uint32_t (&qf)[KSTEPS][4], F q_of, int lane, const float* cs = nullptr,
+                                       const float* sn = nullptr) {
     const bf16* r0 = q_of(lane >> 2);
     const bf16* r1 = q_of((lane >> 2) + 8);
     int c = (lane & 3) * 2;
 #pragma unroll
     for (int kk = 0; kk < KSTEPS; ++kk) {
-        qf[kk][0] = r0 ? *reinterpret_cast<const uint32_t*>(r0 + kk * 16 + c) : 0u;
-        qf[kk][1] = r1 ? *reinterpret_cast<const uint32_t*>(r1 + kk * 16 + c) : 0u;
-        qf[kk][2] = r0 ? *reinterpret_cast<const uint32_t*>(r0 + kk * 16 + 8 + c) : 0u;
-        qf[kk][3] = r1 ? *reinterpret_cast<const uint32_t*>(r1 + kk * 16 + 8 + c) : 0u;
+        if (cs) {
+            qf[kk][0] = r0 ? rotated_pair(r0, kk * 16 + c, cs, sn) : 0u;
+            qf[kk][1] = r1 ? rotated_pair(r1, kk * 16 + c, cs, sn) : 0u;
+            qf[kk][2] = r0 ? rotated_pair(r0, kk * 16 + 8 + c, cs, sn) : 0u;
+            qf[kk][3] = r1 ? rotated_pair(r1, kk * 16 + 8 + c, cs, sn) : 0u;
+        } else {
+            qf[kk][0] = r0 ? *reinterpret_cast<const uint32_t*>(r0 + kk * 16 + c) : 0u;
+            qf[kk][1] = r1 ? *reinterpret_cast<const uint32_t*>(r1 + kk * 16 + c) : 0u;
+            qf[kk][2] = r0 ? *reinterpret_cast<const uint32_t*>(r0 + kk * 16 + 8 + c) : 0u;
+            qf[kk][3] = r1 ? *reinterpret_cast<const uint32_t*>(r1 + kk * 16 + 8 + c) : 0u;
+        }
     }
 }
 
@@ -247,14 +280,17 @@ __device__ __forceinline__ Ring make_ring(uint8_t* smem_raw) {
     r.ptr = smem_raw + (r.base - raw);
     return r;
 }
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 128;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 16 * (DH + 8) * 2 + 128;     // ring, staged queries, alignment slack
 
 // ------------------------------------------------------------------ decode
 __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     Ring ring = make_ring(smem_raw);
-    llb_grid_dependency_sync();
+    // With append_new nothing this kernel fetches from the cache was written by the kernels just before it
+    // (the new token's row comes from the projections), and the step's description was copied before the
+    // step's first kernel: the first tiles are requested before the grid dependency resolves.
+    if (!p.append_new) llb_grid_dependency_sync();
 
     const int b = blockIdx.z;
     const int G = p.nh / p.nkvh;
@@ -262,8 +298,13 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
     const int kvh = blockIdx.y / chunks, chunk = blockIdx.y - kvh * chunks;
     const int head0 = kvh * G + chunk * 16, n_heads = min(16, G - chunk * 16);
     const int tok = p.seq_start[b];
-    const int pos = p.seq_len_before[b];                 // the new token's position; it is already cached
+    const int pos = p.seq_len_before[b];                 // the new token's position
     const int key_lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    // with append_new the new token's key and value are not in the cache: tiles are fetched up to pos - 1 and
+    // the block that owns the last tile puts the new row there itself
+    const int fetch_hi = p.append_new ? pos - 1 : pos;
+    const float* cs = p.rope_cos ? p.rope_cos + (size_t)min(pos, p.rope_rows - 1) * (DH / 2) : nullptr;
+    const float* sn = p.rope_cos ? p.rope_sin + (size_t)min(pos, p.rope_rows - 1) * (DH / 2) : nullptr;
     int tile_lo = key_lo / TILE, tile_hi = pos / TILE + 1;
     {
         int n = tile_hi - tile_lo, per = (n + p.n_splits - 1) / p.n_splits;
@@ -275,13 +316,35 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
     Source src{p.kpool, p.vpool, nullptr, nullptr, p.page_table + (size_t)b * p.table_stride,
                p.ring, p.nkvh, kvh, 0, 0, 0, false};
     for (int i = 0; i < STAGES; ++i) {
-        if (i < n_tiles) issue_tile(src, tile_lo + i, key_lo, pos, ring.stage(i), tid);
+        if (i < n_tiles) issue_tile(src, tile_lo + i, key_lo, fetch_hi, ring.stage(i), tid);
         cp_async_commit();                                 // one group per stage, empty or not
     }
+    if (p.append_new) llb_grid_dependency_sync();          // the projections are read from here on
 
+    // the query heads of this block, rotated if asked for, staged in shared memory behind the ring
+    bf16* qs = reinterpret_cast<bf16*>(ring.ptr + STAGES * STAGE_BYTES);       // [16][DH + 8]
+    {
+        constexpr int HALF = DH / 2;
+        const bf16* qg = p.q + (size_t)tok * p.row_stride + (size_t)head0 * DH;
+        for (int i = tid; i < 16 * HALF; i += THREADS) {
+            int r = i / HALF, j = i - r * HALF;
+            float a = 0.f, c2 = 0.f;
+            if (r < n_heads) {
+                a = to_f32(qg[r * DH + j]);
+                c2 = to_f32(qg[r * DH + j + HALF]);
+                if (cs) {
+                    float co = cs[j], si = sn[j], ra = a * co - c2 * si, rb = c2 * co + a * si;
+                    a = ra;
+                    c2 = rb;
+                }
+            }
+            qs[r * (DH + 8) + j] = __float2bfloat16_rn(a);
+            qs[r * (DH + 8) + j + HALF] = __float2bfloat16_rn(c2);
+        }
+    }
+    __syncthreads();
     uint32_t qf[KSTEPS][4];
-    load_q(qf, [&](int r) -> const bf16* {
-        return r < n_heads ? p.q + (size_t)tok * p.row_stride + (size_t)(head0 + r) * DH : nullptr; }, lane);
+    load_q(qf, [&](int r) -> const bf16* { return qs + r * (DH + 8); }, lane);
     float o[DTILES][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 #pragma unroll
     for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
@@ -290,10 +353,28 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
     for (int i = 0; i < n_tiles; ++i) {
         cp_async_wait<STAGES - 1>();                       // this thread's copies of tile i have landed
         __syncthreads();                                   // ... and everyone else's
+        if (p.append_new && tile_lo + i == pos / TILE) {
+            // the new token's row: from the packed projections into this tile (and, once per kv head, into the cache)
+            const bf16* kn = p.k_new + (size_t)tok * p.row_stride + (size_t)kvh * DH;
+            const bf16* vn = p.v_new + (size_t)tok * p.row_stride + (size_t)kvh * DH;
+            uint8_t* krow = ring.stage_ptr(i) + (pos % TILE) * ROW_STRIDE;
+            size_t goff = paged_row(src.table, p.ring, pos, kvh, p.nkvh, DH);
+            for (int d = tid * 2; d < DH; d += THREADS * 2) {
+                uint32_t kk = cs ? rotated_pair(kn, d, cs, sn) : *reinterpret_cast<const uint32_t*>(kn + d);
+                uint32_t vv = *reinterpret_cast<const uint32_t*>(vn + d);
+                *reinterpret_cast<uint32_t*>(krow + d * 2) = kk;
+                *reinterpret_cast<uint32_t*>(krow + TILE_BYTES + d * 2) = vv;
+                if (chunk == 0) {
+                    *reinterpret_cast<uint32_t*>(const_cast<bf16*>(p.kpool) + goff + d) = kk;
+                    *reinterpret_cast<uint32_t*>(const_cast<bf16*>(p.vpool) + goff + d) = vv;
+                }
+            }
+            __syncthreads();
+        }
         zero_unfetched(ring.stage_ptr(i), tile_lo + i, key_lo, pos, tid);
         tile_step<2>(qf, o, m, l, ring.stage(i), warp * 16, (tile_lo + i) * TILE, key_lo, pos, key_lo, pos, scale_log2, lane);
         __syncthreads();                                   // the stage is free
-        if (i + STAGES < n_tiles) issue_tile(src, tile_lo + i + STAGES, key_lo, pos, ring.stage(i + STAGES), tid);
+        if (i + STAGES < n_tiles) issue_tile(src, tile_lo + i + STAGES, key_lo, fetch_hi, ring.stage(i + STAGES), tid);
         cp_async_commit();
     }
     cp_async_wait<0>();
@@ -319,6 +400,9 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
         }
     }
     __syncthreads();
+    // merged over the four warps: fin_ml [16][2], fin_o [16][DH] (kept in shared memory for the cluster merge)
+    float* fin_ml = sm_o + 4 * 16 * DH;
+    float* fin_o = fin_ml + 16 * 2;
     for (int i = tid; i < n_heads * DH; i += THREADS) {
         int r = i / DH, d = i - r * DH;
         float M = -INFINITY;
@@ -337,15 +421,62 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
         int head = head0 + r;
         if (p.n_splits == 1) {
             p.out[(size_t)tok * p.nh * DH + (size_t)head * DH + d] = __float2bfloat16_rn(acc / L);
+        } else if (p.cluster) {
+            fin_o[r * DH + d] = acc;
+            if (d == 0) {
+                fin_ml[r * 2] = M;                    // base-2 logarithmic scale
+                fin_ml[r * 2 + 1] = L;
+            }
         } else {
             size_t slot = ((size_t)b * p.nh + head) * p.n_splits + blockIdx.x;
             p.part_o[slot * DH + d] = acc;
             if (d == 0) {
-                p.part_ml[slot * 2] = M;              // base-2 logarithmic scale
+                p.part_ml[slot * 2] = M;
                 p.part_ml[slot * 2 + 1] = L;
             }
         }
     }
+    if (p.n_splits == 1 || !p.cluster) return;
+
+    // ---- cluster merge of the key slices: block `rank` produces one share of the (head, dim) outputs
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    {
+        const int S = p.n_splits;                                  // cluster size, at most 8
+        uint32_t rank;
+        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+        const int total = n_heads * DH, share = (total + S - 1) / S;
+        const uint32_t ml_addr = smem_u32(fin_ml), o_addr = smem_u32(fin_o);
+        for (int i = (int)rank * share + tid; i < min(total, ((int)rank + 1) * share); i += THREADS) {
+            int r = i / DH, d = i - r * DH;
+            float ms[8], ls[8], os[8];
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) {
+                ms[sp] = -INFINITY;
+                ls[sp] = os[sp] = 0.f;
+                if (sp < S) {
+                    uint32_t ra;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(ml_addr + (uint32_t)(r * 8)), "r"(sp));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ms[sp]) : "r"(ra) : "memory");
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ls[sp]) : "r"(ra + 4) : "memory");
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(o_addr + (uint32_t)((r * DH + d) * 4)), "r"(sp));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(os[sp]) : "r"(ra) : "memory");
+                }
+            }
+            float M = -INFINITY;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) M = fmaxf(M, ms[sp]);
+            float L = 0.f, acc = 0.f;
+#pragma unroll
+            for (int sp = 0; sp < 8; ++sp) {
+                float f = ms[sp] == -INFINITY ? 0.f : exp2f(ms[sp] - M);
+                L += ls[sp] * f;
+                acc += os[sp] * f;
+            }
+            p.out[(size_t)tok * p.nh * DH + (size_t)(head0 + r) * DH + d] = __float2bfloat16_rn(acc / L);
+        }
+    }
+    // no block may leave while another still reads its shared memory
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 __global__ void attn_mma_combine_kernel(bf16* __restrict__ out, const float* __restrict__ part_o,
@@ -470,15 +601,40 @@ LLB_API int llb_attn_mma_prefill(MmaAttnParams p, int B, int max_new, cudaStream
 
 LLB_API int llb_attn_mma_decode(MmaAttnParams p, int B, cudaStream_t stream) {
     if (B == 0) return 0;
-    if (!aligned_ok(p) || p.n_splits < 1) return (int)cudaErrorInvalidValue;
+    if (!aligned_ok(p) || p.n_splits < 1 || p.n_splits > 64) return (int)cudaErrorInvalidValue;
+    if (p.cluster && p.n_splits > 8) return (int)cudaErrorInvalidValue;
     int G = p.nh / p.nkvh;
     dim3 grid(p.n_splits, p.nkvh * ((G + 15) / 16), B);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
     int rc = configure<1>(attn_mma_decode_kernel);
     if (rc) return rc;
-    llb_launch(attn_mma_decode_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, p);
+    if (p.cluster && p.n_splits > 1) {
+        llb_prefer_max_shared((const void*)attn_mma_decode_kernel);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(THREADS);
+        cfg.dynamicSmemBytes = SMEM_BYTES;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        int n_attr = 0;
+        if (llb_pdl_enabled()) {
+            attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+            ++n_attr;
+        }
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = (unsigned)p.n_splits;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = 1;
+        ++n_attr;
+        cfg.attrs = attr;
+        cfg.numAttrs = n_attr;
+        cudaLaunchKernelEx(&cfg, attn_mma_decode_kernel, p);
+    } else {
+        llb_launch(attn_mma_decode_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, p);
+    }
     rc = llb_status();
-    if (rc == 0 && p.n_splits > 1) {
+    if (rc == 0 && p.n_splits > 1 && !p.cluster) {
         llb_launch(attn_mma_combine_kernel, dim3(p.nh, B), dim3(128), 0, stream, p.out, p.part_o, p.part_ml, p.seq_start, p.nh, p.n_splits);
         rc = llb_status();
     }

@@ -33,43 +33,88 @@ LLB_API int llb_embedding(float* out, const void* table, int table_dtype, const 
 // ------------------------------------------------------------------ residual add + RMSNorm
 // Row r of the output is norm(residual[src] + sum_p delta[p][src]) with src = rows ? rows[r] : r.
 // When write_back is set the summed row replaces residual[src] (never together with `rows`).
-template <typename TD, typename TW, typename TO>
-__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta,
-                                   int n_part, size_t part_stride, const TW* __restrict__ weight,
-                                   TO* __restrict__ out, const int* __restrict__ rows, int H,
-                                   float eps, int write_back) {
-    extern __shared__ float rowbuf[];          // H floats
-    __shared__ float red[32];
+template <typename TD, typename TW, typename TO, int PER>     // PER > 0: H <= PER * 256 and the row lives in registers
+__global__ void __launch_bounds__(256)
+add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, int n_part, size_t part_stride,
+                   const TW* __restrict__ weight, TO* __restrict__ out, const int* __restrict__ rows, int H,
+                   float eps, int write_back) {
+    extern __shared__ float rowbuf[];          // H floats when PER == 0
+    __shared__ float red[8];
+    const int r = blockIdx.x, tid = threadIdx.x;
+    float x[PER > 0 ? PER : 1], w[PER > 0 ? PER : 1];
+    if (PER > 0) {                             // the norm weight depends on no earlier kernel: fetch it first
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            int j = tid + i * 256;
+            w[i] = (j < H && out) ? to_f32(weight[j]) : 0.f;
+        }
+    }
     llb_grid_dependency_sync();
-    int r = blockIdx.x;
-    size_t src = rows ? (size_t)rows[r] : (size_t)r;
+    const size_t src = rows ? (size_t)rows[r] : (size_t)r;
     float* res = residual + src * H;
     float ss = 0.f;
-    for (int j = threadIdx.x; j < H; j += blockDim.x) {
-        float x = res[j];
-        if (delta) {
-            float d = 0.f;
-            for (int p = 0; p < n_part; ++p) d += to_f32(delta[p * part_stride + src * H + j]);
-            x += d;
-            if (write_back) res[j] = x;
+    if (PER > 0) {
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            int j = tid + i * 256;
+            x[i] = j < H ? res[j] : 0.f;
         }
-        rowbuf[j] = x;
-        ss += x * x;
+        if (delta) {
+            // the partial sums are added to one another first, then to the residual, as in the general path
+            float d[PER > 0 ? PER : 1];
+#pragma unroll
+            for (int i = 0; i < PER; ++i) d[i] = 0.f;
+            for (int p = 0; p < n_part; ++p) {
+#pragma unroll
+                for (int i = 0; i < PER; ++i) {
+                    int j = tid + i * 256;
+                    if (j < H) d[i] += to_f32(delta[p * part_stride + src * H + j]);
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < PER; ++i) x[i] += d[i];
+            if (write_back) {
+#pragma unroll
+                for (int i = 0; i < PER; ++i) {
+                    int j = tid + i * 256;
+                    if (j < H) res[j] = x[i];
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < PER; ++i) ss += x[i] * x[i];
+    } else {
+        for (int j = tid; j < H; j += 256) {
+            float v = res[j];
+            if (delta) {
+                float d = 0.f;
+                for (int p = 0; p < n_part; ++p) d += to_f32(delta[p * part_stride + src * H + j]);
+                v += d;
+                if (write_back) res[j] = v;
+            }
+            rowbuf[j] = v;
+            ss += v * v;
+        }
     }
     ss = warp_sum(ss);
-    int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-    if (lane == 0) red[w] = ss;
+    const int lane = tid & 31, wp = tid >> 5;
+    if (lane == 0) red[wp] = ss;
     __syncthreads();
-    if (w == 0) {
-        float v = lane < (blockDim.x >> 5) ? red[lane] : 0.f;
-        v = warp_sum(v);
-        if (lane == 0) red[0] = v;
-    }
-    __syncthreads();
-    float inv = 1.0f / sqrtf(red[0] / (float)H + eps);
-    if (out)
-        for (int j = threadIdx.x; j < H; j += blockDim.x)
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float inv = 1.0f / sqrtf(tot / (float)H + eps);
+    if (!out) return;
+    if (PER > 0) {
+#pragma unroll
+        for (int i = 0; i < PER; ++i) {
+            int j = tid + i * 256;
+            if (j < H) out[(size_t)r * H + j] = from_f32<TO>(x[i] * w[i] * inv);
+        }
+    } else {
+        for (int j = tid; j < H; j += 256)
             out[(size_t)r * H + j] = from_f32<TO>(rowbuf[j] * to_f32(weight[j]) * inv);
+    }
 }
 
 template <typename TD, typename TW>
@@ -78,10 +123,15 @@ static int add_rmsnorm_out(float* residual, const void* delta, int n_part, size_
                            int H, float eps, int write_back, cudaStream_t stream) {
     size_t smem = (size_t)H * sizeof(float);
     LLB_DISPATCH_DTYPE(out_dtype, TO, {
-        auto k = add_rmsnorm_kernel<TD, TW, TO>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        llb_launch(k, dim3(R), dim3(256), smem, stream, residual, (const TD*)delta, n_part, part_stride,
-                   (const TW*)weight, (TO*)out, rows, H, eps, write_back);
+        if (H <= 8 * 256) {
+            llb_launch(add_rmsnorm_kernel<TD, TW, TO, 8>, dim3(R), dim3(256), 0, stream, residual, (const TD*)delta,
+                       n_part, part_stride, (const TW*)weight, (TO*)out, rows, H, eps, write_back);
+        } else {
+            auto k = add_rmsnorm_kernel<TD, TW, TO, 0>;
+            if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            llb_launch(k, dim3(R), dim3(256), smem, stream, residual, (const TD*)delta, n_part, part_stride,
+                       (const TW*)weight, (TO*)out, rows, H, eps, write_back);
+        }
     });
     return llb_status();
 }

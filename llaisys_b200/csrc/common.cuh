@@ -70,8 +70,21 @@ static inline bool llb_pdl_enabled() {
     return v != 0;
 }
 
+// All kernels ask for the same split of the SM's L1/shared memory (all of it as shared memory), so
+// that an SM never has to drain and reconfigure between two kernels of a step.
+static inline void llb_prefer_max_shared(const void* kernel) {
+    static const void* seen[256];
+    static int n_seen = 0;
+    for (int i = 0; i < n_seen; ++i)
+        if (seen[i] == kernel) return;
+    if (getenv("LLAISYS_CARVEOUT") && getenv("LLAISYS_CARVEOUT")[0] == '0') return;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+    if (n_seen < 256) seen[n_seen++] = kernel;
+}
+
 template <typename... P, typename... A>
 static inline void llb_launch(void (*kernel)(P...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, A... args) {
+    llb_prefer_max_shared((const void*)kernel);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;

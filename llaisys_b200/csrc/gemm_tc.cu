@@ -14,10 +14,15 @@
 //   -> tcgen05.mma issued by one thread, accumulator in tensor memory
 //   -> tcgen05.ld by all four warps -> bias -> transposed store to Y.
 //
-// With `splits` > 1 the K range is divided over gridDim.z CTAs.  Each writes its float32 partial
-// tile to `scratch`; the CTA that arrives last at the tile's counter adds the partials in split
-// order (so the sum does not depend on arrival order), applies the bias and stores.  Counters
-// return to zero, so the same scratch serves every launch of a stream.
+// With `splits` > 1 the K range is divided over gridDim.z CTAs, and their float32 partial tiles
+// are added in split order (so the sum does not depend on arrival order) in one of two ways:
+//   * cluster (splits 2, 4 or 8, tiles up to 128 tokens): the CTAs of a tile form a thread-block
+//     cluster; each leaves its partial tile in its own shared memory, and after a cluster
+//     barrier each adds one slice of the rows of all partials through distributed shared
+//     memory, applies the bias and stores.  No global memory round trip.
+//   * scratch (any split count): each CTA writes its partial tile to `scratch`; the CTA that
+//     arrives last at the tile's counter adds them and stores.  Counters return to zero, so the
+//     same scratch serves every launch of a stream.
 //
 // With DUAL the CTA multiplies two 128-row weight blocks (rows m and m + dual_offset: the gate
 // and up rows of a fused [2I, K] matrix) into two accumulators and stores
@@ -130,6 +135,7 @@ struct GemmArgs {
     int T, N, K, ldy;
     int dual_offset;       // DUAL: rows between the gate block and the up block of W
     int splits;
+    int cluster;           // 1: the splits of a tile are a thread-block cluster and reduce through shared memory
     float* scratch;        // [tiles][splits][accs][BN][BM] float32
     int* counters;         // [tiles], zero between launches
     int* err;
@@ -262,18 +268,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int m = m0 + tid;                                   // this thread's weight row (output column)
     const int n_valid = min(BN, g.T - n0);
     const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
-    const int n_out = DUAL ? g.dual_offset : g.N;             // DUAL: the output has I columns
     const bool row_ok = m < (DUAL ? g.dual_offset : g.N);
 
-    auto finish = [&](float acc0, float acc1, int j) {
+    auto finish_at = [&](float acc0, float acc1, int j, int row) {
         float v = acc0;
         if (DUAL) v = acc1 * (acc0 / (1.0f + __expf(-acc0)));
-        if (g.bias) v += g.bias_dtype == LLB_F32 ? ((const float*)g.bias)[m] : to_f32(((const bf16*)g.bias)[m]);
-        size_t o = (size_t)(n0 + j) * g.ldy + m;
+        if (g.bias) v += g.bias_dtype == LLB_F32 ? ((const float*)g.bias)[row] : to_f32(((const bf16*)g.bias)[row]);
+        size_t o = (size_t)(n0 + j) * g.ldy + row;
         if (g.y_dtype == LLB_F32) ((float*)g.Y)[o] = v;
         else ((bf16*)g.Y)[o] = __float2bfloat16_rn(v);
     };
-    (void)n_out;
+    auto finish = [&](float acc0, float acc1, int j) { finish_at(acc0, acc1, j, m); };
 
     if (!aborted) {
         if (g.splits == 1) {
@@ -286,6 +291,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         if (c + j < n_valid) finish(v0[j], DUAL ? v1[j] : 0.f, c + j);
+            }
+        } else if (g.cluster) {
+            // this CTA's partial tile into its own shared memory (the ring is idle now): [acc][token][row]
+            float* stg = reinterpret_cast<float*>(gen_base);
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                float v0[16], v1[16];
+                tmem_ld16(lane_addr + c, v0);
+                if (DUAL) tmem_ld16(lane_addr + BN + c, v1);
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                    if (c + j < n_valid) {
+                        stg[(c + j) * BM + tid] = v0[j];
+                        if (DUAL) stg[(BN + c + j) * BM + tid] = v1[j];
+                    }
             }
         } else {
             const int tile = blockIdx.y * gridDim.x + blockIdx.x;
@@ -339,6 +359,53 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (tid == 0) g.counters[tile] = 0;
             }
         }
+    }
+    if (g.cluster && g.splits > 1) {
+        // Every CTA of the cluster passes both barriers, whether it gave up or not.
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (!aborted) {
+            uint32_t rank;
+            asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+            const int S_ = g.splits, R = BM / S_;               // this CTA adds rows [rank * R, rank * R + R)
+            const int row = (int)rank * R + (tid % R), tg = tid / R;
+            const int mm = m0 + row;
+            const bool ok2 = mm < (DUAL ? g.dual_offset : g.N);
+            // four tokens at a time with all their remote loads issued before the first is used;
+            // each token's partials are still added in split order
+            for (int j0 = tg; j0 < n_valid; j0 += 4 * S_) {
+                float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
+                float v0[4][8], v1[4][8];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const int j = j0 + u * S_;
+                    const uint32_t l0 = base + (uint32_t)((j * BM + row) * 4), l1 = base + (uint32_t)(((BN + j) * BM + row) * 4);
+#pragma unroll
+                    for (int s = 0; s < 8; ++s) {
+                        v0[u][s] = v1[u][s] = 0.f;
+                        if (s < S_ && j < n_valid) {
+                            uint32_t r0;
+                            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r0) : "r"(l0), "r"(s));
+                            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v0[u][s]) : "r"(r0) : "memory");
+                            if (DUAL) {
+                                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r0) : "r"(l1), "r"(s));
+                                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v1[u][s]) : "r"(r0) : "memory");
+                            }
+                        }
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+#pragma unroll
+                    for (int s = 0; s < 8; ++s) {
+                        a0[u] += v0[u][s];
+                        a1[u] += v1[u][s];
+                    }
+                    if (ok2 && j0 + u * S_ < n_valid) finish_at(a0[u], a1[u], j0 + u * S_, mm);
+                }
+            }
+        }
+        // no CTA may leave while another still reads its shared memory
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -413,7 +480,29 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& g, dim3
         if (e != cudaSuccess) return -2000 - (int)e;       // shared-memory opt-in refused: -(2000 + cudaError)
         configured = true;
     }
-    llb_launch(k, grid, dim3(THREADS), smem, stream, mw, mx, g);
+    llb_prefer_max_shared((const void*)k);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (llb_pdl_enabled()) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    if (g.cluster && g.splits > 1) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = 1;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = (unsigned)g.splits;
+        ++n_attr;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    cudaLaunchKernelEx(&cfg, k, mw, mx, g);
     return llb_status();
 }
 
@@ -431,10 +520,11 @@ LLB_API long long llb_gemm_tc_scratch_elems(int T, int N, int bn, int splits, in
 
 // X [T, K] bf16 with row stride ldx; W [N, K] bf16 dense ([2 * dual_offset, K] when dual_offset > 0,
 // giving Y [T, dual_offset]); bias bf16/f32 or null; Y bf16 or f32 with row stride ldy.
-// bn: tokens per tile (16, 32, 64, 128, 256).  Requirements: K and ldx multiples of 8, X and W 16-byte
+// bn: tokens per tile (16, 32, 64, 128, 256).  cluster: reduce the splits through a thread-block cluster where
+// that applies (splits 2, 4 or 8 and bn <= 128), else through `scratch`.  Requirements: K and ldx multiples of 8, X and W 16-byte
 // aligned.  Returns 0, a cudaError, or cudaErrorInvalidValue for a shape it does not take.
 LLB_API int llb_gemm_tc(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int y_dtype,
-                        int T, int N, int K, int ldx, int ldy, int bn, int splits, int dual_offset,
+                        int T, int N, int K, int ldx, int ldy, int bn, int splits, int cluster, int dual_offset,
                         float* scratch, long long scratch_elems, int* counters, int n_counters, int* err,
                         cudaStream_t stream) {
     if (T <= 0 || N <= 0) return 0;
@@ -452,7 +542,9 @@ LLB_API int llb_gemm_tc(const void* X, const void* W, const void* bias, int bias
     }
     dim3 grid((rows_out + BM - 1) / BM, (T + bn - 1) / bn, splits);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
-    if (splits > 1) {
+    if (cluster && !(splits == 2 || splits == 4 || splits == 8) ) cluster = 0;
+    if (cluster && bn > 128) cluster = 0;
+    if (splits > 1 && !cluster) {
         long long need = llb_gemm_tc_scratch_elems(T, rows_out, bn, splits, dual);
         if (!scratch || !counters || need > scratch_elems || (long long)grid.x * grid.y > n_counters)
             return (int)cudaErrorInvalidValue;
@@ -462,7 +554,7 @@ LLB_API int llb_gemm_tc(const void* X, const void* W, const void* bias, int bias
     if (rc) return rc;
     rc = get_map(X, T, K, ldx, bn, &mx);
     if (rc) return rc;
-    GemmArgs g{bias, bias_dtype, Y, y_dtype, T, N, K, ldy, dual_offset, splits, scratch, counters, err};
+    GemmArgs g{bias, bias_dtype, Y, y_dtype, T, N, K, ldy, dual_offset, splits, cluster, scratch, counters, err};
 #define LLB_TC(BN_, ST_, STD_) \
     case BN_: return dual ? launch<BN_, STD_, true>(mw, mx, g, grid, stream) : launch<BN_, ST_, false>(mw, mx, g, grid, stream)
     switch (bn) {
@@ -557,7 +649,7 @@ int llb_gemm_tc_noalloc(const void* X, const void* W, const void* bias, int bias
     if (rc) return rc;
     rc = encode_map_uncached(X, T, K, ldx, bn, &mx);
     if (rc) return rc;
-    GemmArgs g{bias, bias_dtype, Y, y_dtype, T, N, K, ldy, 0, splits, ptrs.scratch, ptrs.counters, ptrs.err};
+    GemmArgs g{bias, bias_dtype, Y, y_dtype, T, N, K, ldy, 0, splits, 0, ptrs.scratch, ptrs.counters, ptrs.err};
     switch (bn) {
         case 16: return launch<16, 6, false>(mw, mx, g, grid, stream);
         case 32: return launch<32, 5, false>(mw, mx, g, grid, stream);

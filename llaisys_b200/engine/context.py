@@ -100,4 +100,9 @@ class StepContext:
         step's shape alone, so a captured step stays valid as sequences grow)."""
         pages = max(self.widths) if self.widths else 1
         want = -(-2 * self.sm_count // max(1, self.n_seqs * n_kv_heads))
-        return max(1, min(want, pages, 64))
+        splits = max(1, min(want, pages, 64))
+        # up to eight slices merge inside a thread-block cluster, which is cheaper than a second kernel:
+        # prefer that while a block then still has at most sixteen pages to walk
+        if splits > 8 and pages <= 8 * 16:
+            splits = 8
+        return splits

@@ -187,28 +187,34 @@ def _sm_count(device) -> int:
     return torch.cuda.get_device_properties(device).multi_processor_count
 
 
+_TC_STAGES = {False: {16: 6, 32: 5, 64: 4, 128: 6, 256: 4}, True: {16: 3, 32: 3, 64: 4, 128: 4, 256: 3}}
+
+
 def tc_plan(T: int, rows_out: int, K: int, sms: int, dual: bool = False):
     """(tokens per tile, K splits) of a tensor-core launch.
 
     The tile is the smallest that holds the tokens.  When the weight has fewer row blocks than
-    the device has SMs (decode), K is split so that more CTAs stream it; the number of splits
-    minimises a cost fitted to measurements on a B200 (microseconds):
-        k-blocks per CTA * 0.28  +  (2 + 0.025 * tile tokens * accumulators * splits  if split)
-    the first term being one CTA's streaming time, the second the fix-up of the partial tiles."""
+    the device can run CTAs (decode), K is split 2, 4 or 8 ways over a thread-block cluster that
+    reduces through shared memory.  The split minimises a cost fitted to measurements on a B200
+    (microseconds): k-blocks per CTA times 0.0155 per KB of a pipeline stage, plus, when split,
+    1.2 + 0.0015 * tile tokens * accumulators * splits for the cluster reduction; the CTAs must
+    all be resident at once (two per SM while a CTA's shared memory stays under 113 KB; with one
+    per SM, clusters of eight fill a GPC unevenly, so fewer CTAs are allowed)."""
     bn = 16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else 128 if T <= 128 else 256
     tiles = -(-rows_out // 128) * -(-T // bn)
     kblocks = -(-K // 64)
     accs = 2 if dual else 1
-    best, best_cost = 1, kblocks * 0.28
-    if tiles < sms:
-        for s in range(2, max(2, kblocks // 2) + 1):
-            if tiles * s > 2 * sms or tiles * s * accs * bn * 128 > _TC_SCRATCH_ELEMS:
+    stage_kb = accs * 16 + bn / 8
+    two_per_sm = stage_kb * _TC_STAGES[dual][bn] <= 112
+    capacity = (sms * 2 * 280) // 296 if two_per_sm else (sms * 112) // 148
+    best, best_cost = 1, kblocks * stage_kb * 0.0155
+    if bn <= 128:
+        for s in (2, 4, 8):
+            if s > kblocks // 2 or tiles * s > capacity:
                 break
-            cost = -(-kblocks // s) * 0.28 + 2 + 0.025 * bn * accs * s
+            cost = -(-kblocks // s) * stage_kb * 0.0155 + 1.2 + 0.0015 * bn * accs * s
             if cost < best_cost:
                 best, best_cost = s, cost
-    if tiles > _TC_COUNTERS:
-        best = 1
     return bn, best
 
 
@@ -221,12 +227,14 @@ def _gemm_tc(x, weight, bias, out, dual_offset=0, plan=None):
     M, K = x.shape
     N = weight.shape[0]
     scratch, counters, err = _tc_resources(x.device)
-    bn, splits = plan or tc_plan(M, dual_offset or N, K, _sm_count(x.device), bool(dual_offset))
+    plan = plan or tc_plan(M, dual_offset or N, K, _sm_count(x.device), bool(dual_offset))
+    bn, splits = plan[0], plan[1]
+    cluster = plan[2] if len(plan) > 2 else 1            # (bn, splits, 0) forces the reduction through scratch
     f = _fn(load_module("gemm_tc.cu"), "llb_gemm_tc",
             [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-             c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p])
+             c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p])
     _check(f(_ptr(x), _ptr(weight), _ptr(bias), _dt(bias) if bias is not None else 0, _ptr(out), _dt(out),
-             M, N, K, x.stride(0), out.stride(0), bn, splits, dual_offset, _ptr(scratch), scratch.numel(),
+             M, N, K, x.stride(0), out.stride(0), bn, splits, cluster, dual_offset, _ptr(scratch), scratch.numel(),
              _ptr(counters), counters.numel(), _ptr(err), _stream()), "linear (tensor cores)")
 
 
@@ -283,7 +291,8 @@ class _MmaAttnParams(ctypes.Structure):
                 ("table_stride", c_int), ("ring", c_int), ("seq_start", c_void_p),
                 ("seq_len_before", c_void_p), ("nh", c_int), ("nkvh", c_int), ("window", c_int),
                 ("scale", c_float), ("all_from_cache", c_int), ("n_splits", c_int), ("part_o", c_void_p),
-                ("part_ml", c_void_p)]
+                ("part_ml", c_void_p), ("rope_cos", c_void_p), ("rope_sin", c_void_p), ("rope_rows", c_int),
+                ("append_new", c_int), ("cluster", c_int)]
 
 
 MMA_ATTENTION = True                         # tests switch the tensor-core attention off to compare
@@ -291,6 +300,12 @@ MMA_ATTENTION = True                         # tests switch the tensor-core atte
 
 def _mma_ok(qkv, dh) -> bool:
     return MMA_ATTENTION and qkv.dtype == torch.bfloat16 and dh % 16 == 0 and dh <= 128 and qkv.stride(0) % 8 == 0
+
+
+def decode_fusion_ok(dtype: torch.dtype, dh: int) -> bool:
+    """True when decode attention can itself rotate the query and the new key and append the
+    new key and value to the cache (the tensor-core kernel), so that no kernel has to do it before."""
+    return MMA_ATTENTION and dtype == torch.bfloat16 and dh % 16 == 0 and dh <= 128
 
 
 def _mma_lib(dh: int):
@@ -344,23 +359,37 @@ def attention_prefill(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_sta
 
 
 def attention_decode(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before,
-                     n_seqs: int, window, scale, n_splits: int = 1) -> torch.Tensor:
-    """Attention of one new token per sequence (already appended to the cache) over the cache."""
+                     n_seqs: int, window, scale, n_splits: int = 1, rope=None, append_new: bool = False) -> torch.Tensor:
+    """Attention of one new token per sequence over the cache.
+
+    By default the new token's (rotated) key and value are already in the cache.  Where
+    decode_fusion_ok() holds, the kernel can do that work itself: rope = (cos, sin) tables makes it
+    rotate the query heads (and the new key), append_new makes it take the new key and value from
+    `qkv`, use them and write them to the cache."""
     _need_cuda(qkv, kpool, vpool, page_table)
     assert qkv.dtype == kpool.dtype == vpool.dtype
     out = torch.empty((qkv.shape[0], nh * dh), dtype=qkv.dtype, device=qkv.device)
     mma = _mma_ok(qkv, dh)
     p = _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before, window, scale,
                      _MmaAttnParams if mma else None)
+    if (rope is not None or append_new) and not mma:
+        raise KernelError("attention_decode: the fused rotation / append needs the tensor-core kernel (see decode_fusion_ok)")
     keep = None
-    if n_splits > 1:
+    if mma:
+        n_splits = min(n_splits, 64)
+        if rope is not None:
+            p.rope_cos, p.rope_sin, p.rope_rows = rope[0].data_ptr(), rope[1].data_ptr(), rope[0].shape[0]
+        p.append_new = int(append_new)
+        p.cluster = int(1 < n_splits <= 8)          # few slices merge inside a cluster, through shared memory
+    p.n_splits = n_splits
+    if n_splits > 1 and not (mma and p.cluster):
         part_o = torch.empty((n_seqs, nh, n_splits, dh), dtype=torch.float32, device=qkv.device)
         part_ml = torch.empty((n_seqs, nh, n_splits, 2), dtype=torch.float32, device=qkv.device)
         p.n_splits, p.part_o, p.part_ml = n_splits, part_o.data_ptr(), part_ml.data_ptr()
         keep = (part_o, part_ml)
     if mma:
         f = _fn(_mma_lib(dh), "llb_attn_mma_decode", [_MmaAttnParams, c_int, c_void_p])
-        _check(f(p, n_seqs, _stream()), "attention_decode (tensor cores)", 2 if n_splits > 1 else 1)
+        _check(f(p, n_seqs, _stream()), "attention_decode (tensor cores)", 2 if (n_splits > 1 and not p.cluster) else 1)
     else:
         f = _fn(_attn_lib(dh), "llb_attn_decode", [_AttnParams, c_int, c_int, c_void_p])
         _check(f(p, _dt(qkv), n_seqs, _stream()), "attention_decode", 2 if n_splits > 1 else 1)

@@ -81,16 +81,25 @@ class GQAttention(Mixer):
             append = dict(tok_seq=ctx.tok_seq, seq_start=ctx.seq_start, seq_len_before=ctx.seq_len_before,
                           kpool=kv.k, vpool=kv.v, page_table=kv.page_table, ring=kv.ring)
         decode = ctx.is_decode
-        # position encoding; in decode the same kernel also appends to the cache
-        if self.position is not None:
-            self.position.apply(qkv, self.nh, self.nkvh, ctx, append=append if decode else None)
-        elif decode and append:
-            kernels.rope_append(qkv, self.nh, self.nkvh, self.dh, tok_pos=ctx.tok_pos, append=append, err=ctx.err)
         common = (qkv, self.nh, self.nkvh, self.dh, kv.k, kv.v, kv.page_table, kv.ring,
                   ctx.seq_start, ctx.seq_len_before, ctx.n_seqs)
         if decode:
-            out = kernels.attention_decode(*common, self.window, self.scale, n_splits=ctx.decode_splits(self.nkvh))
+            fused_tables = getattr(self.position, "fused_tables", None) if self.position is not None else None
+            if kernels.decode_fusion_ok(qkv.dtype, self.dh) and (self.position is None or fused_tables is not None):
+                # the attention kernel rotates the query and the new key itself and appends to the cache
+                rope = fused_tables(ctx.max_position + 1) if fused_tables is not None else None
+                out = kernels.attention_decode(*common, self.window, self.scale, n_splits=ctx.decode_splits(self.nkvh),
+                                               rope=rope, append_new=kv.writable)
+            else:
+                # position encoding; the same kernel also appends to the cache
+                if self.position is not None:
+                    self.position.apply(qkv, self.nh, self.nkvh, ctx, append=append)
+                elif append:
+                    kernels.rope_append(qkv, self.nh, self.nkvh, self.dh, tok_pos=ctx.tok_pos, append=append, err=ctx.err)
+                out = kernels.attention_decode(*common, self.window, self.scale, n_splits=ctx.decode_splits(self.nkvh))
         else:
+            if self.position is not None:
+                self.position.apply(qkv, self.nh, self.nkvh, ctx, append=None)
             out = kernels.attention_prefill(*common, ctx.max_new, self.window, self.scale,
                                             all_from_cache=not kv.writable)
             if append:

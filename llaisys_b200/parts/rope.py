@@ -35,6 +35,10 @@ class RotaryHalfSplit(PositionEncoding):
             self._sin = torch.sin(ang).to(torch.float32).to(self.env.device)
         return self._cos, self._sin
 
+    def fused_tables(self, positions: int):
+        """(cos, sin) for kernels that apply this rotation themselves (decode attention)."""
+        return self.table(positions)
+
     def prepare(self, max_positions):
         self.table(max_positions)          # full size once: a captured step must not see the table move
 

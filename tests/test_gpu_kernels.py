@@ -217,7 +217,7 @@ def test_attention_prefill(dtype, nh, nkvh, dh, window):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkvh,dh,window", [(4, 2, 32, None), (6, 1, 48, 70), (12, 2, 128, None), (5, 5, 64, 3), (40, 1, 16, 129)])
-@pytest.mark.parametrize("splits", [1, 3, 7])
+@pytest.mark.parametrize("splits", [1, 3, 8, 11])
 def test_attention_decode(dtype, nh, nkvh, dh, window, splits):
     from llaisys_b200 import kernels
     lens_before, news = [0, 129, 63, 64, 500], [1, 1, 1, 1, 1]
@@ -363,22 +363,25 @@ def test_linear_tensor_cores(T, N, K):
 
 
 @pytest.mark.parametrize("bn", [16, 32, 64, 128, 256])
-@pytest.mark.parametrize("splits", [1, 2, 5])
-def test_linear_tensor_cores_every_tile_and_split(bn, splits):
+@pytest.mark.parametrize("splits,cluster", [(1, 0), (2, 0), (5, 0), (2, 1), (4, 1), (8, 1)])
+def test_linear_tensor_cores_every_tile_and_split(bn, splits, cluster):
+    """cluster = 1: the splits reduce through distributed shared memory (a tile of 256 tokens falls back to
+    the scratch buffer); cluster = 0: through the scratch buffer and the last-arriver fix-up."""
     from llaisys_b200 import kernels
-    T, N, K = bn + 3, 300, 712                  # two token tiles, three row tiles, twelve k-blocks (the last one partial)
-    x, w, _ = _tc_case(T, N, K, bn * splits)
-    want = plain.linear(x.double().cpu().numpy(), w.double().cpu().numpy())
+    T, N, K = bn + 3, 300, 1096                 # two token tiles, three row tiles, eighteen k-blocks (the last one partial)
+    x, w, b = _tc_case(T, N, K, bn * splits, bias=torch.float32)
+    want = plain.linear(x.double().cpu().numpy(), w.double().cpu().numpy(), b.double().cpu().numpy())
     for _ in range(2):                          # twice: the tile counters must be back at zero
-        _tc_check(kernels.linear(x, w, out_dtype=torch.float32, plan=(bn, splits)), want, K)
+        _tc_check(kernels.linear(x, w, b, out_dtype=torch.float32, plan=(bn, splits, cluster)), want, K)
     wide = torch.zeros((T, K + 16), dtype=torch.bfloat16, device=DEV)
     wide[:, 8:8 + K] = x
-    _tc_check(kernels.linear(wide[:, 8:8 + K], w, out_dtype=torch.float32, plan=(bn, splits)), want, K)
+    _tc_check(kernels.linear(wide[:, 8:8 + K], w, b, out_dtype=torch.float32, plan=(bn, splits, cluster)), want, K)
     assert kernels.tc_error(DEV) == 0
 
 
 @pytest.mark.parametrize("T,I,K,plan", [(8, 8960, 1536, None), (3, 200, 72, None), (70, 136, 96, None), (300, 264, 200, None),
-                                        (20, 300, 712, (32, 3)), (20, 300, 712, (256, 2)), (130, 300, 712, (128, 4))])
+                                        (20, 300, 712, (32, 3)), (20, 300, 712, (256, 2)), (130, 300, 712, (128, 4)),
+                                        (130, 300, 712, (128, 4, 0)), (9, 300, 1096, (16, 8)), (40, 136, 520, (64, 2))])
 def test_linear_swiglu_tensor_cores(T, I, K, plan):
     from llaisys_b200 import kernels
     x, w, _ = _tc_case(T, 2 * I, K, T + I)
@@ -396,3 +399,40 @@ def test_linear_falls_back_where_tensor_cores_do_not_apply():
     x, w, _ = _tc_case(5, 40, 36, 1)             # K = 36 is no multiple of 8
     want = plain.linear(x.double().cpu().numpy(), w.double().cpu().numpy())
     _tc_check(kernels.linear(x, w, out_dtype=torch.float32), want, 36)
+
+
+@pytest.mark.parametrize("nh,nkvh,dh,window", [(12, 2, 128, None), (6, 1, 48, 70), (40, 1, 16, 129), (4, 4, 64, 3)])
+@pytest.mark.parametrize("splits", [1, 5, 13])
+def test_attention_decode_fused_rotation_and_append(nh, nkvh, dh, window, splits):
+    """The tensor-core decode kernel can rotate the query and the new key and append to the cache
+    itself; that must give what the separate rotation/append kernel followed by attention gives,
+    in the output and in the cache."""
+    from llaisys_b200 import kernels
+    from llaisys_b200.config import PartSpec
+    from llaisys_b200.parts import BuildEnv, build_part
+    dtype = torch.bfloat16
+    lens_before, news = [0, 129, 63, 64, 500], [1, 1, 1, 1, 1]
+    d, _ = _attention_case(dtype, nh, nkvh, dh, lens_before, news, window, seed=nh + dh + splits)
+    rope = build_part("position", PartSpec("rope_half_split", {"head_dim": dh, "theta": 1e4}), BuildEnv(dtype, torch.device(DEV)))
+    cos, sin = rope.table(600)
+    width = d["table"].shape[1]
+    args = lambda q, k, v: (q, nh, nkvh, dh, k, v, d["table"], width, d["seq_start"], d["len_before"], 5, window, 1 / math.sqrt(dh))
+    # separate kernels
+    q1, k1, v1 = d["qkv"].clone(), d["kpool"].clone(), d["vpool"].clone()
+    tok = torch.arange(5, dtype=torch.int32, device=DEV)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    kernels.rope_append(q1, nh, nkvh, dh, cos=cos, sin=sin, tok_pos=d["len_before"], err=err, append=dict(
+        tok_seq=tok, seq_start=d["seq_start"], seq_len_before=d["len_before"], kpool=k1, vpool=v1,
+        page_table=d["table"], ring=width))
+    want = kernels.attention_decode(*args(q1, k1, v1), n_splits=splits)
+    # one kernel
+    q2, k2, v2 = d["qkv"].clone(), d["kpool"].clone(), d["vpool"].clone()
+    got = kernels.attention_decode(*args(q2, k2, v2), n_splits=splits, rope=(cos, sin), append_new=True)
+    assert torch.equal(q2, d["qkv"])                                   # the projections are left as they were
+    assert torch.isfinite(got).all() and float((got.float() - want.float()).abs().max()) <= 2.0 ** -7 * float(want.float().abs().max())
+    written = torch.isfinite(k1)                                       # untouched rows of the test pool are NaN
+    assert torch.equal(written, torch.isfinite(k2)) and torch.equal(k1[written], k2[written])
+    assert torch.equal(torch.isfinite(v1), torch.isfinite(v2)) and torch.equal(v1[torch.isfinite(v1)], v2[torch.isfinite(v2)])
+    # the same kernel twice more: the counters of the slice merge must be back at zero
+    got2 = kernels.attention_decode(*args(q1, k1, v1), n_splits=splits)
+    assert torch.equal(got2, want)
