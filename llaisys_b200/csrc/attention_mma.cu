@@ -36,7 +36,8 @@ constexpr int ROW_BYTES = DH * 2;
 constexpr int ROW_STRIDE = ROW_BYTES + 16;     // padded shared-memory row
 constexpr int TILE_BYTES = TILE * ROW_STRIDE;
 constexpr int STAGE_BYTES = 2 * TILE_BYTES;    // keys, then values
-constexpr int STAGES = 3;
+constexpr int STAGES = 3;     // ring depth.  (A deeper ring for decode was measured: its blocks fill an SM's shared memory,
+                              // the next kernel's blocks can no longer start early and stream their weights, and the step slows.)
 constexpr int THREADS = 128;
 constexpr int KSTEPS = DH / 16;
 constexpr int DTILES = DH / 8;
@@ -266,27 +267,30 @@ __device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], float
     }
 }
 
+template <int NST>
 struct Ring {
     uint32_t base;
     uint8_t* ptr;
-    __device__ uint32_t stage(int i) const { return base + (i % STAGES) * STAGE_BYTES; }
-    __device__ uint8_t* stage_ptr(int i) const { return ptr + (i % STAGES) * STAGE_BYTES; }
+    __device__ uint32_t stage(int i) const { return base + (i % NST) * STAGE_BYTES; }
+    __device__ uint8_t* stage_ptr(int i) const { return ptr + (i % NST) * STAGE_BYTES; }
 };
 
-__device__ __forceinline__ Ring make_ring(uint8_t* smem_raw) {
-    Ring r;
+template <int NST>
+__device__ __forceinline__ Ring<NST> make_ring(uint8_t* smem_raw) {
+    Ring<NST> r;
     uint32_t raw = smem_u32(smem_raw);
     r.base = (raw + 127u) & ~127u;
     r.ptr = smem_raw + (r.base - raw);
     return r;
 }
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 16 * (DH + 8) * 2 + 128;     // ring, staged queries, alignment slack
+constexpr int smem_bytes(int nst) { return nst * STAGE_BYTES + 16 * (DH + 8) * 2 + 128; }     // ring, staged queries, alignment slack
 
 // ------------------------------------------------------------------ decode
+template <int NST>
 __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    Ring ring = make_ring(smem_raw);
+    Ring<NST> ring = make_ring<NST>(smem_raw);
     // With append_new nothing this kernel fetches from the cache was written by the kernels just before it
     // (the new token's row comes from the projections), and the step's description was copied before the
     // step's first kernel: the first tiles are requested before the grid dependency resolves.
@@ -315,14 +319,14 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
 
     Source src{p.kpool, p.vpool, nullptr, nullptr, p.page_table + (size_t)b * p.table_stride,
                p.ring, p.nkvh, kvh, 0, 0, 0, false};
-    for (int i = 0; i < STAGES; ++i) {
+    for (int i = 0; i < NST; ++i) {
         if (i < n_tiles) issue_tile(src, tile_lo + i, key_lo, fetch_hi, ring.stage(i), tid);
         cp_async_commit();                                 // one group per stage, empty or not
     }
     if (p.append_new) llb_grid_dependency_sync();          // the projections are read from here on
 
     // the query heads of this block, rotated if asked for, staged in shared memory behind the ring
-    bf16* qs = reinterpret_cast<bf16*>(ring.ptr + STAGES * STAGE_BYTES);       // [16][DH + 8]
+    bf16* qs = reinterpret_cast<bf16*>(ring.ptr + NST * STAGE_BYTES);       // [16][DH + 8]
     {
         constexpr int HALF = DH / 2;
         const bf16* qg = p.q + (size_t)tok * p.row_stride + (size_t)head0 * DH;
@@ -351,7 +355,7 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
     const float scale_log2 = p.scale * 1.4426950408889634f;
 
     for (int i = 0; i < n_tiles; ++i) {
-        cp_async_wait<STAGES - 1>();                       // this thread's copies of tile i have landed
+        cp_async_wait<NST - 1>();                       // this thread's copies of tile i have landed
         __syncthreads();                                   // ... and everyone else's
         if (p.append_new && tile_lo + i == pos / TILE) {
             // the new token's row: from the packed projections into this tile (and, once per kv head, into the cache)
@@ -374,7 +378,7 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
         zero_unfetched(ring.stage_ptr(i), tile_lo + i, key_lo, pos, tid);
         tile_step<2>(qf, o, m, l, ring.stage(i), warp * 16, (tile_lo + i) * TILE, key_lo, pos, key_lo, pos, scale_log2, lane);
         __syncthreads();                                   // the stage is free
-        if (i + STAGES < n_tiles) issue_tile(src, tile_lo + i + STAGES, key_lo, fetch_hi, ring.stage(i + STAGES), tid);
+        if (i + NST < n_tiles) issue_tile(src, tile_lo + i + NST, key_lo, fetch_hi, ring.stage(i + NST), tid);
         cp_async_commit();
     }
     cp_async_wait<0>();
@@ -512,7 +516,7 @@ __global__ void __launch_bounds__(THREADS) attn_mma_prefill_kernel(MmaAttnParams
     const int tok0 = p.seq_start[b], n_new = p.seq_start[b + 1] - tok0, len_before = p.seq_len_before[b];
     const int t0 = blockIdx.x * 64;
     if (t0 >= n_new) return;
-    Ring ring = make_ring(smem_raw);
+    Ring<STAGES> ring = make_ring<STAGES>(smem_raw);
     const int kvh = head / (p.nh / p.nkvh);
     const int n_rows = min(64, n_new - t0);
     const int first_pos = len_before + t0, last_pos = first_pos + n_rows - 1;
@@ -569,10 +573,10 @@ __global__ void __launch_bounds__(THREADS) attn_mma_prefill_kernel(MmaAttnParams
 }
 
 template <int WHICH, typename K>       // WHICH tells the kernels apart: they share one function type
-int configure(K kernel) {
+int configure(K kernel, int smem) {
     static bool done = false;
-    if (!done && SMEM_BYTES > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (!done && smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
     }
     done = true;
@@ -593,9 +597,9 @@ LLB_API int llb_attn_mma_prefill(MmaAttnParams p, int B, int max_new, cudaStream
     if (!aligned_ok(p)) return (int)cudaErrorInvalidValue;
     dim3 grid((max_new + 63) / 64, p.nh, B);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
-    int rc = configure<0>(attn_mma_prefill_kernel);
+    int rc = configure<0>(attn_mma_prefill_kernel, smem_bytes(STAGES));
     if (rc) return rc;
-    llb_launch(attn_mma_prefill_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, p);
+    llb_launch(attn_mma_prefill_kernel, grid, dim3(THREADS), smem_bytes(STAGES), stream, p);
     return llb_status();
 }
 
@@ -606,14 +610,16 @@ LLB_API int llb_attn_mma_decode(MmaAttnParams p, int B, cudaStream_t stream) {
     int G = p.nh / p.nkvh;
     dim3 grid(p.n_splits, p.nkvh * ((G + 15) / 16), B);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
-    int rc = configure<1>(attn_mma_decode_kernel);
+    auto kernel = attn_mma_decode_kernel<STAGES>;
+    const int smem = smem_bytes(STAGES);
+    int rc = configure<1>(kernel, smem);
     if (rc) return rc;
     if (p.cluster && p.n_splits > 1) {
-        llb_prefer_max_shared((const void*)attn_mma_decode_kernel);
+        llb_prefer_max_shared((const void*)kernel);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;
         cfg.blockDim = dim3(THREADS);
-        cfg.dynamicSmemBytes = SMEM_BYTES;
+        cfg.dynamicSmemBytes = smem;
         cfg.stream = stream;
         cudaLaunchAttribute attr[2];
         int n_attr = 0;
@@ -629,9 +635,9 @@ LLB_API int llb_attn_mma_decode(MmaAttnParams p, int B, cudaStream_t stream) {
         ++n_attr;
         cfg.attrs = attr;
         cfg.numAttrs = n_attr;
-        cudaLaunchKernelEx(&cfg, attn_mma_decode_kernel, p);
+        cudaLaunchKernelEx(&cfg, kernel, p);
     } else {
-        llb_launch(attn_mma_decode_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, p);
+        llb_launch(kernel, grid, dim3(THREADS), smem, stream, p);
     }
     rc = llb_status();
     if (rc == 0 && p.n_splits > 1 && !p.cluster) {

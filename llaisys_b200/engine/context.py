@@ -99,7 +99,8 @@ class StepContext:
         most one slice per page the widest page table of the step can hold (a function of the
         step's shape alone, so a captured step stays valid as sequences grow)."""
         pages = max(self.widths) if self.widths else 1
-        want = -(-2 * self.sm_count // max(1, self.n_seqs * n_kv_heads))
+        # two blocks fit an SM; more blocks than that would run as a second, mostly empty wave
+        want = (2 * self.sm_count) // max(1, self.n_seqs * n_kv_heads)
         splits = max(1, min(want, pages, 64))
         # up to eight slices merge inside a thread-block cluster, which is cheaper than a second kernel:
         # prefer that while a block then still has at most sixteen pages to walk
