@@ -36,7 +36,8 @@ constexpr int ROW_BYTES = DH * 2;
 constexpr int ROW_STRIDE = ROW_BYTES + 16;     // padded shared-memory row
 constexpr int TILE_BYTES = TILE * ROW_STRIDE;
 constexpr int STAGE_BYTES = 2 * TILE_BYTES;    // keys, then values
-constexpr int STAGES = 3;     // ring depth.  (A deeper ring for decode was measured: its blocks fill an SM's shared memory,
+constexpr int STAGES_PREFILL = 2;   // prefill: two stages leave room for three blocks per SM (twelve warps to hide latency)
+constexpr int STAGES = 3;     // ring depth of decode.  (A deeper ring for decode was measured: its blocks fill an SM's shared memory,
                               // the next kernel's blocks can no longer start early and stream their weights, and the step slows.)
 constexpr int THREADS = 128;
 constexpr int KSTEPS = DH / 16;
@@ -90,6 +91,13 @@ __device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], 
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// 2^x by the special-function unit (relative error about 2^-22; exp2(-inf) = 0).  The results feed
+// bfloat16 probabilities and float32 sums whose other terms carry the same error.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
 }
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
@@ -186,7 +194,7 @@ __device__ __forceinline__ void load_q(uint32_t (&qf)[KSTEPS][4], F q_of, int la
 // One warp: scores of its 16 rows against NT*8 keys starting at row `key0` of the tile in `stage`,
 // masking, online softmax update, and O += P V.  lo0/hi0 and lo1/hi1: visible key positions of
 // the thread's two rows (lane/4 and lane/4 + 8).
-template <int NT>
+template <int NT, bool MASKED = true>
 __device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], float (&o)[DTILES][4], float (&m)[2],
                                           float (&l)[2], uint32_t stage, int key0, int pos0, int lo0, int hi0, int lo1,
                                           int hi1, float scale_log2, int lane) {
@@ -205,15 +213,22 @@ __device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], float
             mma16816(s[2 * n2 + 1], qf[kk], b[2], b[3]);
         }
     }
-    // mask and row maxima
+    // mask and row maxima (MASKED = false: the caller knows every key of the tile is visible to every row)
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
-        int kp = pos0 + key0 + n * 8 + (lane & 3) * 2;
-        s[n][0] = (kp >= lo0 && kp <= hi0) ? s[n][0] * scale_log2 : -INFINITY;
-        s[n][1] = (kp + 1 >= lo0 && kp + 1 <= hi0) ? s[n][1] * scale_log2 : -INFINITY;
-        s[n][2] = (kp >= lo1 && kp <= hi1) ? s[n][2] * scale_log2 : -INFINITY;
-        s[n][3] = (kp + 1 >= lo1 && kp + 1 <= hi1) ? s[n][3] * scale_log2 : -INFINITY;
+        if (MASKED) {
+            int kp = pos0 + key0 + n * 8 + (lane & 3) * 2;
+            s[n][0] = (kp >= lo0 && kp <= hi0) ? s[n][0] * scale_log2 : -INFINITY;
+            s[n][1] = (kp + 1 >= lo0 && kp + 1 <= hi0) ? s[n][1] * scale_log2 : -INFINITY;
+            s[n][2] = (kp >= lo1 && kp <= hi1) ? s[n][2] * scale_log2 : -INFINITY;
+            s[n][3] = (kp + 1 >= lo1 && kp + 1 <= hi1) ? s[n][3] * scale_log2 : -INFINITY;
+        } else {
+            s[n][0] *= scale_log2;
+            s[n][1] *= scale_log2;
+            s[n][2] *= scale_log2;
+            s[n][3] *= scale_log2;
+        }
         mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
         mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
     }
@@ -225,14 +240,14 @@ __device__ __forceinline__ void tile_step(const uint32_t (&qf)[KSTEPS][4], float
     // a row that has seen no visible key yet keeps m = -inf; use 0 as the exponent base then so that
     // exp2(-inf - 0) = 0 and no inf - inf arises
     float b0 = mn0 == -INFINITY ? 0.f : mn0, b1 = mn1 == -INFINITY ? 0.f : mn1;
-    float a0 = exp2f(m[0] - b0), a1 = exp2f(m[1] - b1);
+    float a0 = fast_exp2(m[0] - b0), a1 = fast_exp2(m[1] - b1);
     m[0] = mn0;
     m[1] = mn1;
     float sum0 = 0.f, sum1 = 0.f;
     uint32_t pf[NT][2];
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
-        float p0 = exp2f(s[n][0] - b0), p1 = exp2f(s[n][1] - b0), p2 = exp2f(s[n][2] - b1), p3 = exp2f(s[n][3] - b1);
+        float p0 = fast_exp2(s[n][0] - b0), p1 = fast_exp2(s[n][1] - b0), p2 = fast_exp2(s[n][2] - b1), p3 = fast_exp2(s[n][3] - b1);
         sum0 += p0 + p1;
         sum1 += p2 + p3;
         pf[n][0] = pack_bf16(p0, p1);
@@ -508,7 +523,7 @@ __global__ void attn_mma_combine_kernel(bf16* __restrict__ out, const float* __r
 }
 
 // ------------------------------------------------------------------ prefill
-__global__ void __launch_bounds__(THREADS) attn_mma_prefill_kernel(MmaAttnParams p) {
+__global__ void __launch_bounds__(THREADS, 3) attn_mma_prefill_kernel(MmaAttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int b = blockIdx.z, head = blockIdx.y;
@@ -516,7 +531,7 @@ __global__ void __launch_bounds__(THREADS) attn_mma_prefill_kernel(MmaAttnParams
     const int tok0 = p.seq_start[b], n_new = p.seq_start[b + 1] - tok0, len_before = p.seq_len_before[b];
     const int t0 = blockIdx.x * 64;
     if (t0 >= n_new) return;
-    Ring<STAGES> ring = make_ring<STAGES>(smem_raw);
+    Ring<STAGES_PREFILL> ring = make_ring<STAGES_PREFILL>(smem_raw);
     const int kvh = head / (p.nh / p.nkvh);
     const int n_rows = min(64, n_new - t0);
     const int first_pos = len_before + t0, last_pos = first_pos + n_rows - 1;
@@ -525,7 +540,7 @@ __global__ void __launch_bounds__(THREADS) attn_mma_prefill_kernel(MmaAttnParams
 
     Source src{p.kpool, p.vpool, p.k_new, p.v_new, p.page_table + (size_t)b * p.table_stride,
                p.ring, p.nkvh, kvh, p.row_stride, tok0, len_before, !p.all_from_cache};
-    for (int i = 0; i < STAGES; ++i) {
+    for (int i = 0; i < STAGES_PREFILL; ++i) {
         if (i < n_tiles) issue_tile(src, tile_lo + i, key_lo, last_pos, ring.stage(i), tid);
         cp_async_commit();
     }
@@ -546,14 +561,19 @@ __global__ void __launch_bounds__(THREADS) attn_mma_prefill_kernel(MmaAttnParams
     const float scale_log2 = p.scale * 1.4426950408889634f;
 
     for (int i = 0; i < n_tiles; ++i) {
-        cp_async_wait<STAGES - 1>();
+        cp_async_wait<STAGES_PREFILL - 1>();
         __syncthreads();
         zero_unfetched(ring.stage_ptr(i), tile_lo + i, key_lo, last_pos, tid);
         int p0 = (tile_lo + i) * TILE;
-        if (p0 <= warp_hi && p0 + TILE - 1 >= warp_lo)               // the tile holds a key some row of the warp sees
-            tile_step<8>(qf, o, m, l, ring.stage(i), 0, p0, lo0, hi0, lo1, hi1, scale_log2, lane);
+        if (p0 <= warp_hi && p0 + TILE - 1 >= warp_lo) {             // the tile holds a key some row of the warp sees
+            // every key of the tile visible to every row of the warp (most tiles of a causal prompt): no masks
+            const bool all_visible = p0 + TILE - 1 <= first_pos + warp * 16 &&
+                                     (p.window <= 0 || p0 >= first_pos + warp * 16 + 15 - p.window + 1);
+            if (all_visible) tile_step<8, false>(qf, o, m, l, ring.stage(i), 0, p0, lo0, hi0, lo1, hi1, scale_log2, lane);
+            else tile_step<8, true>(qf, o, m, l, ring.stage(i), 0, p0, lo0, hi0, lo1, hi1, scale_log2, lane);
+        }
         __syncthreads();
-        if (i + STAGES < n_tiles) issue_tile(src, tile_lo + i + STAGES, key_lo, last_pos, ring.stage(i + STAGES), tid);
+        if (i + STAGES_PREFILL < n_tiles) issue_tile(src, tile_lo + i + STAGES_PREFILL, key_lo, last_pos, ring.stage(i + STAGES_PREFILL), tid);
         cp_async_commit();
     }
     cp_async_wait<0>();
@@ -597,9 +617,9 @@ LLB_API int llb_attn_mma_prefill(MmaAttnParams p, int B, int max_new, cudaStream
     if (!aligned_ok(p)) return (int)cudaErrorInvalidValue;
     dim3 grid((max_new + 63) / 64, p.nh, B);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
-    int rc = configure<0>(attn_mma_prefill_kernel, smem_bytes(STAGES));
+    int rc = configure<0>(attn_mma_prefill_kernel, smem_bytes(STAGES_PREFILL));
     if (rc) return rc;
-    llb_launch(attn_mma_prefill_kernel, grid, dim3(THREADS), smem_bytes(STAGES), stream, p);
+    llb_launch(attn_mma_prefill_kernel, grid, dim3(THREADS), smem_bytes(STAGES_PREFILL), stream, p);
     return llb_status();
 }
 
