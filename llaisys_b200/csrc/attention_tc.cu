@@ -1,0 +1,507 @@
+// bfloat16 prefill attention over the paged cache on the 5th-generation tensor cores (tcgen05),
+// for head sizes 64 and 128.  Same formula and masks as attention_simt.cu (xsmccc/llaisys
+// src/ops/self_attention/cpu/self_attention_cpu.cpp:28-112, plus the window).  All keys, those of
+// the step included, are read from the cache: the caller appends before it attends.
+//
+// A CTA owns 128 consecutive new tokens of one query head.  Warps 0-3 are the softmax warps:
+// thread r owns query row r (and lane r of tensor memory).  Warp 4 issues every copy and every
+// matrix product, so the softmax warps never leave their arithmetic.  Per tile of one cache page
+// (64 keys):
+//
+//   warp 4   TMA            K and V pages -> shared memory (128-byte swizzle), two stages each
+//   warp 4   tcgen05.mma    S[128, 64] = Q K^T into one of two score buffers in tensor memory, two tiles
+//                           ahead of the softmax (Q, K both K-major)
+//   rows     tcgen05.ld of the own row of S: mask, maximum, exponentials (float32, no cross-thread
+//            reduction: a row is one thread's), P as bfloat16 into shared memory
+//   warp 4   tcgen05.mma    O[128, dh] += P V  (P K-major, V MN-major as it lies in the cache); the
+//                           accumulator stays in tensor memory over all tiles
+//
+// The exponent base of a row is its running maximum, but it moves only when the maximum has grown
+// by more than 8 (a factor 256, far inside the range of bfloat16 and float32): then the row's sum
+// and its accumulator in tensor memory are scaled by exp2(old base - new base) (tcgen05.ld, multiply,
+// tcgen05.st) before the next product is added.  After the first tiles that is rare, and the result
+// is the same quotient O / l.  With the accumulator out of the registers the compiler has room to
+// interleave the independent chains of a row, which a warp alone on its scheduler needs.
+// Two CTAs share an SM (112 KB of shared memory and 256 tensor-memory columns each).
+// Every mbarrier wait is bounded; a wait that runs out sets *err and the CTA leaves in order.
+#include "common.cuh"
+
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+#ifndef LLB_HEAD_DIM
+#error "compile with -DLLB_HEAD_DIM=<64 or 128>"
+#endif
+
+namespace {
+
+constexpr int DH = LLB_HEAD_DIM;
+static_assert(DH == 64 || DH == 128, "the tcgen05 attention kernel takes head sizes 64 and 128");
+constexpr int BQ = 128;                    // query rows of a CTA (UMMA M)
+constexpr int BKV = LLB_PAGE;              // keys of a tile (UMMA N of Q K^T, K of P V)
+constexpr int NBLK = DH / 64;              // 64-column (128-byte) blocks of a head
+constexpr int ROW_THREADS = 128;           // warps 0-3: one query row each
+constexpr int THREADS = 160;               // warp 4: copies and matrix products
+constexpr int Q_BYTES = BQ * DH * 2;       // [NBLK][128 rows][128 B]
+constexpr int KV_BYTES = BKV * DH * 2;     // [NBLK][64 rows][128 B]
+constexpr int P_BYTES = BQ * BKV * 2;      // [128 rows][128 B]
+constexpr int KV_STAGES = 2;
+constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + KV_STAGES * KV_BYTES, OFF_P = OFF_V + KV_STAGES * KV_BYTES;
+constexpr int OFF_BAR = OFF_P + P_BYTES;
+constexpr int SMEM_BYTES = OFF_BAR + 80;
+constexpr int TMEM_COLS = 256;             // S: two buffers at columns [0, 64) and [64, 128); O: columns [128, 128 + DH)
+constexpr int O_COL = 128;
+constexpr float BASE_STEP = 8.f;           // the exponent base follows the maximum in steps larger than this (log2)
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+enum { ERR_ATTN_TC_WAIT = 121, ERR_ATTN_TC_ALIGN = 122 };
+
+struct TcAttnParams {
+    bf16* out;                  // [T, nh * DH]
+    const int* page_table;      // [B, table_stride]
+    int table_stride;
+    const int* seq_start;
+    const int* seq_len_before;
+    int nh, nkvh, window;
+    float scale;
+    int* err;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
+// Bounded wait; gives up early when another thread of the CTA has already given up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+// The same for a whole (converged) warp: either every lane goes on or none does, so that the
+// warp-wide tensor-memory instructions that follow never run with lanes missing.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    return !__any_sync(0xffffffffu, !mbar_wait(bar, parity, abort_flag));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+// K-major operand tile: rows of 128 bytes, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// MN-major operand tile (V as it lies in the cache: a row per key, the head dimension contiguous): 64-element
+// column blocks `lbo` bytes apart, groups of 8 keys 1024 bytes apart, 128-byte swizzle.
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t lbo) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ uint32_t idesc_f16(int n, bool b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(BQ >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// One row of 16 accumulator columns; several loads can be in flight before one tmem_wait().
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};"
+        ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// two float32 multiply-adds in one instruction
+__device__ __forceinline__ void fma2(float& lo, float& hi, float a_lo, float a_hi, uint64_t b, uint64_t c) {
+    uint64_t a, d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(a) : "f"(a_lo), "f"(a_hi));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(d));
+}
+// acc += both bfloat16 halves of w (float32 accumulation)
+__device__ __forceinline__ void add_bf16_pair(float& acc, uint32_t w) {
+    asm("{\n\t.reg .b16 lo, hi;\n\tmov.b32 {lo, hi}, %1;\n\tadd.rn.f32.bf16 %0, lo, %0;\n\tadd.rn.f32.bf16 %0, hi, %0;\n\t}" : "+f"(acc) : "r"(w));
+}
+__device__ __forceinline__ uint64_t twice(float v) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %1};" : "=l"(r) : "f"(v));
+    return r;
+}
+__device__ __forceinline__ void tmem_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__global__ void __launch_bounds__(THREADS, 2)
+attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                       const __grid_constant__ CUtensorMap map_v, TcAttnParams p) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    const uint32_t base = smem_u32(smem);
+    // barriers: Q landed; K / V stage landed; score buffer written; P V done; P stored by all rows
+    const uint32_t bar_q = base + OFF_BAR, bar_k = bar_q + 8, bar_v = bar_k + 8 * KV_STAGES, bar_s = bar_v + 8 * KV_STAGES,
+                   bar_o = bar_s + 16, bar_p = bar_o + 8;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + 72);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(smem + OFF_BAR + 76);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    if (tid == 0) {
+        *s_abort = (base & 1023u) ? 1 : 0;          // the swizzled tiles need a 1024-byte aligned base
+        if (*s_abort) atomicExch(p.err, ERR_ATTN_TC_ALIGN);
+        mbar_init(bar_q, 1);
+        for (int s = 0; s < KV_STAGES; ++s) {
+            mbar_init(bar_k + 8 * s, 1);
+            mbar_init(bar_v + 8 * s, 1);
+            mbar_init(bar_s + 8 * s, 1);
+        }
+        mbar_init(bar_o, 1);
+        mbar_init(bar_p, ROW_THREADS);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     ::"r"(base + OFF_BAR + 72), "r"((uint32_t)TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    llb_grid_dependency_sync();
+
+    // ---- which rows, which keys
+    const int b = blockIdx.z, head = blockIdx.y;
+    const int tok0 = p.seq_start[b], n_new = p.seq_start[b + 1] - tok0, len_before = p.seq_len_before[b];
+    const int t0 = blockIdx.x * BQ;
+    const bool active = t0 < n_new && !*s_abort;
+    const int kvh = head / (p.nh / p.nkvh);
+    const int n_rows = min(BQ, n_new - t0);
+    const int first_pos = len_before + t0, last_pos = first_pos + n_rows - 1;
+    const int key_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
+    const int tile_lo = key_lo / BKV, n_tiles = active ? last_pos / BKV + 1 - tile_lo : 0;
+    const int* table = p.page_table + (size_t)b * p.table_stride;
+    bool failed = false;
+
+    if (warp == 4) {
+        // ================================================= copies and matrix products (lane 0 issues)
+        auto issue_k = [&](int i) {
+            const int s = i % KV_STAGES, row = (table[tile_lo + i] * p.nkvh + kvh) * BKV;
+            mbar_expect_tx(bar_k + 8 * s, KV_BYTES);
+#pragma unroll
+            for (int blk = 0; blk < NBLK; ++blk)
+                tma_load_2d(base + OFF_K + s * KV_BYTES + blk * (BKV * 128), &map_k, bar_k + 8 * s, blk * 64, row);
+        };
+        auto issue_v = [&](int i) {
+            const int s = i % KV_STAGES, row = (table[tile_lo + i] * p.nkvh + kvh) * BKV;
+            mbar_expect_tx(bar_v + 8 * s, KV_BYTES);
+#pragma unroll
+            for (int blk = 0; blk < NBLK; ++blk)
+                tma_load_2d(base + OFF_V + s * KV_BYTES + blk * (BKV * 128), &map_v, bar_v + 8 * s, blk * 64, row);
+        };
+        const uint32_t idesc_s = idesc_f16(BKV, false), idesc_o = idesc_f16(DH, true);
+        // S(i) = Q K(i)^T into score buffer i % 2; the keys must have landed
+        auto issue_qk = [&](int i) {
+            const int s = i % KV_STAGES;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int ks = 0; ks < DH / 16; ++ks) {
+                uint32_t qa = base + (ks / 4) * (BQ * 128) + (ks % 4) * 32;
+                uint32_t ka = base + OFF_K + s * KV_BYTES + (ks / 4) * (BKV * 128) + (ks % 4) * 32;
+                umma(tmem + s * BKV, desc_kmajor(qa), desc_kmajor(ka), idesc_s, ks > 0);
+            }
+            umma_commit(bar_s + 8 * s);
+        };
+        if (n_tiles > 0) {
+            if (lane == 0) {
+                mbar_expect_tx(bar_q, Q_BYTES);
+#pragma unroll
+                for (int blk = 0; blk < NBLK; ++blk)
+                    tma_load_2d(base + blk * (BQ * 128), &map_q, bar_q, head * DH + blk * 64, tok0 + t0);
+                for (int i = 0; i < min(KV_STAGES, n_tiles); ++i) { issue_k(i); issue_v(i); }
+            }
+            failed = !warp_wait(bar_q, 0, s_abort);
+            for (int i = 0; i < min(KV_STAGES, n_tiles) && !failed; ++i) {
+                failed = !warp_wait(bar_k + 8 * i, 0, s_abort);
+                if (!failed && lane == 0) issue_qk(i);
+                __syncwarp();
+            }
+        }
+        for (int i = 0; i < n_tiles && !failed; ++i) {
+            const int s = i % KV_STAGES;
+            const uint32_t ph = (i / KV_STAGES) & 1;
+            // S(i) is complete: the key stage of tile i is free for tile i + 2
+            if (!warp_wait(bar_s + 8 * s, ph, s_abort)) { failed = true; break; }
+            if (lane == 0 && i + 2 < n_tiles) issue_k(i + 2);
+            // P V of tile i - 1 is complete: its value stage is free for tile i + 1
+            if (i > 0) {
+                if (!warp_wait(bar_o, (i - 1) & 1, s_abort)) { failed = true; break; }
+                if (lane == 0 && i + 1 < n_tiles && i + 1 >= KV_STAGES) issue_v(i + 1);
+            }
+            // every row has read S(i), brought O to its base and stored P(i)
+            if (!warp_wait(bar_p, i & 1, s_abort)) { failed = true; break; }
+            if (!warp_wait(bar_v + 8 * s, ph, s_abort)) { failed = true; break; }
+            if (lane == 0) {
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int ks = 0; ks < BKV / 16; ++ks) {
+                    uint32_t pa = base + OFF_P + ks * 32;
+                    uint32_t va = base + OFF_V + s * KV_BYTES + ks * (16 * 128);
+                    umma(tmem + O_COL, desc_kmajor(pa), desc_mnmajor(va, BKV * 128), idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
+                }
+                umma_commit(bar_o);
+            }
+            __syncwarp();
+            if (i + 2 < n_tiles) {
+                if (!warp_wait(bar_k + 8 * s, ph ^ 1, s_abort)) { failed = true; break; }
+                if (lane == 0) issue_qk(i + 2);
+                __syncwarp();
+            }
+        }
+    } else {
+        // ================================================= softmax: thread r owns query row r
+        const int qpos = first_pos + min(tid, n_rows - 1);          // rows past the end behave like the last row
+        const int qlo = p.window > 0 ? max(0, qpos - p.window + 1) : 0;
+        const float scale_log2 = p.scale * 1.4426950408889634f;
+        const uint64_t scale2 = twice(scale_log2);
+        const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
+        uint8_t* prow = smem + OFF_P + tid * 128;
+        float m = -INFINITY, l = 0.f;                               // m: the exponent base of the row
+
+        for (int i = 0; i < n_tiles && !failed; ++i) {
+            const int s = i % KV_STAGES;
+            const int p0 = (tile_lo + i) * BKV;
+            if (!warp_wait(bar_s + 8 * s, (i / KV_STAGES) & 1, s_abort)) { failed = true; break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t sr[BKV];
+#pragma unroll
+            for (int c = 0; c < BKV; c += 16) tmem_ld16_nowait(lane_addr + s * BKV + c, sr + c);
+            tmem_wait();
+
+            // ---- mask (only tiles that some row of the block sees in part), maximum
+            if (!(p0 + BKV - 1 <= first_pos && (p.window <= 0 || p0 >= last_pos - p.window + 1))) {
+#pragma unroll
+                for (int j = 0; j < BKV; ++j)
+                    if (!(p0 + j >= qlo && p0 + j <= qpos)) sr[j] = 0xff800000u;       // -inf
+            }
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < BKV; j += 8) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) mx[c] = fmax3(mx[c], __uint_as_float(sr[j + 2 * c]), __uint_as_float(sr[j + 2 * c + 1]));
+            }
+            const float mt = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;      // the scale is positive
+            // ---- the base follows the maximum in large steps only
+            const bool move = mt > m + BASE_STEP;                    // false while both are -inf
+            const float alpha = move ? fast_exp2(m - mt) : 1.f;      // 0 at the row's first visible key
+            if (move) m = mt;
+            const float nbase = m == -INFINITY ? 0.f : -m;
+            const uint64_t nbase2 = twice(nbase);
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < BKV; j += 2) {
+                float pa, pb;
+                fma2(pa, pb, __uint_as_float(sr[j]), __uint_as_float(sr[j + 1]), scale2, nbase2);
+                pa = fast_exp2(pa);
+                pb = fast_exp2(pb);
+                sr[j / 2] = pack_bf16(pa, pb);                       // packed in place: sr[0..31] hold P
+                // the row sum is that of the rounded values, the same weights the product with V uses: their
+                // rounding errors then cancel in O / l (a single dominant key gives exactly its value)
+                add_bf16_pair(sum[(j / 2) % 4], sr[j / 2]);
+            }
+            l = l * alpha + (sum[0] + sum[1]) + (sum[2] + sum[3]);
+
+            // ---- P V of tile i - 1 is done: the accumulator can be scaled, the P buffer written
+            if (i > 0) {
+                if (!warp_wait(bar_o, (i - 1) & 1, s_abort)) { failed = true; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (__any_sync(0xffffffffu, move)) {
+#pragma unroll
+                    for (int c0 = 0; c0 < DH; c0 += 32) {
+                        uint32_t v[32];
+                        tmem_ld16_nowait(lane_addr + O_COL + c0, v);
+                        tmem_ld16_nowait(lane_addr + O_COL + c0 + 16, v + 16);
+                        tmem_wait();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
+                        tmem_st16(lane_addr + O_COL + c0, v);
+                        tmem_st16(lane_addr + O_COL + c0 + 16, v + 16);
+                    }
+                    tmem_wait_st();
+                }
+            }
+            // ---- P(i) into shared memory; 8 keys = one 16-byte piece, whose place is its index XOR (row mod 8)
+#pragma unroll
+            for (int c = 0; c < BKV / 8; ++c)
+                *reinterpret_cast<uint4*>(prow + ((c ^ (tid & 7)) * 16)) = make_uint4(sr[4 * c], sr[4 * c + 1], sr[4 * c + 2], sr[4 * c + 3]);
+            // rows of the page beyond the last position of this block were never written for this sequence:
+            // a zero probability must meet a finite value
+            if (p0 + BKV - 1 > last_pos) {
+                if (!warp_wait(bar_v + 8 * s, (i / KV_STAGES) & 1, s_abort)) { failed = true; break; }
+                const int j0 = last_pos - p0 + 1;
+                for (int idx = tid; idx < (BKV - j0) * NBLK * 8; idx += ROW_THREADS) {
+                    int j = j0 + idx / (NBLK * 8), rest = idx % (NBLK * 8);
+                    *reinterpret_cast<uint4*>(smem + OFF_V + s * KV_BYTES + (rest / 8) * (BKV * 128) + j * 128 + (rest % 8) * 16) =
+                        make_uint4(0, 0, 0, 0);
+                }
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P (and the zeroed rows) before the tensor core reads them
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(bar_p);
+        }
+        if (!failed && n_tiles > 0) failed = !warp_wait(bar_o, (n_tiles - 1) & 1, s_abort);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (n_tiles > 0 && !__any_sync(0xffffffffu, failed)) {
+            const float inv = 1.0f / l;
+            bf16* dst = p.out + (size_t)(tok0 + t0 + tid) * p.nh * DH + (size_t)head * DH;
+#pragma unroll
+            for (int c0 = 0; c0 < DH; c0 += 32) {
+                uint32_t v[32];
+                tmem_ld16_nowait(lane_addr + O_COL + c0, v);
+                tmem_ld16_nowait(lane_addr + O_COL + c0 + 16, v + 16);
+                tmem_wait();
+                if (tid < n_rows) {
+#pragma unroll
+                    for (int d = 0; d < 32; d += 8) {
+                        uint4 w;
+                        w.x = pack_bf16(__uint_as_float(v[d]) * inv, __uint_as_float(v[d + 1]) * inv);
+                        w.y = pack_bf16(__uint_as_float(v[d + 2]) * inv, __uint_as_float(v[d + 3]) * inv);
+                        w.z = pack_bf16(__uint_as_float(v[d + 4]) * inv, __uint_as_float(v[d + 5]) * inv);
+                        w.w = pack_bf16(__uint_as_float(v[d + 6]) * inv, __uint_as_float(v[d + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c0 + d) = w;
+                    }
+                }
+            }
+        }
+    }
+    if (failed) {
+        *s_abort = 1;
+        atomicExch(p.err, ERR_ATTN_TC_WAIT);
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);       // copies that may still be in flight get a bounded time to land
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (*s_abort && !failed)                                     // a CTA that gave up leaves together, after the same bounded time
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)TMEM_COLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* q = nullptr;
+        cudaDriverEntryPointQueryResult r;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &q, cudaEnableDefault, &r) == cudaSuccess &&
+            r == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)q;
+    });
+    return fn;
+}
+struct MapKey {
+    const void* ptr; long long rows; int cols, ld, box_rows;
+    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = (size_t)k.ptr ^ (size_t)k.rows * 1000003u;
+        for (int v : {k.cols, k.ld, k.box_rows}) h = h * 1000003u ^ (size_t)v;
+        return h;
+    }
+};
+// Row-major bf16 matrix [rows, cols], row stride ld elements; boxes of {64 columns, box_rows rows}, 128-byte swizzle.
+int get_map(const void* ptr, long long rows, int cols, int ld, int box_rows, CUtensorMap* out) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    MapKey key{ptr, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return -1000 - (int)r;
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
+}  // namespace
+
+LLB_API int llb_attn_tc_head_dim() { return DH; }
+
+// q: the packed projections [T, row_stride] (query heads first, already rotated); kpool / vpool: one call's pages
+// [n_pages, nkvh, 64, DH], already holding the step's keys and values.  max_new: most new tokens of a sequence.
+LLB_API int llb_attn_tc_prefill(const void* q, int T, int row_stride, const void* kpool, const void* vpool, int n_pages,
+                                TcAttnParams p, int B, int max_new, cudaStream_t stream) {
+    if (B == 0 || max_new == 0) return 0;
+    if (p.nkvh <= 0 || p.nh % p.nkvh || !(p.scale > 0.f) || row_stride % 8 || (((uintptr_t)q | (uintptr_t)kpool | (uintptr_t)vpool | (uintptr_t)p.out) & 15))
+        return (int)cudaErrorInvalidValue;
+    dim3 grid((max_new + BQ - 1) / BQ, p.nh, B);
+    if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
+    CUtensorMap mq, mk, mv;
+    int rc = get_map(q, T, p.nh * DH, row_stride, BQ, &mq);
+    if (rc) return rc;
+    rc = get_map(kpool, (long long)n_pages * p.nkvh * BKV, DH, DH, BKV, &mk);
+    if (rc) return rc;
+    rc = get_map(vpool, (long long)n_pages * p.nkvh * BKV, DH, DH, BKV, &mv);
+    if (rc) return rc;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tc_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        if (e != cudaSuccess) return -2000 - (int)e;
+        configured = true;
+    }
+    llb_launch(attn_tc_prefill_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, mq, mk, mv, p);
+    return llb_status();
+}

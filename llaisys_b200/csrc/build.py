@@ -137,6 +137,7 @@ DEFAULT_MODULES = [
     ("basic.cu", {}), ("gemm_simt.cu", {}), ("gemm_tc.cu", {}), ("sampling.cu", {}),
     *[("attention_simt.cu", {"LLB_HEAD_DIM": d}) for d in (16, 24, 32, 48, 64, 128)],
     *[("attention_mma.cu", {"LLB_HEAD_DIM": d}) for d in (16, 32, 48, 64, 128)],
+    *[("attention_tc.cu", {"LLB_HEAD_DIM": d}) for d in (64, 128)],
 ]
 
 

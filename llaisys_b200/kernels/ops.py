@@ -308,6 +308,21 @@ def decode_fusion_ok(dtype: torch.dtype, dh: int) -> bool:
     return MMA_ATTENTION and dtype == torch.bfloat16 and dh % 16 == 0 and dh <= 128
 
 
+class _TcAttnParams(ctypes.Structure):
+    _fields_ = [("out", c_void_p), ("page_table", c_void_p), ("table_stride", c_int), ("seq_start", c_void_p),
+                ("seq_len_before", c_void_p), ("nh", c_int), ("nkvh", c_int), ("window", c_int), ("scale", c_float),
+                ("err", c_void_p)]
+
+
+TC_ATTENTION = True                          # tests switch the tcgen05 prefill attention off to compare
+
+
+def prefill_tc_ok(dtype: torch.dtype, dh: int) -> bool:
+    """True when prefill attention can run on tcgen05 (csrc/attention_tc.cu): bfloat16, head size 64
+    or 128.  That kernel reads every key, those of the step included, from the cache."""
+    return TC_ATTENTION and dtype == torch.bfloat16 and dh in (64, 128)
+
+
 def _mma_lib(dh: int):
     return load_module("attention_mma.cu", {"LLB_HEAD_DIM": dh})
 
@@ -344,6 +359,17 @@ def attention_prefill(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_sta
     _need_cuda(qkv, kpool, vpool, page_table)
     assert qkv.dtype == kpool.dtype == vpool.dtype
     out = torch.empty((qkv.shape[0], nh * dh), dtype=qkv.dtype, device=qkv.device)
+    if all_from_cache and prefill_tc_ok(qkv.dtype, dh) and ring >= page_table.shape[1] and qkv.stride(0) % 8 == 0:
+        p = _TcAttnParams()
+        p.out, p.page_table, p.table_stride = out.data_ptr(), page_table.data_ptr(), page_table.shape[1]
+        p.seq_start, p.seq_len_before = seq_start.data_ptr(), seq_len_before.data_ptr()
+        p.nh, p.nkvh, p.window, p.scale = nh, nkvh, int(window or 0), scale
+        p.err = _tc_resources(qkv.device)[2].data_ptr()
+        f = _fn(load_module("attention_tc.cu", {"LLB_HEAD_DIM": dh}), "llb_attn_tc_prefill",
+                [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, _TcAttnParams, c_int, c_int, c_void_p])
+        _check(f(qkv.data_ptr(), qkv.shape[0], qkv.stride(0), kpool.data_ptr(), vpool.data_ptr(), kpool.shape[0],
+                 p, n_seqs, max_new, _stream()), "attention_prefill (tcgen05)")
+        return out
     if _mma_ok(qkv, dh):
         p = _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before, window,
                          scale, _MmaAttnParams)

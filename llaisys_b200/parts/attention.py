@@ -97,6 +97,13 @@ class GQAttention(Mixer):
                 elif append:
                     kernels.rope_append(qkv, self.nh, self.nkvh, self.dh, tok_pos=ctx.tok_pos, append=append, err=ctx.err)
                 out = kernels.attention_decode(*common, self.window, self.scale, n_splits=ctx.decode_splits(self.nkvh))
+        elif self.window is None and kernels.prefill_tc_ok(qkv.dtype, self.dh):
+            # every key is kept: append first (in the rotation kernel), then attend over the cache alone
+            if self.position is not None:
+                self.position.apply(qkv, self.nh, self.nkvh, ctx, append=append)
+            elif append:
+                kernels.rope_append(qkv, self.nh, self.nkvh, self.dh, tok_pos=ctx.tok_pos, append=append, err=ctx.err)
+            out = kernels.attention_prefill(*common, ctx.max_new, self.window, self.scale, all_from_cache=True)
         else:
             if self.position is not None:
                 self.position.apply(qkv, self.nh, self.nkvh, ctx, append=None)

@@ -436,3 +436,31 @@ def test_attention_decode_fused_rotation_and_append(nh, nkvh, dh, window, splits
     # the same kernel twice more: the counters of the slice merge must be back at zero
     got2 = kernels.attention_decode(*args(q1, k1, v1), n_splits=splits)
     assert torch.equal(got2, want)
+
+
+@pytest.mark.parametrize("nh,nkvh,dh,window", [(4, 2, 64, None), (12, 2, 128, None), (3, 3, 64, 70), (8, 1, 128, 5), (2, 1, 128, 200)])
+def test_attention_prefill_from_cache_tcgen05(nh, nkvh, dh, window):
+    """Prefill attention with every key read from the cache (the tcgen05 kernel for head sizes 64
+    and 128): sequences of unequal lengths, some with cached history, against the plain formula."""
+    from llaisys_b200 import kernels
+    dtype = torch.bfloat16
+    lens_before, news = [0, 130, 64, 5, 0], [100, 37, 1, 200, 300]
+    d, want = _attention_case(dtype, nh, nkvh, dh, lens_before, news, window, seed=nh * dh + 1)
+    T = sum(news)
+    tok_seq = torch.tensor(np.repeat(np.arange(5), news), dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor(np.concatenate([np.arange(l, l + n) for l, n in zip(lens_before, news)]), dtype=torch.int32, device=DEV)
+    width = d["table"].shape[1]
+    kernels.rope_append(d["qkv"], nh, nkvh, dh, tok_pos=tok_pos, err=torch.zeros(1, dtype=torch.int32, device=DEV), append=dict(
+        tok_seq=tok_seq, seq_start=d["seq_start"], seq_len_before=d["len_before"], kpool=d["kpool"], vpool=d["vpool"],
+        page_table=d["table"], ring=width))
+    args = (d["qkv"], nh, nkvh, dh, d["kpool"], d["vpool"], d["table"], width, d["seq_start"], d["len_before"], 5, max(news),
+            window, 1 / math.sqrt(dh))
+    got = kernels.attention_prefill(*args, all_from_cache=True)
+    assert kernels.tc_error(DEV) == 0
+    _close(got, want, dtype, atol=6e-3)
+    # and the same through the mma.sync kernel
+    kernels.ops.TC_ATTENTION = False
+    try:
+        _close(kernels.attention_prefill(*args, all_from_cache=True), want, dtype, atol=6e-3)
+    finally:
+        kernels.ops.TC_ATTENTION = True
