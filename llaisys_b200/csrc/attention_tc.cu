@@ -45,11 +45,11 @@ constexpr int ROW_THREADS = 128;           // warps 0-3: one query row each
 constexpr int THREADS = 160;               // warp 4: copies and matrix products
 constexpr int Q_BYTES = BQ * DH * 2;       // [NBLK][128 rows][128 B]
 constexpr int KV_BYTES = BKV * DH * 2;     // [NBLK][64 rows][128 B]
-constexpr int P_BYTES = BQ * BKV * 2;      // [128 rows][128 B]
-constexpr int KV_STAGES = 2;
-constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + KV_STAGES * KV_BYTES, OFF_P = OFF_V + KV_STAGES * KV_BYTES;
-constexpr int OFF_BAR = OFF_P + P_BYTES;
-constexpr int SMEM_BYTES = OFF_BAR + 80;
+constexpr int KV_STAGES = 2;               // value stages (and score buffers)
+constexpr int K_STAGES = 3;                // key stages
+constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + K_STAGES * KV_BYTES;
+constexpr int OFF_BAR = OFF_V + KV_STAGES * KV_BYTES;
+constexpr int SMEM_BYTES = OFF_BAR + 112;
 constexpr int TMEM_COLS = 256;             // S: two buffers at columns [0, 64) and [64, 128); O: columns [128, 128 + DH)
 constexpr int O_COL = 128;
 constexpr float BASE_STEP = 8.f;           // the exponent base follows the maximum in steps larger than this (log2)
@@ -80,19 +80,24 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
                  : "=r"(done) : "r"(bar), "r"(parity) : "memory");
     return done != 0;
 }
-// Bounded wait; gives up early when another thread of the CTA has already given up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+// Bounded wait of a whole (converged) warp: every lane polls and the vote keeps the control flow uniform, so
+// either every lane goes on or none does and the warp-wide instructions that follow never run with lanes
+// missing.  Gives up early when another warp of the CTA has already given up.  (Measured: a satisfied wait
+// costs 60 cycles this way and 300 when one lane polls in a divergent branch and a shuffle spreads the result.)
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
     for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
-        if (mbar_try(bar, parity)) return true;
-        if ((i & 255u) == 255u && *abort_flag) return false;
+        if (__all_sync(0xffffffffu, mbar_try(bar, parity))) return true;
+        if ((i & 255u) == 255u && __any_sync(0xffffffffu, *abort_flag != 0)) return false;
     }
     *abort_flag = 1;
     return false;
 }
-// The same for a whole (converged) warp: either every lane goes on or none does, so that the
-// warp-wide tensor-memory instructions that follow never run with lanes missing.
-__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-    return !__any_sync(0xffffffffu, !mbar_wait(bar, parity, abort_flag));
+// True in exactly one lane of a converged warp.  The compiler knows that the code under it runs in one
+// thread, which lets it feed the tensor-core and copy instructions from uniform registers directly.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -112,13 +117,18 @@ __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t addr, uint32_t lbo) {
     return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
-__device__ __forceinline__ uint32_t idesc_f16(int n, bool b_mn_major) {
+__host__ __device__ constexpr uint32_t idesc_f16(int n, bool b_mn_major) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((uint32_t)(n >> 3) << 17) |
            ((uint32_t)(BQ >> 4) << 24);
 }
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// the same with the A operand in tensor memory (row r in lane r, two 16-bit elements to a 32-bit column)
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -175,30 +185,34 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, TcAttnParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t base = smem_u32(smem);
-    // barriers: Q landed; K / V stage landed; score buffer written; P V done; P stored by all rows
-    const uint32_t bar_q = base + OFF_BAR, bar_k = bar_q + 8, bar_v = bar_k + 8 * KV_STAGES, bar_s = bar_v + 8 * KV_STAGES,
-                   bar_o = bar_s + 16, bar_p = bar_o + 8;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + 72);
-    volatile int* s_abort = reinterpret_cast<volatile int*>(smem + OFF_BAR + 76);
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // barriers: Q landed; K / V stage landed; score buffer written; P V done; P of a score buffer stored by all rows
+    // (one per buffer: the rows may be a tile ahead of the issuing warp); the last P V done.
+    // A waiter must never be a whole phase behind or ahead of its barrier, or the parity would lie: hence the
+    // pairs, and a barrier of its own for the end.
+    const uint32_t bar_q = base + OFF_BAR, bar_k = bar_q + 8, bar_v = bar_k + 8 * K_STAGES, bar_s = bar_v + 8 * KV_STAGES,
+                   bar_o = bar_s + 16, bar_p = bar_o + 16, bar_done = bar_p + 16;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + 104);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(smem + OFF_BAR + 108);
+    const int tid = threadIdx.x, warp = tid >> 5;
 
     if (tid == 0) {
         *s_abort = (base & 1023u) ? 1 : 0;          // the swizzled tiles need a 1024-byte aligned base
         if (*s_abort) atomicExch(p.err, ERR_ATTN_TC_ALIGN);
         mbar_init(bar_q, 1);
+        for (int s = 0; s < K_STAGES; ++s) mbar_init(bar_k + 8 * s, 1);
         for (int s = 0; s < KV_STAGES; ++s) {
-            mbar_init(bar_k + 8 * s, 1);
             mbar_init(bar_v + 8 * s, 1);
             mbar_init(bar_s + 8 * s, 1);
+            mbar_init(bar_p + 8 * s, ROW_THREADS);
+            mbar_init(bar_o + 8 * s, 1);
         }
-        mbar_init(bar_o, 1);
-        mbar_init(bar_p, ROW_THREADS);
+        mbar_init(bar_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 0) {
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(base + OFF_BAR + 72), "r"((uint32_t)TMEM_COLS) : "memory");
+                     ::"r"(base + OFF_BAR + 104), "r"((uint32_t)TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -221,79 +235,94 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     bool failed = false;
 
     if (warp == 4) {
-        // ================================================= copies and matrix products (lane 0 issues)
-        auto issue_k = [&](int i) {
-            const int s = i % KV_STAGES, row = (table[tile_lo + i] * p.nkvh + kvh) * BKV;
-            mbar_expect_tx(bar_k + 8 * s, KV_BYTES);
+        // ================================================= copies and matrix products (one elected lane issues)
+        // Descriptors are made once; an instruction's own differs from them by a constant.  (Built per
+        // instruction, the address arithmetic of the single issuing thread cost more than the products.)
+        const uint64_t q_desc = desc_kmajor(base), k_desc0 = desc_kmajor(base + OFF_K),
+                       v_desc0 = desc_mnmajor(base + OFF_V, BKV * 128);
+        constexpr uint32_t IDESC_S = idesc_f16(BKV, false), IDESC_O = idesc_f16(DH, true);
+        auto page_row = [&](int i) { return i < n_tiles ? (table[tile_lo + i] * p.nkvh + kvh) * BKV : 0; };
+        auto issue_k = [&](int stage, int row) {
+            mbar_expect_tx(bar_k + 8 * stage, KV_BYTES);
 #pragma unroll
             for (int blk = 0; blk < NBLK; ++blk)
-                tma_load_2d(base + OFF_K + s * KV_BYTES + blk * (BKV * 128), &map_k, bar_k + 8 * s, blk * 64, row);
+                tma_load_2d(base + OFF_K + stage * KV_BYTES + blk * (BKV * 128), &map_k, bar_k + 8 * stage, blk * 64, row);
         };
-        auto issue_v = [&](int i) {
-            const int s = i % KV_STAGES, row = (table[tile_lo + i] * p.nkvh + kvh) * BKV;
-            mbar_expect_tx(bar_v + 8 * s, KV_BYTES);
+        auto issue_v = [&](int stage, int row) {
+            mbar_expect_tx(bar_v + 8 * stage, KV_BYTES);
 #pragma unroll
             for (int blk = 0; blk < NBLK; ++blk)
-                tma_load_2d(base + OFF_V + s * KV_BYTES + blk * (BKV * 128), &map_v, bar_v + 8 * s, blk * 64, row);
+                tma_load_2d(base + OFF_V + stage * KV_BYTES + blk * (BKV * 128), &map_v, bar_v + 8 * stage, blk * 64, row);
         };
-        const uint32_t idesc_s = idesc_f16(BKV, false), idesc_o = idesc_f16(DH, true);
-        // S(i) = Q K(i)^T into score buffer i % 2; the keys must have landed
-        auto issue_qk = [&](int i) {
-            const int s = i % KV_STAGES;
+        // S = Q K^T of the keys in `stage` into score buffer `buf`
+        auto issue_qk = [&](int stage, int buf) {
+            const uint64_t kd = k_desc0 + (uint64_t)(stage * (KV_BYTES >> 4));
+            const uint32_t d = tmem + buf * BKV;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-            for (int ks = 0; ks < DH / 16; ++ks) {
-                uint32_t qa = base + (ks / 4) * (BQ * 128) + (ks % 4) * 32;
-                uint32_t ka = base + OFF_K + s * KV_BYTES + (ks / 4) * (BKV * 128) + (ks % 4) * 32;
-                umma(tmem + s * BKV, desc_kmajor(qa), desc_kmajor(ka), idesc_s, ks > 0);
-            }
-            umma_commit(bar_s + 8 * s);
+            for (int ks = 0; ks < DH / 16; ++ks)
+                umma(d, q_desc + (uint64_t)(((ks / 4) * (BQ * 128) + (ks % 4) * 32) >> 4),
+                     kd + (uint64_t)(((ks / 4) * (BKV * 128) + (ks % 4) * 32) >> 4), IDESC_S, ks > 0 ? 1u : 0u);
+            umma_commit(bar_s + 8 * buf);
         };
+        int r1 = page_row(1), r2 = page_row(2), r3 = page_row(3);     // page rows of tiles i + 1, i + 2, i + 3
         if (n_tiles > 0) {
-            if (lane == 0) {
+            if (elect_one()) {
                 mbar_expect_tx(bar_q, Q_BYTES);
 #pragma unroll
                 for (int blk = 0; blk < NBLK; ++blk)
                     tma_load_2d(base + blk * (BQ * 128), &map_q, bar_q, head * DH + blk * 64, tok0 + t0);
-                for (int i = 0; i < min(KV_STAGES, n_tiles); ++i) { issue_k(i); issue_v(i); }
+                const int r0 = page_row(0);
+                issue_k(0, r0);
+                issue_v(0, r0);
+                if (n_tiles > 1) { issue_k(1, r1); issue_v(1, r1); }
+                if (n_tiles > 2) issue_k(2, r2);
             }
             failed = !warp_wait(bar_q, 0, s_abort);
-            for (int i = 0; i < min(KV_STAGES, n_tiles) && !failed; ++i) {
+            for (int i = 0; i < min(2, n_tiles) && !failed; ++i) {
                 failed = !warp_wait(bar_k + 8 * i, 0, s_abort);
-                if (!failed && lane == 0) issue_qk(i);
+                if (!failed && elect_one()) issue_qk(i, i);
                 __syncwarp();
             }
         }
+        int k_stage = 0, k_phase = 0;                   // key stage and phase of tile i; tile i + 2 sits in stage k2
         for (int i = 0; i < n_tiles && !failed; ++i) {
-            const int s = i % KV_STAGES;
-            const uint32_t ph = (i / KV_STAGES) & 1;
-            // S(i) is complete: the key stage of tile i is free for tile i + 2
-            if (!warp_wait(bar_s + 8 * s, ph, s_abort)) { failed = true; break; }
-            if (lane == 0 && i + 2 < n_tiles) issue_k(i + 2);
-            // P V of tile i - 1 is complete: its value stage is free for tile i + 1
-            if (i > 0) {
-                if (!warp_wait(bar_o, (i - 1) & 1, s_abort)) { failed = true; break; }
-                if (lane == 0 && i + 1 < n_tiles && i + 1 >= KV_STAGES) issue_v(i + 1);
-            }
-            // every row has read S(i), brought O to its base and stored P(i)
-            if (!warp_wait(bar_p, i & 1, s_abort)) { failed = true; break; }
+            const int s = i & 1;                        // score buffer and value stage of tile i
+            const uint32_t ph = (i >> 1) & 1;
+            const int k2 = k_stage == 0 ? 2 : k_stage - 1;
+            const int k2_phase = k_stage == 0 ? k_phase : k_phase ^ 1;      // (i + 2) / 3 is i / 3 or one more
+            const int r4 = page_row(i + 4);             // for the next round; its latency hides behind the waits
+            // every row has read S(i), brought O to its base and stored P(i): the product can go, and the key
+            // stage of tile i is free (the rows saw S(i), so Q K^T of tile i is done)
+            if (!warp_wait(bar_p + 8 * s, ph, s_abort)) { failed = true; break; }
             if (!warp_wait(bar_v + 8 * s, ph, s_abort)) { failed = true; break; }
-            if (lane == 0) {
+            if (elect_one()) {
+                const uint64_t vd = v_desc0 + (uint64_t)(s * (KV_BYTES >> 4));
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
-                for (int ks = 0; ks < BKV / 16; ++ks) {
-                    uint32_t pa = base + OFF_P + ks * 32;
-                    uint32_t va = base + OFF_V + s * KV_BYTES + ks * (16 * 128);
-                    umma(tmem + O_COL, desc_kmajor(pa), desc_mnmajor(va, BKV * 128), idesc_o, (i > 0 || ks > 0) ? 1u : 0u);
-                }
-                umma_commit(bar_o);
+                for (int ks = 0; ks < BKV / 16; ++ks)
+                    umma_ts(tmem + O_COL, tmem + s * BKV + ks * 8, vd + (uint64_t)((ks * 16 * 128) >> 4), IDESC_O,
+                            (i > 0 || ks > 0) ? 1u : 0u);
+                umma_commit(bar_o + 8 * s);
+                if (i == n_tiles - 1) umma_commit(bar_done);
             }
             __syncwarp();
             if (i + 2 < n_tiles) {
-                if (!warp_wait(bar_k + 8 * s, ph ^ 1, s_abort)) { failed = true; break; }
-                if (lane == 0) issue_qk(i + 2);
+                if (!warp_wait(bar_k + 8 * k2, k2_phase, s_abort)) { failed = true; break; }
+                if (elect_one()) issue_qk(k2, s);
                 __syncwarp();
             }
+            // ---- refill: keys of tile i + 3 into the stage of tile i; values of tile i + 1 once P V of tile
+            // i - 1 is done
+            if (i + 3 < n_tiles && elect_one()) issue_k(k_stage, r3);
+            __syncwarp();
+            if (i > 0 && i + 1 < n_tiles) {
+                if (!warp_wait(bar_o + 8 * (s ^ 1), ((i - 1) >> 1) & 1, s_abort)) { failed = true; break; }
+                if (elect_one()) issue_v(s ^ 1, r1);
+                __syncwarp();
+            }
+            r1 = r2; r2 = r3; r3 = r4;
+            if (++k_stage == K_STAGES) { k_stage = 0; k_phase ^= 1; }
         }
     } else {
         // ================================================= softmax: thread r owns query row r
@@ -302,7 +331,6 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const float scale_log2 = p.scale * 1.4426950408889634f;
         const uint64_t scale2 = twice(scale_log2);
         const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
-        uint8_t* prow = smem + OFF_P + tid * 128;
         float m = -INFINITY, l = 0.f;                               // m: the exponent base of the row
 
         for (int i = 0; i < n_tiles && !failed; ++i) {
@@ -348,29 +376,26 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             }
             l = l * alpha + (sum[0] + sum[1]) + (sum[2] + sum[3]);
 
-            // ---- P V of tile i - 1 is done: the accumulator can be scaled, the P buffer written
-            if (i > 0) {
-                if (!warp_wait(bar_o, (i - 1) & 1, s_abort)) { failed = true; break; }
+            // ---- a row's base moved: once P V of tile i - 1 is done, its accumulator is scaled to the new base
+            if (i > 0 && __any_sync(0xffffffffu, move)) {
+                if (!warp_wait(bar_o + 8 * ((i - 1) & 1), ((i - 1) >> 1) & 1, s_abort)) { failed = true; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                if (__any_sync(0xffffffffu, move)) {
 #pragma unroll
-                    for (int c0 = 0; c0 < DH; c0 += 32) {
-                        uint32_t v[32];
-                        tmem_ld16_nowait(lane_addr + O_COL + c0, v);
-                        tmem_ld16_nowait(lane_addr + O_COL + c0 + 16, v + 16);
-                        tmem_wait();
+                for (int c0 = 0; c0 < DH; c0 += 32) {
+                    uint32_t v[32];
+                    tmem_ld16_nowait(lane_addr + O_COL + c0, v);
+                    tmem_ld16_nowait(lane_addr + O_COL + c0 + 16, v + 16);
+                    tmem_wait();
 #pragma unroll
-                        for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
-                        tmem_st16(lane_addr + O_COL + c0, v);
-                        tmem_st16(lane_addr + O_COL + c0 + 16, v + 16);
-                    }
-                    tmem_wait_st();
+                    for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(__uint_as_float(v[e]) * alpha);
+                    tmem_st16(lane_addr + O_COL + c0, v);
+                    tmem_st16(lane_addr + O_COL + c0 + 16, v + 16);
                 }
             }
-            // ---- P(i) into shared memory; 8 keys = one 16-byte piece, whose place is its index XOR (row mod 8)
-#pragma unroll
-            for (int c = 0; c < BKV / 8; ++c)
-                *reinterpret_cast<uint4*>(prow + ((c ^ (tid & 7)) * 16)) = make_uint4(sr[4 * c], sr[4 * c + 1], sr[4 * c + 2], sr[4 * c + 3]);
+            // ---- P(i) takes the place of the row's scores in tensor memory: 64 keys in 32 columns
+            tmem_st16(lane_addr + s * BKV, sr);
+            tmem_st16(lane_addr + s * BKV + 16, sr + 16);
+            tmem_wait_st();
             // rows of the page beyond the last position of this block were never written for this sequence:
             // a zero probability must meet a finite value
             if (p0 + BKV - 1 > last_pos) {
@@ -381,12 +406,12 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     *reinterpret_cast<uint4*>(smem + OFF_V + s * KV_BYTES + (rest / 8) * (BKV * 128) + j * 128 + (rest % 8) * 16) =
                         make_uint4(0, 0, 0, 0);
                 }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the zeroed rows before the tensor core reads them
             }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // P (and the zeroed rows) before the tensor core reads them
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(bar_p);
+            mbar_arrive(bar_p + 8 * s);
         }
-        if (!failed && n_tiles > 0) failed = !warp_wait(bar_o, (n_tiles - 1) & 1, s_abort);
+        if (!failed && n_tiles > 0) failed = !warp_wait(bar_done, 0, s_abort);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (n_tiles > 0 && !__any_sync(0xffffffffu, failed)) {
             const float inv = 1.0f / l;
