@@ -49,7 +49,7 @@ constexpr int KV_STAGES = 2;               // value stages (and score buffers)
 constexpr int K_STAGES = 3;                // key stages
 constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + K_STAGES * KV_BYTES;
 constexpr int OFF_BAR = OFF_V + KV_STAGES * KV_BYTES;
-constexpr int SMEM_BYTES = OFF_BAR + 112;
+constexpr int SMEM_BYTES = OFF_BAR + 80;
 constexpr int TMEM_COLS = 256;             // S: two buffers at columns [0, 64) and [64, 128); O: columns [128, 128 + DH)
 constexpr int O_COL = 128;
 constexpr float BASE_STEP = 8.f;           // the exponent base follows the maximum in steps larger than this (log2)
@@ -185,25 +185,26 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, TcAttnParams p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     const uint32_t base = smem_u32(smem);
-    // barriers: Q landed; K / V stage landed; score buffer written; P V done; P of a score buffer stored by all rows
-    // (one per buffer: the rows may be a tile ahead of the issuing warp); the last P V done.
+    // barriers: Q landed; the first two key tiles landed; score buffer written; P V done; tile ready (one per score
+    // buffer, the rows may be a tile ahead of the issuing warp): P stored by all 128 rows, the tile's values landed,
+    // the keys of the tile two ahead landed, so that one wait of the issuing warp covers all that its two products
+    // need; the last P V done.
     // A waiter must never be a whole phase behind or ahead of its barrier, or the parity would lie: hence the
     // pairs, and a barrier of its own for the end.
-    const uint32_t bar_q = base + OFF_BAR, bar_k = bar_q + 8, bar_v = bar_k + 8 * K_STAGES, bar_s = bar_v + 8 * KV_STAGES,
-                   bar_o = bar_s + 16, bar_p = bar_o + 16, bar_done = bar_p + 16;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + 104);
-    volatile int* s_abort = reinterpret_cast<volatile int*>(smem + OFF_BAR + 108);
+    const uint32_t bar_q = base + OFF_BAR, bar_k01 = bar_q + 8, bar_s = bar_k01 + 8, bar_o = bar_s + 16, bar_p = bar_o + 16,
+                   bar_done = bar_p + 16;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + 72);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(smem + OFF_BAR + 76);
     const int tid = threadIdx.x, warp = tid >> 5;
 
     if (tid == 0) {
         *s_abort = (base & 1023u) ? 1 : 0;          // the swizzled tiles need a 1024-byte aligned base
         if (*s_abort) atomicExch(p.err, ERR_ATTN_TC_ALIGN);
         mbar_init(bar_q, 1);
-        for (int s = 0; s < K_STAGES; ++s) mbar_init(bar_k + 8 * s, 1);
+        mbar_init(bar_k01, 1);
         for (int s = 0; s < KV_STAGES; ++s) {
-            mbar_init(bar_v + 8 * s, 1);
             mbar_init(bar_s + 8 * s, 1);
-            mbar_init(bar_p + 8 * s, ROW_THREADS);
+            mbar_init(bar_p + 8 * s, ROW_THREADS + 2);          // the rows, the value copy, the key copy
             mbar_init(bar_o + 8 * s, 1);
         }
         mbar_init(bar_done, 1);
@@ -212,7 +213,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (warp == 0) {
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(base + OFF_BAR + 104), "r"((uint32_t)TMEM_COLS) : "memory");
+                     ::"r"(base + OFF_BAR + 72), "r"((uint32_t)TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -242,17 +243,18 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        v_desc0 = desc_mnmajor(base + OFF_V, BKV * 128);
         constexpr uint32_t IDESC_S = idesc_f16(BKV, false), IDESC_O = idesc_f16(DH, true);
         auto page_row = [&](int i) { return i < n_tiles ? (table[tile_lo + i] * p.nkvh + kvh) * BKV : 0; };
-        auto issue_k = [&](int stage, int row) {
-            mbar_expect_tx(bar_k + 8 * stage, KV_BYTES);
+        // keys / values of one tile into `stage`; the bytes count on `bar`, which also gets one arrival
+        auto issue_k = [&](int stage, int row, uint32_t bar) {
+            mbar_expect_tx(bar, KV_BYTES);
 #pragma unroll
             for (int blk = 0; blk < NBLK; ++blk)
-                tma_load_2d(base + OFF_K + stage * KV_BYTES + blk * (BKV * 128), &map_k, bar_k + 8 * stage, blk * 64, row);
+                tma_load_2d(base + OFF_K + stage * KV_BYTES + blk * (BKV * 128), &map_k, bar, blk * 64, row);
         };
-        auto issue_v = [&](int stage, int row) {
-            mbar_expect_tx(bar_v + 8 * stage, KV_BYTES);
+        auto issue_v = [&](int stage, int row, uint32_t bar) {
+            mbar_expect_tx(bar, KV_BYTES);
 #pragma unroll
             for (int blk = 0; blk < NBLK; ++blk)
-                tma_load_2d(base + OFF_V + stage * KV_BYTES + blk * (BKV * 128), &map_v, bar_v + 8 * stage, blk * 64, row);
+                tma_load_2d(base + OFF_V + stage * KV_BYTES + blk * (BKV * 128), &map_v, bar, blk * 64, row);
         };
         // S = Q K^T of the keys in `stage` into score buffer `buf`
         auto issue_qk = [&](int stage, int buf) {
@@ -273,29 +275,47 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 for (int blk = 0; blk < NBLK; ++blk)
                     tma_load_2d(base + blk * (BQ * 128), &map_q, bar_q, head * DH + blk * 64, tok0 + t0);
                 const int r0 = page_row(0);
-                issue_k(0, r0);
-                issue_v(0, r0);
-                if (n_tiles > 1) { issue_k(1, r1); issue_v(1, r1); }
-                if (n_tiles > 2) issue_k(2, r2);
+                // the first two key tiles have a barrier of their own (one arrival, the bytes of both)
+                mbar_expect_tx(bar_k01, KV_BYTES * min(2, n_tiles));
+#pragma unroll
+                for (int blk = 0; blk < NBLK; ++blk) {
+                    tma_load_2d(base + OFF_K + blk * (BKV * 128), &map_k, bar_k01, blk * 64, r0);
+                    if (n_tiles > 1) tma_load_2d(base + OFF_K + KV_BYTES + blk * (BKV * 128), &map_k, bar_k01, blk * 64, r1);
+                }
+                // tile 0: its values and the keys of tile 2; tile 1: its values (the keys of tile 3 follow in round 0)
+                issue_v(0, r0, bar_p);
+                if (n_tiles > 2) issue_k(2, r2, bar_p); else mbar_arrive(bar_p);
+                if (n_tiles > 1) issue_v(1, r1, bar_p + 8);
             }
-            failed = !warp_wait(bar_q, 0, s_abort);
-            for (int i = 0; i < min(2, n_tiles) && !failed; ++i) {
-                failed = !warp_wait(bar_k + 8 * i, 0, s_abort);
-                if (!failed && elect_one()) issue_qk(i, i);
-                __syncwarp();
+            failed = !warp_wait(bar_q, 0, s_abort) || !warp_wait(bar_k01, 0, s_abort);
+            if (!failed && elect_one()) {
+                issue_qk(0, 0);
+                if (n_tiles > 1) issue_qk(1, 1);
             }
+            __syncwarp();
         }
-        int k_stage = 0, k_phase = 0;                   // key stage and phase of tile i; tile i + 2 sits in stage k2
+        int k_stage = 0;                                // key stage of tile i; tile i + 2 sits in stage k2
         for (int i = 0; i < n_tiles && !failed; ++i) {
             const int s = i & 1;                        // score buffer and value stage of tile i
             const uint32_t ph = (i >> 1) & 1;
             const int k2 = k_stage == 0 ? 2 : k_stage - 1;
-            const int k2_phase = k_stage == 0 ? k_phase : k_phase ^ 1;      // (i + 2) / 3 is i / 3 or one more
-            const int r4 = page_row(i + 4);             // for the next round; its latency hides behind the waits
-            // every row has read S(i), brought O to its base and stored P(i): the product can go, and the key
-            // stage of tile i is free (the rows saw S(i), so Q K^T of tile i is done)
+            const int r4 = page_row(i + 4);             // for the next round; its latency hides behind the wait
+            // every row has read S(i), brought O to its base and stored P(i); V(i) and K(i + 2) have landed.  The
+            // key stage of tile i is free as well (the rows saw S(i), so Q K^T of tile i is done).
             if (!warp_wait(bar_p + 8 * s, ph, s_abort)) { failed = true; break; }
-            if (!warp_wait(bar_v + 8 * s, ph, s_abort)) { failed = true; break; }
+            // rows of the last page beyond the last position of this block were never written for this sequence:
+            // a zero probability must meet a finite value
+            const int p0 = (tile_lo + i) * BKV;
+            if (p0 + BKV - 1 > last_pos) {
+                const int j0 = last_pos - p0 + 1;
+                for (int idx = tid - ROW_THREADS; idx < (BKV - j0) * NBLK * 8; idx += 32) {
+                    int j = j0 + idx / (NBLK * 8), rest = idx % (NBLK * 8);
+                    *reinterpret_cast<uint4*>(smem + OFF_V + s * KV_BYTES + (rest / 8) * (BKV * 128) + j * 128 + (rest % 8) * 16) =
+                        make_uint4(0, 0, 0, 0);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // before the tensor core reads them
+                __syncwarp();
+            }
             if (elect_one()) {
                 const uint64_t vd = v_desc0 + (uint64_t)(s * (KV_BYTES >> 4));
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -305,24 +325,21 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                             (i > 0 || ks > 0) ? 1u : 0u);
                 umma_commit(bar_o + 8 * s);
                 if (i == n_tiles - 1) umma_commit(bar_done);
+                if (i + 2 < n_tiles) issue_qk(k2, s);
+                // ---- refill for tile i + 1: the keys of tile i + 3 into the stage of tile i
+                if (i + 1 < n_tiles) {
+                    if (i + 3 < n_tiles) issue_k(k_stage, r3, bar_p + 8 * (s ^ 1)); else mbar_arrive(bar_p + 8 * (s ^ 1));
+                }
             }
             __syncwarp();
-            if (i + 2 < n_tiles) {
-                if (!warp_wait(bar_k + 8 * k2, k2_phase, s_abort)) { failed = true; break; }
-                if (elect_one()) issue_qk(k2, s);
-                __syncwarp();
-            }
-            // ---- refill: keys of tile i + 3 into the stage of tile i; values of tile i + 1 once P V of tile
-            // i - 1 is done
-            if (i + 3 < n_tiles && elect_one()) issue_k(k_stage, r3);
-            __syncwarp();
+            // ---- and its values, once P V of tile i - 1 has left their stage (tile 1's were sent at the start)
             if (i > 0 && i + 1 < n_tiles) {
                 if (!warp_wait(bar_o + 8 * (s ^ 1), ((i - 1) >> 1) & 1, s_abort)) { failed = true; break; }
-                if (elect_one()) issue_v(s ^ 1, r1);
+                if (elect_one()) issue_v(s ^ 1, r1, bar_p + 8 * (s ^ 1));
                 __syncwarp();
             }
             r1 = r2; r2 = r3; r3 = r4;
-            if (++k_stage == K_STAGES) { k_stage = 0; k_phase ^= 1; }
+            if (++k_stage == K_STAGES) k_stage = 0;
         }
     } else {
         // ================================================= softmax: thread r owns query row r
@@ -396,18 +413,6 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             tmem_st16(lane_addr + s * BKV, sr);
             tmem_st16(lane_addr + s * BKV + 16, sr + 16);
             tmem_wait_st();
-            // rows of the page beyond the last position of this block were never written for this sequence:
-            // a zero probability must meet a finite value
-            if (p0 + BKV - 1 > last_pos) {
-                if (!warp_wait(bar_v + 8 * s, (i / KV_STAGES) & 1, s_abort)) { failed = true; break; }
-                const int j0 = last_pos - p0 + 1;
-                for (int idx = tid; idx < (BKV - j0) * NBLK * 8; idx += ROW_THREADS) {
-                    int j = j0 + idx / (NBLK * 8), rest = idx % (NBLK * 8);
-                    *reinterpret_cast<uint4*>(smem + OFF_V + s * KV_BYTES + (rest / 8) * (BKV * 128) + j * 128 + (rest % 8) * 16) =
-                        make_uint4(0, 0, 0, 0);
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // the zeroed rows before the tensor core reads them
-            }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(bar_p + 8 * s);
         }
