@@ -44,6 +44,18 @@ QWEN2_1_5B = {
     "use_sliding_window": False, "sliding_window": 4096, "max_window_layers": 21,
     "eos_token_id": 151643,
 }
+# The other two large shapes that xsmccc/llaisys' Qwen2 code path serves; `--shape` selects them for
+# measurements beside the default one (the reported metric stays that of the default shape).
+SHAPES = {
+    "1.5b": ("Qwen2-1.5B shape (DeepSeek-R1-Distill-Qwen-1.5B config)", QWEN2_1_5B),
+    "7b": ("Qwen2.5-7B shape", dict(QWEN2_1_5B, num_hidden_layers=28, hidden_size=3584, num_attention_heads=28,
+                                    num_key_value_heads=4, intermediate_size=18944, vocab_size=152064,
+                                    max_position_embeddings=32768, rope_theta=1e6, max_window_layers=28)),
+    "32b": ("Qwen2.5-32B shape", dict(QWEN2_1_5B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=40,
+                                      num_key_value_heads=8, intermediate_size=27648, vocab_size=152064,
+                                      max_position_embeddings=32768, rope_theta=1e6, rms_norm_eps=1e-5,
+                                      max_window_layers=64)),
+}
 PROMPT_LEN, CONTEXT, PREFILL_TOKENS = 2048, 4096, 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
@@ -157,6 +169,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--shape", choices=sorted(SHAPES), default="1.5b", help="layer sizes (default: the benchmark's)")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / batch 64 points and the end-to-end run")
     ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
                     help="for a profiler: warm up, then run two uncaptured steps of this kind between "
@@ -184,7 +197,8 @@ def main() -> int:
 
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
-    cfg_dict = dict(QWEN2_1_5B)
+    shape_name, shape = SHAPES[args.shape]
+    cfg_dict = dict(shape)
     full_layers = cfg_dict["num_hidden_layers"]
     layers = args.layers or full_layers
     cfg_dict["num_hidden_layers"] = layers
@@ -292,15 +306,15 @@ def main() -> int:
                "h2d_bytes_per_step": 4 * meta_ints, "d2h_bytes_per_step": 4 * args.batch}
 
     out = {
-        "metric": "decode tok/s @ batch 8 (Qwen2-1.5B shape, bf16, 2048-token prompts, context 4096)",
+        "metric": f"decode tok/s @ batch {args.batch} ({shape_name.split(' shape')[0]} shape, bf16, 2048-token prompts, context 4096)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random weights N(0,0.02), seeded uniform-random token ids",
-        "config": {"model": "Qwen2-1.5B shape (DeepSeek-R1-Distill-Qwen-1.5B config)", "layers": layers,
+        "config": {"model": shape_name, "layers": layers,
                    "layers_of_config": full_layers, "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
                    "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size,
                    "vocab": cfg.vocab_size, "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN,
-                   "parallelism": "single GPU", "l2": "no flush: each step streams 3.1 GB of weights, larger than L2",
+                   "parallelism": "single GPU", "l2": f"no flush: each step streams {weight_bytes / 1e9:.1f} GB of weights, larger than L2",
                    "peaks": pk_src},
         "clocks": clocks, "gpu_launches": launches, "prefill": prefill, "roofline": roofline, "points": points,
     }
