@@ -325,10 +325,10 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
     const float* cs = p.rope_cos ? p.rope_cos + (size_t)min(pos, p.rope_rows - 1) * (DH / 2) : nullptr;
     const float* sn = p.rope_cos ? p.rope_sin + (size_t)min(pos, p.rope_rows - 1) * (DH / 2) : nullptr;
     int tile_lo = key_lo / TILE, tile_hi = pos / TILE + 1;
-    {
-        int n = tile_hi - tile_lo, per = (n + p.n_splits - 1) / p.n_splits;
-        tile_lo += blockIdx.x * per;
-        tile_hi = min(tile_hi, tile_lo + per);
+    {   // as even a share of the tiles as there is: the slowest block of a sequence sets the time of all
+        const int n = tile_hi - tile_lo, q = n / p.n_splits, r = n - q * p.n_splits, x = blockIdx.x;
+        tile_lo += x * q + min(x, r);
+        tile_hi = tile_lo + q + (x < r ? 1 : 0);
     }
     const int n_tiles = max(0, tile_hi - tile_lo);
 
@@ -338,27 +338,53 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
         if (i < n_tiles) issue_tile(src, tile_lo + i, key_lo, fetch_hi, ring.stage(i), tid);
         cp_async_commit();                                 // one group per stage, empty or not
     }
+    // The ring holds NST tiles; the pages of the block's next two tiles are asked into L2 now, so that their
+    // copies, which can start only when a stage is free, find them there (a page is contiguous per kv head).
+    // Only two: a block with a long walk (large batches) streams at full rate anyway, and asking for all its
+    // pages at once was measured to cost 5 % at batch 64.
+    for (int i = NST; i < min(n_tiles, NST + 2); ++i) {
+        const size_t off = paged_row(src.table, p.ring, (tile_lo + i) * TILE, kvh, p.nkvh, DH);
+        for (int c = tid * 64; c < TILE * DH; c += THREADS * 64) {          // 64 elements = one 128-byte line
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p.kpool + off + c));
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p.vpool + off + c));
+        }
+    }
+    // The query staging below gives each thread one pair index j of the rotation: its angle is fetched now.
+    constexpr int HALF = DH / 2, Q_ROWS_PER_PASS = THREADS / HALF, Q_PASSES = (16 + Q_ROWS_PER_PASS - 1) / Q_ROWS_PER_PASS;
+    const int qj = tid % HALF, qr0 = tid / HALF;
+    float q_co = 1.f, q_si = 0.f;
+    if (cs) { q_co = cs[qj]; q_si = sn[qj]; }
     if (p.append_new) llb_grid_dependency_sync();          // the projections are read from here on
 
-    // the query heads of this block, rotated if asked for, staged in shared memory behind the ring
+    // the new token's key and value (for the block that owns the last tile): loaded now, used at that tile
+    const bool owns_new = p.append_new && n_tiles > 0 && tile_hi - 1 == pos / TILE;
+    uint32_t new_k = 0, new_v = 0;
+    if (owns_new && tid * 2 < DH) {
+        const bf16* kn = p.k_new + (size_t)tok * p.row_stride + (size_t)kvh * DH;
+        const bf16* vn = p.v_new + (size_t)tok * p.row_stride + (size_t)kvh * DH;
+        new_k = cs ? rotated_pair(kn, tid * 2, cs, sn) : *reinterpret_cast<const uint32_t*>(kn + tid * 2);
+        new_v = *reinterpret_cast<const uint32_t*>(vn + tid * 2);
+    }
+    // the query heads of this block, rotated if asked for, staged in shared memory behind the ring: all loads
+    // of a thread are in flight together
     bf16* qs = reinterpret_cast<bf16*>(ring.ptr + NST * STAGE_BYTES);       // [16][DH + 8]
     {
-        constexpr int HALF = DH / 2;
         const bf16* qg = p.q + (size_t)tok * p.row_stride + (size_t)head0 * DH;
-        for (int i = tid; i < 16 * HALF; i += THREADS) {
-            int r = i / HALF, j = i - r * HALF;
-            float a = 0.f, c2 = 0.f;
-            if (r < n_heads) {
-                a = to_f32(qg[r * DH + j]);
-                c2 = to_f32(qg[r * DH + j + HALF]);
-                if (cs) {
-                    float co = cs[j], si = sn[j], ra = a * co - c2 * si, rb = c2 * co + a * si;
-                    a = ra;
-                    c2 = rb;
-                }
+        float qa[Q_PASSES], qb[Q_PASSES];
+#pragma unroll
+        for (int k = 0; k < Q_PASSES; ++k) {
+            const int r = qr0 + k * Q_ROWS_PER_PASS;
+            const bool in = qr0 < Q_ROWS_PER_PASS && r < n_heads;
+            qa[k] = in ? to_f32(qg[r * DH + qj]) : 0.f;
+            qb[k] = in ? to_f32(qg[r * DH + qj + HALF]) : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < Q_PASSES; ++k) {
+            const int r = qr0 + k * Q_ROWS_PER_PASS;
+            if (qr0 < Q_ROWS_PER_PASS && r < 16) {
+                qs[r * (DH + 8) + qj] = __float2bfloat16_rn(qa[k] * q_co - qb[k] * q_si);
+                qs[r * (DH + 8) + qj + HALF] = __float2bfloat16_rn(qb[k] * q_co + qa[k] * q_si);
             }
-            qs[r * (DH + 8) + j] = __float2bfloat16_rn(a);
-            qs[r * (DH + 8) + j + HALF] = __float2bfloat16_rn(c2);
         }
     }
     __syncthreads();
@@ -372,20 +398,17 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
     for (int i = 0; i < n_tiles; ++i) {
         cp_async_wait<NST - 1>();                       // this thread's copies of tile i have landed
         __syncthreads();                                   // ... and everyone else's
-        if (p.append_new && tile_lo + i == pos / TILE) {
-            // the new token's row: from the packed projections into this tile (and, once per kv head, into the cache)
-            const bf16* kn = p.k_new + (size_t)tok * p.row_stride + (size_t)kvh * DH;
-            const bf16* vn = p.v_new + (size_t)tok * p.row_stride + (size_t)kvh * DH;
+        if (owns_new && tile_lo + i == pos / TILE) {
+            // the new token's row into this tile (and, once per kv head, into the cache)
             uint8_t* krow = ring.stage_ptr(i) + (pos % TILE) * ROW_STRIDE;
-            size_t goff = paged_row(src.table, p.ring, pos, kvh, p.nkvh, DH);
-            for (int d = tid * 2; d < DH; d += THREADS * 2) {
-                uint32_t kk = cs ? rotated_pair(kn, d, cs, sn) : *reinterpret_cast<const uint32_t*>(kn + d);
-                uint32_t vv = *reinterpret_cast<const uint32_t*>(vn + d);
-                *reinterpret_cast<uint32_t*>(krow + d * 2) = kk;
-                *reinterpret_cast<uint32_t*>(krow + TILE_BYTES + d * 2) = vv;
+            const int d = tid * 2;
+            if (d < DH) {
+                *reinterpret_cast<uint32_t*>(krow + d * 2) = new_k;
+                *reinterpret_cast<uint32_t*>(krow + TILE_BYTES + d * 2) = new_v;
                 if (chunk == 0) {
-                    *reinterpret_cast<uint32_t*>(const_cast<bf16*>(p.kpool) + goff + d) = kk;
-                    *reinterpret_cast<uint32_t*>(const_cast<bf16*>(p.vpool) + goff + d) = vv;
+                    size_t goff = paged_row(src.table, p.ring, pos, kvh, p.nkvh, DH);
+                    *reinterpret_cast<uint32_t*>(const_cast<bf16*>(p.kpool) + goff + d) = new_k;
+                    *reinterpret_cast<uint32_t*>(const_cast<bf16*>(p.vpool) + goff + d) = new_v;
                 }
             }
             __syncthreads();
@@ -401,7 +424,8 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
 
     // ---- merge the four warps (each saw a quarter of the keys) through shared memory
     float* sm_ml = reinterpret_cast<float*>(ring.ptr);               // [4][16][2]
-    float* sm_o = sm_ml + 4 * 16 * 2;                                 // [4][16][DH]
+    float* sm_o = sm_ml + 4 * 16 * 2;                                 // [4][16][SO]; SO = DH + 8 keeps the rows' 8-byte
+    constexpr int SO = DH + 8;                                        // stores of a half-warp on distinct banks
     {
         int r0 = lane >> 2, c = (lane & 3) * 2;
         if ((lane & 3) == 0) {
@@ -412,15 +436,15 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
         }
 #pragma unroll
         for (int d = 0; d < DTILES; ++d) {
-            float* w0 = sm_o + (size_t)(warp * 16 + r0) * DH + d * 8 + c;
-            float* w1 = sm_o + (size_t)(warp * 16 + r0 + 8) * DH + d * 8 + c;
-            w0[0] = o[d][0]; w0[1] = o[d][1];
-            w1[0] = o[d][2]; w1[1] = o[d][3];
+            float* w0 = sm_o + (size_t)(warp * 16 + r0) * SO + d * 8 + c;
+            float* w1 = sm_o + (size_t)(warp * 16 + r0 + 8) * SO + d * 8 + c;
+            *reinterpret_cast<float2*>(w0) = make_float2(o[d][0], o[d][1]);
+            *reinterpret_cast<float2*>(w1) = make_float2(o[d][2], o[d][3]);
         }
     }
     __syncthreads();
     // merged over the four warps: fin_ml [16][2], fin_o [16][DH] (kept in shared memory for the cluster merge)
-    float* fin_ml = sm_o + 4 * 16 * DH;
+    float* fin_ml = sm_o + 4 * 16 * SO;
     float* fin_o = fin_ml + 16 * 2;
     for (int i = tid; i < n_heads * DH; i += THREADS) {
         int r = i / DH, d = i - r * DH;
@@ -432,9 +456,9 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
         for (int w = 0; w < 4; ++w) {
             float mw = sm_ml[(w * 16 + r) * 2];
             if (mw != -INFINITY) {
-                float f = exp2f(mw - M);
+                float f = fast_exp2(mw - M);
                 L += sm_ml[(w * 16 + r) * 2 + 1] * f;
-                acc += sm_o[(size_t)(w * 16 + r) * DH + d] * f;
+                acc += sm_o[(size_t)(w * 16 + r) * SO + d] * f;
             }
         }
         int head = head0 + r;
@@ -487,7 +511,7 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
             float L = 0.f, acc = 0.f;
 #pragma unroll
             for (int sp = 0; sp < 8; ++sp) {
-                float f = ms[sp] == -INFINITY ? 0.f : exp2f(ms[sp] - M);
+                float f = ms[sp] == -INFINITY ? 0.f : fast_exp2(ms[sp] - M);
                 L += ls[sp] * f;
                 acc += os[sp] * f;
             }
