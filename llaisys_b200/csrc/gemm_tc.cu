@@ -48,7 +48,7 @@ constexpr uint32_t WAIT_LIMIT = 1u << 22;
 constexpr uint64_t HINT_EVICT_FIRST = 0x12F0000000000000ull;
 constexpr uint64_t HINT_EVICT_LAST = 0x14F0000000000000ull;
 
-enum { ERR_TC_WAIT_FULL = 101, ERR_TC_WAIT_EMPTY = 102, ERR_TC_WAIT_ACC = 103 };
+enum { ERR_TC_WAIT_FULL = 101, ERR_TC_WAIT_EMPTY = 102, ERR_TC_WAIT_ACC = 103, ERR_TC_WAIT_RECV = 104 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -147,7 +147,13 @@ struct Smem {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * A_BYTES + B_BYTES;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int TOTAL = BAR_OFFSET + (2 * STAGES + 1) * 8 + 16 + 1024;   // + slack to align the base
+    // Single-accumulator tiles of up to 32 tokens reduce their cluster's splits by pushing: every CTA has a buffer
+    // of its own, outside the ring, that its peers write their partial sums into: [source rank][row][token].
+    // (With two accumulators the buffer would cost the second CTA of an SM.)
+    static constexpr bool PUSH = BN <= 32 && !DUAL;
+    static constexpr int RECV_OFFSET = BAR_OFFSET + (2 * STAGES + 2) * 8 + 16;     // 16-byte aligned (BAR_OFFSET is)
+    static constexpr int RECV_BYTES = PUSH ? (DUAL ? 2 : 1) * BN * BM * 4 : 0;
+    static constexpr int TOTAL = RECV_OFFSET + RECV_BYTES + 1024;                  // + slack to align the base
 };
 
 template <int BN, int STAGES, bool DUAL>
@@ -159,9 +165,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar_full = base + S::BAR_OFFSET, bar_empty = bar_full + 8 * STAGES, bar_acc = bar_empty + 8 * STAGES;
-    const uint32_t tmem_slot = bar_acc + 8;
+    const uint32_t bar_recv = bar_acc + 8, tmem_slot = bar_recv + 8;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
-    volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(gen_base + S::BAR_OFFSET + (2 * STAGES + 1) * 8);
+    volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(gen_base + S::BAR_OFFSET + (2 * STAGES + 2) * 8);
+    const bool push = S::PUSH && g.cluster && g.splits > 1;
     __shared__ int s_abort, s_last;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -178,8 +185,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             mbar_init(bar_empty + 8 * s, 1);
         }
         mbar_init(bar_acc, 1);
+        mbar_init(bar_recv, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (push) {
+            // what the peers will send: from each of the splits, per accumulator and row of this CTA's share, the
+            // valid tokens rounded up to whole 16-byte pieces
+            const int sent = (min(BN, g.T - n0) + 3) & ~3;
+            mbar_expect_tx(bar_recv, (uint32_t)(g.splits * ACCS * (BM / g.splits) * sent * 4));
+        }
     }
+    // The peers may write into this CTA only once its barrier stands: arrive now, wait just before the first push.
+    if (push) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     if (warp == 0) {
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)TMEM_COLS) : "memory");
@@ -320,6 +336,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                     for (int j = 0; j < 16; ++j)
                         if (c + j < n_valid) finish(v0[j], DUAL ? v1[j] : 0.f, c + j);
             }
+        } else if (push) {
+            // Each thread holds one row of the partial tile; the row belongs to the share of CTA `dest`, which
+            // gets it as 16-byte pieces of four tokens, counted on its receive barrier.
+            const int S_ = g.splits, R = BM / S_;
+            uint32_t rank;
+            asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+            const uint32_t dest = (uint32_t)(tid / R);
+            uint32_t rbar, rbuf;
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbar) : "r"(bar_recv), "r"(dest));
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbuf) : "r"(base + (uint32_t)S::RECV_OFFSET), "r"(dest));
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");      // every peer's barrier stands
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                float v0[16], v1[16];
+                tmem_ld16(lane_addr + c, v0);
+                if (DUAL) tmem_ld16(lane_addr + BN + c, v1);
+#pragma unroll
+                for (int j = 0; j < 16; j += 4)
+                    if (c + j < n_valid) {
+                        const uint32_t a0 = rbuf + (uint32_t)((((rank * ACCS) * R + (tid % R)) * BN + c + j) * 4);
+                        asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
+                                     ::"r"(a0), "f"(v0[j]), "f"(v0[j + 1]), "f"(v0[j + 2]), "f"(v0[j + 3]), "r"(rbar) : "memory");
+                        if (DUAL)
+                            asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
+                                         ::"r"(a0 + (uint32_t)(R * BN * 4)), "f"(v1[j]), "f"(v1[j + 1]), "f"(v1[j + 2]), "f"(v1[j + 3]), "r"(rbar)
+                                         : "memory");
+                    }
+            }
         } else if (g.cluster) {
             // this CTA's partial tile into its own shared memory (the ring is idle now): [acc][token][row]
             float* stg = reinterpret_cast<float*>(gen_base);
@@ -388,7 +432,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
         }
     }
-    if (g.cluster && g.splits > 1) {
+    if (push) {
+        if (aborted) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // pairs with the arrival above
+        // All the peers' pieces (bounded wait: a peer that gave up sends none), then this CTA's share of the rows:
+        // the partial sums are added in split order.
+        bool got = mbar_wait(bar_recv, 0, &s_abort);
+        if (!got && !s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC_WAIT_RECV); }
+        if (got && !aborted) {
+            const int S_ = g.splits, R = BM / S_;
+            uint32_t rank;
+            asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+            const float* rb = reinterpret_cast<const float*>(gen_base + S::RECV_OFFSET);
+            const int row = tid % R, mm = m0 + (int)rank * R + row;
+            if (mm < (DUAL ? g.dual_offset : g.N))
+                for (int j = tid / R; j < n_valid; j += THREADS / R) {
+                    float a0 = 0.f, a1 = 0.f;
+                    for (int sp = 0; sp < S_; ++sp) {
+                        a0 += rb[((sp * ACCS) * R + row) * BN + j];
+                        if (DUAL) a1 += rb[((sp * ACCS + 1) * R + row) * BN + j];
+                    }
+                    finish_at(a0, a1, j, mm);
+                }
+        }
+    } else if (g.cluster && g.splits > 1) {
         // Every CTA of the cluster passes both barriers, whether it gave up or not.
         asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
         if (!aborted) {
@@ -586,8 +652,8 @@ LLB_API int llb_gemm_tc(const void* X, const void* W, const void* bias, int bias
 #define LLB_TC(BN_, ST_, STD_) \
     case BN_: return dual ? launch<BN_, STD_, true>(mw, mx, g, grid, stream) : launch<BN_, ST_, false>(mw, mx, g, grid, stream)
     switch (bn) {
-        LLB_TC(16, 6, 3);       // 108 KB / 102 KB of shared memory: two CTAs per SM
-        LLB_TC(32, 5, 3);       // 100 KB / 108 KB
+        LLB_TC(16, 5, 3);       // 99 KB / 102 KB of shared memory (ring + receive buffer): two CTAs per SM
+        LLB_TC(32, 4, 3);       // 97 KB / 108 KB
         LLB_TC(64, 4, 4);       //  96 KB / 160 KB
         LLB_TC(128, 6, 4);      // 192 KB / 192 KB
         LLB_TC(256, 4, 3);      // 192 KB / 192 KB
@@ -679,8 +745,8 @@ int llb_gemm_tc_noalloc(const void* X, const void* W, const void* bias, int bias
     if (rc) return rc;
     GemmArgs g{bias, bias_dtype, Y, y_dtype, T, N, K, ldy, 0, splits, 0, ptrs.scratch, ptrs.counters, ptrs.err};
     switch (bn) {
-        case 16: return launch<16, 6, false>(mw, mx, g, grid, stream);
-        case 32: return launch<32, 5, false>(mw, mx, g, grid, stream);
+        case 16: return launch<16, 5, false>(mw, mx, g, grid, stream);
+        case 32: return launch<32, 4, false>(mw, mx, g, grid, stream);
         case 64: return launch<64, 4, false>(mw, mx, g, grid, stream);
         case 128: return launch<128, 6, false>(mw, mx, g, grid, stream);
         default: return launch<256, 4, false>(mw, mx, g, grid, stream);

@@ -187,7 +187,7 @@ def _sm_count(device) -> int:
     return torch.cuda.get_device_properties(device).multi_processor_count
 
 
-_TC_STAGES = {False: {16: 6, 32: 5, 64: 4, 128: 6, 256: 4}, True: {16: 3, 32: 3, 64: 4, 128: 4, 256: 3}}
+_TC_STAGES = {False: {16: 5, 32: 4, 64: 4, 128: 6, 256: 4}, True: {16: 3, 32: 3, 64: 4, 128: 4, 256: 3}}
 
 
 def tc_plan(T: int, rows_out: int, K: int, sms: int, dual: bool = False):
@@ -205,7 +205,8 @@ def tc_plan(T: int, rows_out: int, K: int, sms: int, dual: bool = False):
     kblocks = -(-K // 64)
     accs = 2 if dual else 1
     stage_kb = accs * 16 + bn / 8
-    two_per_sm = stage_kb * _TC_STAGES[dual][bn] <= 112
+    recv_kb = bn / 2 if bn <= 32 and not dual else 0          # the push reduction's receive buffer
+    two_per_sm = stage_kb * _TC_STAGES[dual][bn] + recv_kb <= 112
     capacity = (sms * 2 * 280) // 296 if two_per_sm else (sms * 112) // 148
     best, best_cost = 1, kblocks * stage_kb * 0.0155
     if bn <= 128:
