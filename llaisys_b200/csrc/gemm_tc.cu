@@ -135,7 +135,7 @@ struct GemmArgs {
     int T, N, K, ldy;
     int dual_offset;       // DUAL: rows between the gate block and the up block of W
     int splits;
-    int cluster;           // 1: the splits of a tile are a thread-block cluster and reduce through shared memory
+    int cluster;           // 1: the splits of a tile are a thread-block cluster and reduce by pushing into shared memory
     float* scratch;        // [tiles][splits][accs][BN][BM] float32
     int* counters;         // [tiles], zero between launches
     int* err;
@@ -147,12 +147,14 @@ struct Smem {
     static constexpr int B_BYTES = BN * BK * 2;
     static constexpr int STAGE_BYTES = (DUAL ? 2 : 1) * A_BYTES + B_BYTES;
     static constexpr int BAR_OFFSET = STAGES * STAGE_BYTES;
-    // Single-accumulator tiles of up to 32 tokens reduce their cluster's splits by pushing: every CTA has a buffer
-    // of its own, outside the ring, that its peers write their partial sums into: [source rank][row][token].
-    // (With two accumulators the buffer would cost the second CTA of an SM.)
-    static constexpr bool PUSH = BN <= 32 && !DUAL;
+    // The splits of a cluster reduce by pushing: every CTA receives, from each peer, the partial sums of its share
+    // of the tile's rows: [source rank][accumulator][group of 4 tokens][row][4 tokens].  Single-accumulator tiles of
+    // up to 32 tokens have a buffer of their own for that, outside the ring (OWN_RECV), so a peer may push as soon as
+    // it is done; for the others the buffer is the ring itself, which a peer may write only after a cluster barrier
+    // that every CTA passes once its own main loop is over (a buffer of their own would cost the second CTA of an SM).
+    static constexpr bool OWN_RECV = BN <= 32 && !DUAL;
     static constexpr int RECV_OFFSET = BAR_OFFSET + (2 * STAGES + 2) * 8 + 16;     // 16-byte aligned (BAR_OFFSET is)
-    static constexpr int RECV_BYTES = PUSH ? (DUAL ? 2 : 1) * BN * BM * 4 : 0;
+    static constexpr int RECV_BYTES = OWN_RECV ? BN * BM * 4 : 0;
     static constexpr int TOTAL = RECV_OFFSET + RECV_BYTES + 1024;                  // + slack to align the base
 };
 
@@ -168,7 +170,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t bar_recv = bar_acc + 8, tmem_slot = bar_recv + 8;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
     volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(gen_base + S::BAR_OFFSET + (2 * STAGES + 2) * 8);
-    const bool push = S::PUSH && g.cluster && g.splits > 1;
+    const bool push = g.cluster && g.splits > 1;
     __shared__ int s_abort, s_last;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -194,8 +196,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             mbar_expect_tx(bar_recv, (uint32_t)(g.splits * ACCS * (BM / g.splits) * sent * 4));
         }
     }
-    // The peers may write into this CTA only once its barrier stands: arrive now, wait just before the first push.
-    if (push) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    // The peers may write into this CTA's own buffer as soon as its barrier stands: arrive now, wait just before the
+    // first push.  (Without a buffer of its own a CTA arrives when its ring is idle.)
+    if (push && S::OWN_RECV) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     if (warp == 0) {
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)TMEM_COLS) : "memory");
@@ -342,11 +345,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const int S_ = g.splits, R = BM / S_;
             uint32_t rank;
             asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-            const uint32_t dest = (uint32_t)(tid / R);
+            const uint32_t dest = (uint32_t)(tid / R), row = (uint32_t)(tid % R);
             uint32_t rbar, rbuf;
             asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbar) : "r"(bar_recv), "r"(dest));
-            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbuf) : "r"(base + (uint32_t)S::RECV_OFFSET), "r"(dest));
-            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");      // every peer's barrier stands
+            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbuf) : "r"(base + (uint32_t)(S::OWN_RECV ? S::RECV_OFFSET : 0)), "r"(dest));
+            if (!S::OWN_RECV) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");      // this ring is idle
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");      // every peer's barrier stands (and its ring is idle)
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 float v0[16], v1[16];
@@ -355,28 +359,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 #pragma unroll
                 for (int j = 0; j < 16; j += 4)
                     if (c + j < n_valid) {
-                        const uint32_t a0 = rbuf + (uint32_t)((((rank * ACCS) * R + (tid % R)) * BN + c + j) * 4);
+                        const uint32_t piece = (((rank * ACCS) * (BN / 4) + (uint32_t)((c + j) / 4)) * R + row) * 16;
                         asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
-                                     ::"r"(a0), "f"(v0[j]), "f"(v0[j + 1]), "f"(v0[j + 2]), "f"(v0[j + 3]), "r"(rbar) : "memory");
+                                     ::"r"(rbuf + piece), "f"(v0[j]), "f"(v0[j + 1]), "f"(v0[j + 2]), "f"(v0[j + 3]), "r"(rbar) : "memory");
                         if (DUAL)
                             asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.v4.f32 [%0], {%1, %2, %3, %4}, [%5];"
-                                         ::"r"(a0 + (uint32_t)(R * BN * 4)), "f"(v1[j]), "f"(v1[j + 1]), "f"(v1[j + 2]), "f"(v1[j + 3]), "r"(rbar)
-                                         : "memory");
-                    }
-            }
-        } else if (g.cluster) {
-            // this CTA's partial tile into its own shared memory (the ring is idle now): [acc][token][row]
-            float* stg = reinterpret_cast<float*>(gen_base);
-#pragma unroll 1
-            for (int c = 0; c < BN; c += 16) {
-                float v0[16], v1[16];
-                tmem_ld16(lane_addr + c, v0);
-                if (DUAL) tmem_ld16(lane_addr + BN + c, v1);
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                    if (c + j < n_valid) {
-                        stg[(c + j) * BM + tid] = v0[j];
-                        if (DUAL) stg[(BN + c + j) * BM + tid] = v1[j];
+                                         ::"r"(rbuf + piece + (uint32_t)((BN / 4) * R * 16)), "f"(v1[j]), "f"(v1[j + 1]), "f"(v1[j + 2]),
+                                           "f"(v1[j + 3]), "r"(rbar) : "memory");
                     }
             }
         } else {
@@ -433,73 +422,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
     }
     if (push) {
-        if (aborted) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // pairs with the arrival above
+        if (aborted) {      // pairs with the arrivals of the peers
+            if (!S::OWN_RECV) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        }
         // All the peers' pieces (bounded wait: a peer that gave up sends none), then this CTA's share of the rows:
         // the partial sums are added in split order.
         bool got = mbar_wait(bar_recv, 0, &s_abort);
         if (!got && !s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC_WAIT_RECV); }
         if (got && !aborted) {
-            const int S_ = g.splits, R = BM / S_;
+            const int S_ = g.splits, R = BM / S_, groups = (n_valid + 3) / 4;
             uint32_t rank;
             asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-            const float* rb = reinterpret_cast<const float*>(gen_base + S::RECV_OFFSET);
-            const int row = tid % R, mm = m0 + (int)rank * R + row;
-            if (mm < (DUAL ? g.dual_offset : g.N))
-                for (int j = tid / R; j < n_valid; j += THREADS / R) {
-                    float a0 = 0.f, a1 = 0.f;
-                    for (int sp = 0; sp < S_; ++sp) {
-                        a0 += rb[((sp * ACCS) * R + row) * BN + j];
-                        if (DUAL) a1 += rb[((sp * ACCS + 1) * R + row) * BN + j];
-                    }
-                    finish_at(a0, a1, j, mm);
-                }
-        }
-    } else if (g.cluster && g.splits > 1) {
-        // Every CTA of the cluster passes both barriers, whether it gave up or not.
-        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-        if (!aborted) {
-            uint32_t rank;
-            asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-            const int S_ = g.splits, R = BM / S_;               // this CTA adds rows [rank * R, rank * R + R)
-            const int row = (int)rank * R + (tid % R), tg = tid / R;
-            const int mm = m0 + row;
-            const bool ok2 = mm < (DUAL ? g.dual_offset : g.N);
-            // four tokens at a time with all their remote loads issued before the first is used;
-            // each token's partials are still added in split order
-            for (int j0 = tg; j0 < n_valid; j0 += 4 * S_) {
-                float a0[4] = {0.f, 0.f, 0.f, 0.f}, a1[4] = {0.f, 0.f, 0.f, 0.f};
-                float v0[4][8], v1[4][8];
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    const int j = j0 + u * S_;
-                    const uint32_t l0 = base + (uint32_t)((j * BM + row) * 4), l1 = base + (uint32_t)(((BN + j) * BM + row) * 4);
-#pragma unroll
-                    for (int s = 0; s < 8; ++s) {
-                        v0[u][s] = v1[u][s] = 0.f;
-                        if (s < S_ && j < n_valid) {
-                            uint32_t r0;
-                            asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r0) : "r"(l0), "r"(s));
-                            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v0[u][s]) : "r"(r0) : "memory");
-                            if (DUAL) {
-                                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r0) : "r"(l1), "r"(s));
-                                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v1[u][s]) : "r"(r0) : "memory");
-                            }
-                        }
+            const float4* rb = reinterpret_cast<const float4*>(gen_base + (S::OWN_RECV ? S::RECV_OFFSET : 0));
+            for (int item = tid; item < R * groups; item += THREADS) {
+                const int row = item % R, jg = item / R, mm = m0 + (int)rank * R + row;
+                if (mm >= (DUAL ? g.dual_offset : g.N)) continue;
+                float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+                for (int sp = 0; sp < S_; ++sp) {
+                    const float4 p0 = rb[((sp * ACCS) * (BN / 4) + jg) * R + row];
+                    a0.x += p0.x; a0.y += p0.y; a0.z += p0.z; a0.w += p0.w;
+                    if (DUAL) {
+                        const float4 p1 = rb[((sp * ACCS + 1) * (BN / 4) + jg) * R + row];
+                        a1.x += p1.x; a1.y += p1.y; a1.z += p1.z; a1.w += p1.w;
                     }
                 }
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {
-#pragma unroll
-                    for (int s = 0; s < 8; ++s) {
-                        a0[u] += v0[u][s];
-                        a1[u] += v1[u][s];
-                    }
-                    if (ok2 && j0 + u * S_ < n_valid) finish_at(a0[u], a1[u], j0 + u * S_, mm);
-                }
+                const int j = jg * 4;
+                finish_at(a0.x, a1.x, j, mm);
+                if (j + 1 < n_valid) finish_at(a0.y, a1.y, j + 1, mm);
+                if (j + 2 < n_valid) finish_at(a0.z, a1.z, j + 2, mm);
+                if (j + 3 < n_valid) finish_at(a0.w, a1.w, j + 3, mm);
             }
         }
-        // no CTA may leave while another still reads its shared memory
-        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
