@@ -222,6 +222,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
     }
     llb_grid_dependency_sync();      // from here on memory written by earlier kernels is touched
+    // The peers of a cluster start together and arrived before this point in their own code: the wait that must
+    // precede the first push into a buffer of its own costs nothing here, and is off the epilogue.
+    if (push && S::OWN_RECV) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 
     if (warp == 0) {
         if (lane == 0) {
@@ -289,15 +292,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
     const bool row_ok = m < (DUAL ? g.dual_offset : g.N);
 
-    auto finish_at = [&](float acc0, float acc1, int j, int row) {
+    // A row's bias is fetched once, before the first store of the row (a store may alias it as far as the compiler
+    // can tell, so a load after a store is not moved ahead of it).
+    auto bias_of = [&](int row) -> float {
+        if (!g.bias) return 0.f;
+        return g.bias_dtype == LLB_F32 ? ((const float*)g.bias)[row] : to_f32(((const bf16*)g.bias)[row]);
+    };
+    auto finish_at = [&](float acc0, float acc1, int j, int row, float bias_v) {
         float v = acc0;
         if (DUAL) v = acc1 * __fdividef(acc0, 1.0f + __expf(-acc0));
-        if (g.bias) v += g.bias_dtype == LLB_F32 ? ((const float*)g.bias)[row] : to_f32(((const bf16*)g.bias)[row]);
+        v += bias_v;
         size_t o = (size_t)(n0 + j) * g.ldy + row;
         if (g.y_dtype == LLB_F32) ((float*)g.Y)[o] = v;
         else ((bf16*)g.Y)[o] = __float2bfloat16_rn(v);
     };
-    auto finish = [&](float acc0, float acc1, int j) { finish_at(acc0, acc1, j, m); };
+    // (the own row's bias is fetched inside the branches that finish whole rows: a load issued before the push
+    // branch's cluster barrier would be waited for there)
+    auto finish = [&](float acc0, float acc1, int j, float bias_v) { finish_at(acc0, acc1, j, m, bias_v); };
 
     if (!aborted) {
         if (g.splits == 1 && g.y_dtype == LLB_BF16 && m0 + BM <= (DUAL ? g.dual_offset : g.N) &&
@@ -329,6 +340,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 *reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(g.Y) + (size_t)(n0 + j) * g.ldy + m0 + sub * 8) = v;
             }
         } else if (g.splits == 1) {
+            const float own_bias = row_ok ? bias_of(m) : 0.f;
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 float v0[16], v1[16];
@@ -337,7 +349,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (row_ok)
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
-                        if (c + j < n_valid) finish(v0[j], DUAL ? v1[j] : 0.f, c + j);
+                        if (c + j < n_valid) finish(v0[j], DUAL ? v1[j] : 0.f, c + j, own_bias);
             }
         } else if (push) {
             // Each thread holds one row of the partial tile; the row belongs to the share of CTA `dest`, which
@@ -349,8 +361,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             uint32_t rbar, rbuf;
             asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbar) : "r"(bar_recv), "r"(dest));
             asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(rbuf) : "r"(base + (uint32_t)(S::OWN_RECV ? S::RECV_OFFSET : 0)), "r"(dest));
-            if (!S::OWN_RECV) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");      // this ring is idle
-            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");      // every peer's barrier stands (and its ring is idle)
+            if (!S::OWN_RECV) {       // this ring is idle; every peer's must be before anything is written into it
+                asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+                asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+            }
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 float v0[16], v1[16];
@@ -392,6 +406,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const float* all = g.scratch + (size_t)tile * g.splits * (ACCS * BN * BM);
                 // eight tokens at a time and four splits ahead, so that the loads overlap instead of
                 // each waiting for the one before; the sums still run in split order
+                const float own_bias = row_ok ? bias_of(m) : 0.f;
                 if (row_ok)
                     for (int j0 = 0; j0 < n_valid; j0 += 8) {
                         float a0[8], a1[8];
@@ -415,29 +430,34 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         }
 #pragma unroll
                         for (int jj = 0; jj < 8; ++jj)
-                            if (j0 + jj < n_valid) finish(a0[jj], a1[jj], j0 + jj);
+                            if (j0 + jj < n_valid) finish(a0[jj], a1[jj], j0 + jj, own_bias);
                     }
                 if (tid == 0) g.counters[tile] = 0;
             }
         }
     }
     if (push) {
-        if (aborted) {      // pairs with the arrivals of the peers
-            if (!S::OWN_RECV) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        if (aborted && !S::OWN_RECV) {      // pairs with the arrivals of the peers
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
             asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
         }
         // All the peers' pieces (bounded wait: a peer that gave up sends none), then this CTA's share of the rows:
         // the partial sums are added in split order.
+        const int S_ = g.splits, R = BM / S_, groups = (n_valid + 3) / 4;
+        uint32_t rank;
+        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+        const int limit = DUAL ? g.dual_offset : g.N;
+        // the bias of this thread's first output piece is asked for before the wait for the peers
+        float bias_first = 0.f;
+        if (!aborted && tid < R * groups && m0 + (int)rank * R + tid % R < limit) bias_first = bias_of(m0 + (int)rank * R + tid % R);
         bool got = mbar_wait(bar_recv, 0, &s_abort);
         if (!got && !s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC_WAIT_RECV); }
         if (got && !aborted) {
-            const int S_ = g.splits, R = BM / S_, groups = (n_valid + 3) / 4;
-            uint32_t rank;
-            asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
             const float4* rb = reinterpret_cast<const float4*>(gen_base + (S::OWN_RECV ? S::RECV_OFFSET : 0));
-            for (int item = tid; item < R * groups; item += THREADS) {
-                const int row = item % R, jg = item / R, mm = m0 + (int)rank * R + row;
-                if (mm >= (DUAL ? g.dual_offset : g.N)) continue;
+            // one piece: four tokens of one row of this CTA's share
+            auto piece = [&](int item, float bias_v) {
+                const int row = item % R, jg = item / R, mm = m0 + (int)rank * R + row, j = jg * 4;
+                if (mm >= limit) return;
                 float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
                 for (int sp = 0; sp < S_; ++sp) {
                     const float4 p0 = rb[((sp * ACCS) * (BN / 4) + jg) * R + row];
@@ -447,11 +467,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                         a1.x += p1.x; a1.y += p1.y; a1.z += p1.z; a1.w += p1.w;
                     }
                 }
-                const int j = jg * 4;
-                finish_at(a0.x, a1.x, j, mm);
-                if (j + 1 < n_valid) finish_at(a0.y, a1.y, j + 1, mm);
-                if (j + 2 < n_valid) finish_at(a0.z, a1.z, j + 2, mm);
-                if (j + 3 < n_valid) finish_at(a0.w, a1.w, j + 3, mm);
+                finish_at(a0.x, a1.x, j, mm, bias_v);
+                if (j + 1 < n_valid) finish_at(a0.y, a1.y, j + 1, mm, bias_v);
+                if (j + 2 < n_valid) finish_at(a0.z, a1.z, j + 2, mm, bias_v);
+                if (j + 3 < n_valid) finish_at(a0.w, a1.w, j + 3, mm, bias_v);
+            };
+            if (tid < R * groups) piece(tid, bias_first);
+            for (int item = tid + THREADS; item < R * groups; item += THREADS) {      // tiles of 64 tokens and more
+                const int mm = m0 + (int)rank * R + item % R;
+                piece(item, mm < limit ? bias_of(mm) : 0.f);
             }
         }
     }
