@@ -298,7 +298,45 @@ __device__ __forceinline__ Ring<NST> make_ring(uint8_t* smem_raw) {
     r.ptr = smem_raw + (r.base - raw);
     return r;
 }
+constexpr int MAX_CLUSTER = 16;            // key slices that merge inside a thread-block cluster (16 needs the non-portable size)
 constexpr int smem_bytes(int nst) { return nst * STAGE_BYTES + 16 * (DH + 8) * 2 + 128; }     // ring, staged queries, alignment slack
+
+// Block `rank` of a cluster of S (<= MAXS) blocks merges its share of the n_heads * DH outputs from the partial
+// results every block keeps in shared memory (ml: [16][2] maximum and sum, o: [16][DH]) and writes them to out.
+template <int MAXS>
+__device__ __forceinline__ void cluster_merge(int S, int n_heads, uint32_t ml_addr, uint32_t o_addr, bf16* out, int tid) {
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int total = n_heads * DH, share = (total + S - 1) / S;
+    for (int i = (int)rank * share + tid; i < min(total, ((int)rank + 1) * share); i += THREADS) {
+        int r = i / DH, d = i - r * DH;
+        float ms[MAXS], ls[MAXS], os[MAXS];
+#pragma unroll
+        for (int sp = 0; sp < MAXS; ++sp) {
+            ms[sp] = -INFINITY;
+            ls[sp] = os[sp] = 0.f;
+            if (sp < S) {
+                uint32_t ra;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(ml_addr + (uint32_t)(r * 8)), "r"(sp));
+                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ms[sp]) : "r"(ra) : "memory");
+                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ls[sp]) : "r"(ra + 4) : "memory");
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(o_addr + (uint32_t)((r * DH + d) * 4)), "r"(sp));
+                asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(os[sp]) : "r"(ra) : "memory");
+            }
+        }
+        float M = -INFINITY;
+#pragma unroll
+        for (int sp = 0; sp < MAXS; ++sp) M = fmaxf(M, ms[sp]);
+        float L = 0.f, acc = 0.f;
+#pragma unroll
+        for (int sp = 0; sp < MAXS; ++sp) {
+            float f = ms[sp] == -INFINITY ? 0.f : fast_exp2(ms[sp] - M);
+            L += ls[sp] * f;
+            acc += os[sp] * f;
+        }
+        out[(size_t)r * DH + d] = __float2bfloat16_rn(acc / L);
+    }
+}
 
 // ------------------------------------------------------------------ decode
 template <int NST>
@@ -484,39 +522,12 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
     // ---- cluster merge of the key slices: block `rank` produces one share of the (head, dim) outputs
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     {
-        const int S = p.n_splits;                                  // cluster size, at most 8
-        uint32_t rank;
-        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-        const int total = n_heads * DH, share = (total + S - 1) / S;
+        // Two instances of the same code: the common one for up to eight slices stays as short as it was (a block
+        // runs this part once, so its time is the time to fetch its instructions).
         const uint32_t ml_addr = smem_u32(fin_ml), o_addr = smem_u32(fin_o);
-        for (int i = (int)rank * share + tid; i < min(total, ((int)rank + 1) * share); i += THREADS) {
-            int r = i / DH, d = i - r * DH;
-            float ms[8], ls[8], os[8];
-#pragma unroll
-            for (int sp = 0; sp < 8; ++sp) {
-                ms[sp] = -INFINITY;
-                ls[sp] = os[sp] = 0.f;
-                if (sp < S) {
-                    uint32_t ra;
-                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(ml_addr + (uint32_t)(r * 8)), "r"(sp));
-                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ms[sp]) : "r"(ra) : "memory");
-                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(ls[sp]) : "r"(ra + 4) : "memory");
-                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(o_addr + (uint32_t)((r * DH + d) * 4)), "r"(sp));
-                    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(os[sp]) : "r"(ra) : "memory");
-                }
-            }
-            float M = -INFINITY;
-#pragma unroll
-            for (int sp = 0; sp < 8; ++sp) M = fmaxf(M, ms[sp]);
-            float L = 0.f, acc = 0.f;
-#pragma unroll
-            for (int sp = 0; sp < 8; ++sp) {
-                float f = ms[sp] == -INFINITY ? 0.f : fast_exp2(ms[sp] - M);
-                L += ls[sp] * f;
-                acc += os[sp] * f;
-            }
-            p.out[(size_t)tok * p.nh * DH + (size_t)(head0 + r) * DH + d] = __float2bfloat16_rn(acc / L);
-        }
+        bf16* out_tok = p.out + (size_t)tok * p.nh * DH + (size_t)head0 * DH;
+        if (p.n_splits <= 8) cluster_merge<8>(p.n_splits, n_heads, ml_addr, o_addr, out_tok, tid);
+        else cluster_merge<MAX_CLUSTER>(p.n_splits, n_heads, ml_addr, o_addr, out_tok, tid);
     }
     // no block may leave while another still reads its shared memory
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -647,10 +658,39 @@ LLB_API int llb_attn_mma_prefill(MmaAttnParams p, int B, int max_new, cudaStream
     return llb_status();
 }
 
+// How many clusters of `size` blocks of the decode kernel the device can hold at once (0: that size cannot be launched).
+LLB_API int llb_attn_mma_decode_max_clusters(int size) {
+    auto kernel = attn_mma_decode_kernel<STAGES>;
+    const int smem = smem_bytes(STAGES);
+    if (configure<1>(kernel, smem)) return 0;
+    if (size > 8 && cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    llb_prefer_max_shared((const void*)kernel);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(size, 1, 1);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)size;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return n;
+}
+
 LLB_API int llb_attn_mma_decode(MmaAttnParams p, int B, cudaStream_t stream) {
     if (B == 0) return 0;
     if (!aligned_ok(p) || p.n_splits < 1 || p.n_splits > 64) return (int)cudaErrorInvalidValue;
-    if (p.cluster && p.n_splits > 8) return (int)cudaErrorInvalidValue;
+    if (p.cluster && p.n_splits > MAX_CLUSTER) return (int)cudaErrorInvalidValue;
     int G = p.nh / p.nkvh;
     dim3 grid(p.n_splits, p.nkvh * ((G + 15) / 16), B);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
@@ -658,6 +698,14 @@ LLB_API int llb_attn_mma_decode(MmaAttnParams p, int B, cudaStream_t stream) {
     const int smem = smem_bytes(STAGES);
     int rc = configure<1>(kernel, smem);
     if (rc) return rc;
+    if (p.cluster && p.n_splits > 8) {
+        static bool allowed = false;
+        if (!allowed) {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+            if (e != cudaSuccess) return (int)e;
+            allowed = true;
+        }
+    }
     if (p.cluster && p.n_splits > 1) {
         llb_prefer_max_shared((const void*)kernel);
         cudaLaunchConfig_t cfg = {};

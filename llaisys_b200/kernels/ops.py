@@ -303,6 +303,21 @@ def _mma_ok(qkv, dh) -> bool:
     return MMA_ATTENTION and qkv.dtype == torch.bfloat16 and dh % 16 == 0 and dh <= 128 and qkv.stride(0) % 8 == 0
 
 
+_decode16 = {}
+
+
+def decode_clusters16(dtype: torch.dtype, dh: int) -> int:
+    """Clusters of sixteen blocks of the decode attention kernel that the device holds at once
+    (0 where that kernel or that cluster size does not apply)."""
+    if not (MMA_ATTENTION and dtype == torch.bfloat16 and dh % 16 == 0 and dh <= 128):
+        return 0
+    if dh not in _decode16:
+        f = _mma_lib(dh).llb_attn_mma_decode_max_clusters
+        f.argtypes, f.restype = [c_int], c_int
+        _decode16[dh] = int(f(16))
+    return _decode16[dh]
+
+
 def decode_fusion_ok(dtype: torch.dtype, dh: int) -> bool:
     """True when decode attention can itself rotate the query and the new key and append the
     new key and value to the cache (the tensor-core kernel), so that no kernel has to do it before."""
@@ -407,7 +422,7 @@ def attention_decode(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_star
         if rope is not None:
             p.rope_cos, p.rope_sin, p.rope_rows = rope[0].data_ptr(), rope[1].data_ptr(), rope[0].shape[0]
         p.append_new = int(append_new)
-        p.cluster = int(1 < n_splits <= 8)          # few slices merge inside a cluster, through shared memory
+        p.cluster = int(1 < n_splits <= 8 or n_splits == 16)      # few slices merge inside a cluster, through shared memory
     p.n_splits = n_splits
     if n_splits > 1 and not (mma and p.cluster):
         part_o = torch.empty((n_seqs, nh, n_splits, dh), dtype=torch.float32, device=qkv.device)

@@ -88,7 +88,7 @@ class GQAttention(Mixer):
             if kernels.decode_fusion_ok(qkv.dtype, self.dh) and (self.position is None or fused_tables is not None):
                 # the attention kernel rotates the query and the new key itself and appends to the cache
                 rope = fused_tables(ctx.max_position + 1) if fused_tables is not None else None
-                out = kernels.attention_decode(*common, self.window, self.scale, n_splits=ctx.decode_splits(self.nkvh),
+                out = kernels.attention_decode(*common, self.window, self.scale, n_splits=ctx.decode_splits(self.nkvh, kernels.decode_clusters16(qkv.dtype, self.dh)),
                                                rope=rope, append_new=kv.writable)
             else:
                 # position encoding; the same kernel also appends to the cache

@@ -217,7 +217,7 @@ def test_attention_prefill(dtype, nh, nkvh, dh, window):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh,nkvh,dh,window", [(4, 2, 32, None), (6, 1, 48, 70), (12, 2, 128, None), (5, 5, 64, 3), (40, 1, 16, 129)])
-@pytest.mark.parametrize("splits", [1, 3, 8, 11])
+@pytest.mark.parametrize("splits", [1, 3, 8, 11, 16])
 def test_attention_decode(dtype, nh, nkvh, dh, window, splits):
     from llaisys_b200 import kernels
     lens_before, news = [0, 129, 63, 64, 500], [1, 1, 1, 1, 1]
@@ -402,7 +402,7 @@ def test_linear_falls_back_where_tensor_cores_do_not_apply():
 
 
 @pytest.mark.parametrize("nh,nkvh,dh,window", [(12, 2, 128, None), (6, 1, 48, 70), (40, 1, 16, 129), (4, 4, 64, 3)])
-@pytest.mark.parametrize("splits", [1, 5, 13])
+@pytest.mark.parametrize("splits", [1, 5, 13, 16])
 def test_attention_decode_fused_rotation_and_append(nh, nkvh, dh, window, splits):
     """The tensor-core decode kernel can rotate the query and the new key and append to the cache
     itself; that must give what the separate rotation/append kernel followed by attention gives,
