@@ -30,6 +30,31 @@ LLB_API int llb_embedding(float* out, const void* table, int table_dtype, const 
     return llb_status();
 }
 
+// ------------------------------------------------------------------ token ids that stay on the device
+// dst[i] = src[idx[i]] and dst[idx[i]] = src[i]: the last sampled token of every cache slot is kept in a table
+// on the device, written after sampling and read by the next step, so that the next step can be launched
+// before the host has seen the tokens.
+__global__ void gather_i32_kernel(int* __restrict__ dst, const int* __restrict__ src, const int* __restrict__ idx, int n) {
+    llb_grid_dependency_sync();
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[i] = src[idx[i]];
+}
+__global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict__ idx, const int* __restrict__ src, int n) {
+    llb_grid_dependency_sync();
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) dst[idx[i]] = src[i];
+}
+LLB_API int llb_gather_i32(int* dst, const int* src, const int* idx, int n, cudaStream_t stream) {
+    if (n == 0) return 0;
+    llb_launch(gather_i32_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, dst, src, idx, n);
+    return llb_status();
+}
+LLB_API int llb_scatter_i32(int* dst, const int* idx, const int* src, int n, cudaStream_t stream) {
+    if (n == 0) return 0;
+    llb_launch(scatter_i32_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, dst, idx, src, n);
+    return llb_status();
+}
+
 // ------------------------------------------------------------------ residual add + RMSNorm
 // Row r of the output is norm(residual[src] + sum_p delta[p][src]) with src = rows ? rows[r] : r.
 // When write_back is set the summed row replaces residual[src] (never together with `rows`).

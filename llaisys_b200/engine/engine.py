@@ -62,6 +62,9 @@ class Engine:
         self.err = torch.zeros(1, dtype=torch.int32, device=self.env.device)
         self.use_graphs = use_graphs and model.capturable()
         model.prepare(min(self.spec.max_positions, self.cache.n_pages * self.page))
+        # the last sampled token of every slot, for steps that take their tokens from the device (see feed())
+        self.fed_tokens = torch.zeros(self.cache.n_slots, dtype=torch.int32, device=self.env.device)
+        self._last_ctx = None
         self._graphs = {}                      # shape -> [context, graph or None, logits]
         self._stages = [[None, None] for _ in range(self.STAGES)]
         self._stage_i = 0
@@ -111,9 +114,27 @@ class Engine:
         self._stages[i] = [buf, ev]
         return buf, ev
 
-    def step(self, entries: List[StepEntry]) -> Optional[torch.Tensor]:
+    def feed(self, tokens: torch.Tensor) -> None:
+        """Keeps the token chosen for each sequence of the last step on the device (int32 [entries], in
+        the order of that step's entries), where a following step(..., fed=True) finds it."""
+        from .. import kernels
+        ctx = self._last_ctx
+        if ctx is None or tokens.numel() != ctx.n_seqs:
+            raise StepError("feed() takes one token for every sequence of the step before it")
+        kernels.scatter_i32(self.fed_tokens, ctx.seq_slot, tokens)
+
+    def _forward(self, ctx, fed: bool):
+        if fed:
+            from .. import kernels
+            kernels.gather_i32(ctx.tokens, self.fed_tokens, ctx.seq_slot)
+        return self.model.forward(ctx)
+
+    def step(self, entries: List[StepEntry], fed: bool = False) -> Optional[torch.Tensor]:
         """Returns float32 logits [sum(len(e.want)), vocab] in the order of the entries and of
-        their `want` lists (None if nothing is wanted).  The tensor is valid until the next step."""
+        their `want` lists (None if nothing is wanted).  The tensor is valid until the next step.
+
+        fed: every entry brings one token, and that token is not the one in the entry but the one
+        last given to feed() for its slot: the host can launch this step before it has seen the tokens."""
         if not entries:
             return None
         slots = [e.slot for e in entries]
@@ -122,10 +143,12 @@ class Engine:
         n_new = [len(e.tokens) for e in entries]
         if min(n_new) < 1:
             raise StepError("every sequence of a step brings at least one token")
+        if fed and max(n_new) != 1:
+            raise StepError("a step that takes its tokens from the device brings one token per sequence")
         tokens, out_rows, base = [], [], 0
         for e, n in zip(entries, n_new):
             for t in e.tokens:
-                if not (0 <= int(t) < self.spec.vocab_size):
+                if not fed and not (0 <= int(t) < self.spec.vocab_size):
                     raise StepError(f"token id {t} is outside the vocabulary (0..{self.spec.vocab_size - 1})")
             for w in e.want:
                 if not (0 <= int(w) < n):
@@ -154,36 +177,39 @@ class Engine:
             graphed = self.use_graphs and max(n_new) == 1
             shape = StepContext.shape_of(self.cache, slots, n_new, out_rows, bucket=graphed)
             if graphed:
-                logits = self._graphed_step(shape, slots, n_new, tokens, out_rows)
+                logits = self._graphed_step(shape, slots, n_new, tokens, out_rows, fed)
             else:
                 ctx = StepContext(self.cache, self.env.device, *shape, self.err, self.sm_count)
                 buf, ev = self._staging(ctx.meta.numel())
                 ctx.load(slots, n_new, tokens, out_rows, buf)
                 ev.record()
-                logits = self.model.forward(ctx)
+                logits = self._forward(ctx, fed)
+                self._last_ctx = ctx
             for s, n in zip(slots, n_new):
                 book.commit(s, n)
             self.steps_run += 1
         return logits
 
-    def _graphed_step(self, shape, slots, n_new, tokens, out_rows):
+    def _graphed_step(self, shape, slots, n_new, tokens, out_rows, fed=False):
+        shape = shape + (bool(fed),)
         entry = self._graphs.get(shape)
         if entry is None:
             if len(self._graphs) >= self.MAX_GRAPHS:
                 self._graphs.pop(next(iter(self._graphs)))
-            entry = [StepContext(self.cache, self.env.device, *shape, self.err, self.sm_count), None, None]
+            entry = [StepContext(self.cache, self.env.device, *shape[:4], self.err, self.sm_count), None, None]
             self._graphs[shape] = entry
         ctx = entry[0]
+        self._last_ctx = ctx
         buf, ev = self._staging(ctx.meta.numel())
         ctx.load(slots, n_new, tokens, out_rows, buf)
         ev.record()
         if entry[1] is None:
-            logits = self.model.forward(ctx)          # the real step, uncaptured; this also loads every kernel
+            logits = self._forward(ctx, fed)          # the real step, uncaptured; this also loads every kernel
             from ..kernels import ops
             graph = torch.cuda.CUDAGraph()
             n0 = ops.launch_count()
             with torch.cuda.graph(graph):
-                captured = self.model.forward(ctx)    # recorded, not run
+                captured = self._forward(ctx, fed)    # recorded, not run
             entry[1], entry[2] = graph, captured
             entry.append(ops.launch_count() - n0)     # kernels a replay launches
             ops._launches = n0                        # the capture itself launched nothing

@@ -94,6 +94,22 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, err: torch.Tensor) -> torc
     return out
 
 
+def gather_i32(dst: torch.Tensor, src: torch.Tensor, idx: torch.Tensor):
+    """dst[i] = src[idx[i]] (int32, on the device)."""
+    _need_cuda(dst, src, idx)
+    assert dst.dtype == src.dtype == idx.dtype == torch.int32 and dst.numel() == idx.numel()
+    f = _fn(_lib_basic(), "llb_gather_i32", [c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    _check(f(_ptr(dst), _ptr(src), _ptr(idx), idx.numel(), _stream()), "gather_i32")
+
+
+def scatter_i32(dst: torch.Tensor, idx: torch.Tensor, src: torch.Tensor):
+    """dst[idx[i]] = src[i] (int32, on the device; idx without repeats)."""
+    _need_cuda(dst, src, idx)
+    assert dst.dtype == src.dtype == idx.dtype == torch.int32 and src.numel() == idx.numel()
+    f = _fn(_lib_basic(), "llb_scatter_i32", [c_void_p, c_void_p, c_void_p, c_int, c_void_p])
+    _check(f(_ptr(dst), _ptr(idx), _ptr(src), idx.numel(), _stream()), "scatter_i32")
+
+
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                 out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None, want_out: bool = True):
     """residual (float32 [T, H]) += delta, then out = residual * weight / sqrt(mean(residual^2) + eps).

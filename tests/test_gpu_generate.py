@@ -78,6 +78,35 @@ def test_greedy_generation_through_the_entry_point(folders, name, dtype):
     assert not model.engine.cache.live_slots
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_loop_one_step_ahead_of_the_host_decides_like_the_plain_loop(folders, dtype):
+    """With the chosen tokens kept on the device the loop launches a step before it has seen the last tokens;
+    tokens, reasons, steps per request and the slots given back must be those of the loop that waits."""
+    from llaisys_b200.engine.generate import GenerationLoop
+    from llaisys_b200.models import Qwen2
+    from llaisys_b200.sampling import Sampler, SamplingParams
+    cfg = CONFIGS["B"]
+    model = Qwen2(folders.get("B", dtype), dtype=dtype, max_tokens=64 * 3)
+    prompts = random_requests(cfg, [3, 11, 1, 25, 6, 2, 40], seed=9)
+    for params, seed in ((SamplingParams(top_k=1), 0), (SamplingParams(temperature=0.9, top_k=0, top_p=0.95), 5)):
+        free = GenerationLoop(model.engine, Sampler(params, seed), stop_ids=[])
+        free.pipelined = False
+        base = free.run(prompts, 10)
+        # stop tokens that some requests meet early, some late, some never; a limit of one token; a long limit
+        stops = sorted({base[0].tokens[0], base[1].tokens[4], base[3].tokens[9]})
+        for max_new in (1, 2, 10):
+            waiting = GenerationLoop(model.engine, Sampler(params, seed), stop_ids=stops)
+            waiting.pipelined = False
+            want = waiting.run(prompts, max_new)
+            ahead = GenerationLoop(model.engine, Sampler(params, seed), stop_ids=stops)
+            assert ahead.pipelined
+            got = ahead.run(prompts, max_new)
+            assert [(g.tokens, g.reason) for g in got] == [(g.tokens, g.reason) for g in want]
+            assert ahead.batches_run == waiting.batches_run
+            assert not model.engine.cache.live_slots
+    model.engine.check()
+
+
 def test_sampling_generation_is_reproducible_and_batch_independent(folders):
     from llaisys_b200.models import Qwen2
     model = Qwen2(folders["B"], dtype="float32", max_tokens=64 * 8)
