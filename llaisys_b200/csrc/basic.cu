@@ -263,6 +263,70 @@ __global__ void rope_append_kernel(T* __restrict__ qkv, int row_stride, int nh, 
     }
 }
 
+// The same for bfloat16 rows whose head size is a multiple of 16 and whose rows start on 16-byte boundaries: a
+// thread handles eight consecutive pairs (two 16-byte pieces of a head), so every access is a 16-byte one.
+template <bool ROPE, bool APPEND>
+__global__ void __launch_bounds__(128)
+rope_append_vec_kernel(bf16* __restrict__ qkv, int row_stride, int nh, int nkvh, int dh,
+                       const float* __restrict__ cos_t, const float* __restrict__ sin_t, int table_rows,
+                       const int* __restrict__ tok_pos, const int* __restrict__ tok_seq,
+                       const int* __restrict__ seq_start, const int* __restrict__ seq_len_before,
+                       bf16* __restrict__ kpool, bf16* __restrict__ vpool, const int* __restrict__ page_table,
+                       int table_stride, int ring, int* err) {
+    llb_grid_dependency_sync();
+    const int t = blockIdx.x, pos = tok_pos[t], half = dh >> 1, vec_per_half = half >> 3;
+    bf16* row = qkv + (size_t)t * row_stride;
+    const int* table = nullptr;
+    bool store = false;
+    if (APPEND) {
+        const int s = tok_seq[t];
+        table = page_table + (size_t)s * table_stride;
+        const int last = seq_len_before[s] + (seq_start[s + 1] - seq_start[s]) - 1;
+        store = (pos / LLB_PAGE) + ring > (last / LLB_PAGE);
+    }
+    if (ROPE && (pos < 0 || pos >= table_rows)) {
+        if (threadIdx.x == 0) atomicExch(err, 2);
+        return;
+    }
+    // work items: (nh + nkvh) heads x vec_per_half pieces of rotation (or key copy), then nkvh x 2 vec_per_half of values
+    const int n_rot = (nh + nkvh) * vec_per_half, n_val = APPEND && store ? nkvh * 2 * vec_per_half : 0;
+    for (int i = threadIdx.x; i < n_rot + n_val; i += blockDim.x) {
+        if (i < n_rot) {
+            const int h = i / vec_per_half, j = (i - h * vec_per_half) * 8;
+            if (!ROPE && !(APPEND && store && h >= nh)) continue;
+            bf16* x = row + h * dh;
+            uint4 lo = *reinterpret_cast<const uint4*>(x + j), hi = *reinterpret_cast<const uint4*>(x + j + half);
+            if (ROPE) {
+                const float4 c0 = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + j),
+                             c1 = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + j + 4),
+                             s0 = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + j),
+                             s1 = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + j + 4);
+                const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+                const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+                bf16* a = reinterpret_cast<bf16*>(&lo);
+                bf16* b = reinterpret_cast<bf16*>(&hi);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const float av = to_f32(a[e]), bv = to_f32(b[e]);
+                    a[e] = from_f32<bf16>(av * c[e] - bv * sn[e]);
+                    b[e] = from_f32<bf16>(bv * c[e] + av * sn[e]);
+                }
+                *reinterpret_cast<uint4*>(x + j) = lo;
+                *reinterpret_cast<uint4*>(x + j + half) = hi;
+            }
+            if (APPEND && store && h >= nh) {
+                const size_t o = paged_row(table, ring, pos, h - nh, nkvh, dh);
+                *reinterpret_cast<uint4*>(kpool + o + j) = lo;
+                *reinterpret_cast<uint4*>(kpool + o + j + half) = hi;
+            }
+        } else {
+            const int v = i - n_rot, h = v / (2 * vec_per_half), j = (v - h * 2 * vec_per_half) * 8;
+            *reinterpret_cast<uint4*>(vpool + paged_row(table, ring, pos, h, nkvh, dh) + j) =
+                *reinterpret_cast<const uint4*>(row + (nh + nkvh + h) * dh + j);
+        }
+    }
+}
+
 template <typename TT>
 static void launch_rope_append(TT* qkv, int T, int row_stride, int nh, int nkvh, int dh, int do_rope,
                                const float* cos_t, const float* sin_t, int table_rows,
@@ -280,6 +344,27 @@ static void launch_rope_append(TT* qkv, int T, int row_stride, int nh, int nkvh,
 #undef LLB_RA
 }
 
+// bfloat16 with 16-byte pieces where sizes and addresses allow it
+static bool rope_vec_ok(const void* qkv, int row_stride, int dh, const void* cos_t, const void* sin_t, const void* kpool,
+                        const void* vpool) {
+    return dh % 16 == 0 && row_stride % 8 == 0 &&
+           !(((uintptr_t)qkv | (uintptr_t)cos_t | (uintptr_t)sin_t | (uintptr_t)kpool | (uintptr_t)vpool) & 15);
+}
+static void launch_rope_append_vec(bf16* qkv, int T, int row_stride, int nh, int nkvh, int dh, int do_rope,
+                                   const float* cos_t, const float* sin_t, int table_rows, const int* tok_pos,
+                                   int do_append, const int* tok_seq, const int* seq_start, const int* seq_len_before,
+                                   bf16* kpool, bf16* vpool, const int* page_table, int table_stride, int ring, int* err,
+                                   cudaStream_t stream) {
+#define LLB_RAV(R, A)                                                                         \
+    llb_launch(rope_append_vec_kernel<R, A>, dim3(T), dim3(128), 0, stream,                   \
+        qkv, row_stride, nh, nkvh, dh, cos_t, sin_t, table_rows, tok_pos, tok_seq, seq_start, \
+        seq_len_before, kpool, vpool, page_table, table_stride, ring, err)
+    if (do_rope && do_append) LLB_RAV(true, true);
+    else if (do_rope) LLB_RAV(true, false);
+    else if (do_append) LLB_RAV(false, true);
+#undef LLB_RAV
+}
+
 LLB_API int llb_rope_append(void* qkv, int dtype, int T, int row_stride, int nh, int nkvh, int dh,
                             int do_rope, const float* cos_t, const float* sin_t, int table_rows,
                             const int* tok_pos, int do_append, const int* tok_seq,
@@ -288,6 +373,12 @@ LLB_API int llb_rope_append(void* qkv, int dtype, int T, int row_stride, int nh,
                             int* err, cudaStream_t stream) {
     if (T == 0) return 0;
     if (dh % 2) return (int)cudaErrorInvalidValue;
+    if (dtype == LLB_BF16 && rope_vec_ok(qkv, row_stride, dh, cos_t, sin_t, kpool, vpool)) {
+        launch_rope_append_vec((bf16*)qkv, T, row_stride, nh, nkvh, dh, do_rope, cos_t, sin_t, table_rows, tok_pos,
+                               do_append, tok_seq, seq_start, seq_len_before, (bf16*)kpool, (bf16*)vpool, page_table,
+                               table_stride, ring, err, stream);
+        return llb_status();
+    }
     LLB_DISPATCH_DTYPE(dtype, TT,
         launch_rope_append<TT>((TT*)qkv, T, row_stride, nh, nkvh, dh, do_rope, cos_t, sin_t,
                                table_rows, tok_pos, do_append, tok_seq, seq_start, seq_len_before,
