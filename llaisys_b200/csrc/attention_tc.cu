@@ -23,6 +23,13 @@
 // is the same quotient O / l.  With the accumulator out of the registers the compiler has room to
 // interleave the independent chains of a row, which a warp alone on its scheduler needs.
 // Two CTAs share an SM (112 KB of shared memory and 256 tensor-memory columns each).
+//
+// With few row blocks (a prompt of some thousand tokens) the launch is as long as its longest CTA, the last row
+// block, which walks every key tile.  n_split = 2 or 4 then gives each row block to a cluster of CTAs that take even
+// shares of its key tiles; at the end they exchange their rows' (base, sum) pairs, scale their accumulators to the
+// pairs and their accumulators, column share by column share, with the CTA that owns the share (staged in shared
+// memory that is idle by then, sent by bulk copies between two cluster barriers), which scales the shares to the
+// common base, adds them up, divides and stores.
 // Every mbarrier wait is bounded; a wait that runs out sets *err and the CTA leaves in order.
 #include "common.cuh"
 
@@ -49,12 +56,16 @@ constexpr int KV_STAGES = 2;               // value stages (and score buffers)
 constexpr int K_STAGES = 3;                // key stages
 constexpr int OFF_K = Q_BYTES, OFF_V = OFF_K + K_STAGES * KV_BYTES;
 constexpr int OFF_BAR = OFF_V + KV_STAGES * KV_BYTES;
-constexpr int SMEM_BYTES = OFF_BAR + 80;
+constexpr int SMEM_BYTES = OFF_BAR + 96;
+// merge buffers of a split row block, in the shared memory that is idle by then (Q and the ring): staged shares for
+// up to three peers, received shares from up to three peers, the rows' (base, sum) pairs staged and received
+constexpr int OFF_STG = 0, OFF_RECV = 3 * BQ * (DH / 4) * 4, OFF_ML_STG = 2 * OFF_RECV, OFF_ML_RECV = OFF_ML_STG + BQ * 8;
 constexpr int TMEM_COLS = 256;             // S: two buffers at columns [0, 64) and [64, 128); O: columns [128, 128 + DH)
 constexpr int O_COL = 128;
 constexpr float BASE_STEP = 8.f;           // the exponent base follows the maximum in steps larger than this (log2)
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 enum { ERR_ATTN_TC_WAIT = 121, ERR_ATTN_TC_ALIGN = 122 };
+static_assert(OFF_ML_RECV + 4 * BQ * 8 <= OFF_BAR, "the merge buffers fit the idle shared memory");
 
 struct TcAttnParams {
     bf16* out;                  // [T, nh * DH]
@@ -65,6 +76,7 @@ struct TcAttnParams {
     int nh, nkvh, window;
     float scale;
     int* err;
+    int n_split;                // 1, 2 or 4: CTAs (a thread-block cluster) that share the key range of a row block
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -98,6 +110,11 @@ __device__ __forceinline__ bool elect_one() {
     uint32_t pred;
     asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
     return pred != 0;
+}
+__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -192,9 +209,10 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     // A waiter must never be a whole phase behind or ahead of its barrier, or the parity would lie: hence the
     // pairs, and a barrier of its own for the end.
     const uint32_t bar_q = base + OFF_BAR, bar_k01 = bar_q + 8, bar_s = bar_k01 + 8, bar_o = bar_s + 16, bar_p = bar_o + 16,
-                   bar_done = bar_p + 16;
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + 72);
-    volatile int* s_abort = reinterpret_cast<volatile int*>(smem + OFF_BAR + 76);
+                   bar_done = bar_p + 16, bar_merge = bar_done + 8;
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + OFF_BAR + 88);
+    volatile int* s_abort = reinterpret_cast<volatile int*>(smem + OFF_BAR + 92);
+    const int S = p.n_split;
     const int tid = threadIdx.x, warp = tid >> 5;
 
     if (tid == 0) {
@@ -208,12 +226,14 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             mbar_init(bar_o + 8 * s, 1);
         }
         mbar_init(bar_done, 1);
+        mbar_init(bar_merge, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        if (S > 1) mbar_expect_tx(bar_merge, (uint32_t)((S - 1) * (BQ * (DH / S) * 4 + BQ * 8)));    // what the peers will send
     }
     if (warp == 0) {
         __syncwarp();
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                     ::"r"(base + OFF_BAR + 72), "r"((uint32_t)TMEM_COLS) : "memory");
+                     ::"r"(base + OFF_BAR + 88), "r"((uint32_t)TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -223,17 +243,28 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     llb_grid_dependency_sync();
 
     // ---- which rows, which keys
-    const int b = blockIdx.z, head = blockIdx.y;
+    const int b = blockIdx.z, head = blockIdx.x;
     const int tok0 = p.seq_start[b], n_new = p.seq_start[b + 1] - tok0, len_before = p.seq_len_before[b];
-    const int t0 = blockIdx.x * BQ;
+    uint32_t rank = 0;
+    if (S > 1) asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    // Row blocks along y, heads along x: CTAs are handed out x first, so the row blocks with the most key tiles (the
+    // last ones, which get the first y) start first for every head, and the short ones fill the end of the launch.
+    const int t0 = ((int)(gridDim.y - 1 - blockIdx.y) / S) * BQ;
     const bool active = t0 < n_new && !*s_abort;
     const int kvh = head / (p.nh / p.nkvh);
     const int n_rows = min(BQ, n_new - t0);
     const int first_pos = len_before + t0, last_pos = first_pos + n_rows - 1;
     const int key_lo = p.window > 0 ? max(0, first_pos - p.window + 1) : 0;
-    const int tile_lo = key_lo / BKV, n_tiles = active ? last_pos / BKV + 1 - tile_lo : 0;
+    int tile_lo = key_lo / BKV, n_tiles = active ? last_pos / BKV + 1 - tile_lo : 0;
+    if (S > 1) {          // this CTA's even share of the row block's tiles
+        const int q = n_tiles / S, r = n_tiles - q * S;
+        tile_lo += (int)rank * q + min((int)rank, r);
+        n_tiles = q + ((int)rank < r ? 1 : 0);
+    }
     const int* table = p.page_table + (size_t)b * p.table_stride;
     bool failed = false;
+    float m = -INFINITY, l = 0.f;                                   // row threads: the exponent base of the row, its sum
+    const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
 
     if (warp == 4) {
         // ================================================= copies and matrix products (one elected lane issues)
@@ -347,8 +378,6 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const int qlo = p.window > 0 ? max(0, qpos - p.window + 1) : 0;
         const float scale_log2 = p.scale * 1.4426950408889634f;
         const uint64_t scale2 = twice(scale_log2);
-        const uint32_t lane_addr = tmem + ((uint32_t)(warp * 32) << 16);
-        float m = -INFINITY, l = 0.f;                               // m: the exponent base of the row
 
         for (int i = 0; i < n_tiles && !failed; ++i) {
             const int s = i % KV_STAGES;
@@ -418,6 +447,11 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         }
         if (!failed && n_tiles > 0) failed = !warp_wait(bar_done, 0, s_abort);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+    // Every thread of every CTA of a cluster passes this barrier, whatever happened before: behind it nobody reads or
+    // fills its ring any more, so the peers may write into it.
+    if (S > 1) asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (warp < 4 && S == 1) {
         if (n_tiles > 0 && !__any_sync(0xffffffffu, failed)) {
             const float inv = 1.0f / l;
             bf16* dst = p.out + (size_t)(tok0 + t0 + tid) * p.nh * DH + (size_t)head * DH;
@@ -440,6 +474,107 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                 }
             }
         }
+    }
+    if (S > 1) {
+        // ================================================= merge of a split row block
+        // Each CTA stages, per peer, the column share of its accumulator that the peer owns, and its rows' (base, sum)
+        // pairs; after the cluster barrier above one thread sends each block with one bulk copy into the peer's
+        // shared memory, counted on the peer's merge barrier.  (Storing the pieces remotely one by one was measured:
+        // four thousand 16-byte stores per CTA took 10 us, with an mbarrier count on each 12 us.)
+        const int COLS = DH / S, PCS = COLS / 4, SWZ = PCS >= 8 ? 7 : PCS - 1;       // this CTA's columns; 16-byte pieces of a row
+        const uint32_t share_bytes = (uint32_t)(BQ * COLS * 4);
+        const bool take_part = warp < 4 && active && !__any_sync(0xffffffffu, failed);
+        float2* ml_recv = reinterpret_cast<float2*>(smem + OFF_ML_RECV);
+        if (take_part) {
+            reinterpret_cast<float2*>(smem + OFF_ML_STG)[tid] = make_float2(m, l);
+            ml_recv[rank * BQ + tid] = make_float2(m, l);
+#pragma unroll 1
+            for (int c0 = 0; c0 < DH; c0 += 32) {
+                const int owner = c0 / COLS;
+                if (owner == (int)rank) continue;
+                uint32_t v[32];
+                if (n_tiles > 0) {
+                    tmem_ld16_nowait(lane_addr + O_COL + c0, v);
+                    tmem_ld16_nowait(lane_addr + O_COL + c0 + 16, v + 16);
+                    tmem_wait();
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) v[e] = 0u;
+                }
+                uint8_t* row = smem + OFF_STG + (size_t)(owner < (int)rank ? owner : owner - 1) * share_bytes + (size_t)tid * (COLS * 4);
+                const int pc0 = (c0 % COLS) / 4;
+#pragma unroll
+                for (int e = 0; e < 32; e += 4)
+                    *reinterpret_cast<uint4*>(row + (((pc0 + e / 4) ^ (tid & SWZ)) * 16)) = make_uint4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");         // the staged blocks before the bulk copies read them
+        }
+        // every thread of the cluster: all blocks are staged (and every ring is idle)
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+        if (take_part && tid == 0) {
+            for (int o = 0; o < S; ++o) {
+                if (o == (int)rank) continue;
+                const uint32_t slot = (uint32_t)(o < (int)rank ? o : o - 1);          // where this CTA staged the peer's share
+                const uint32_t mine = rank < (uint32_t)o ? rank : rank - 1;           // this CTA's place among the peer's sources
+                const uint32_t rbar = mapa(bar_merge, (uint32_t)o);
+                asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(mapa(base + OFF_RECV + mine * share_bytes, (uint32_t)o)), "r"(base + OFF_STG + slot * share_bytes),
+                               "r"(share_bytes), "r"(rbar) : "memory");
+                asm volatile("cp.async.bulk.shared::cluster.shared::cta.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(mapa(base + OFF_ML_RECV + rank * (uint32_t)(BQ * 8), (uint32_t)o)), "r"(base + OFF_ML_STG),
+                               "r"((uint32_t)(BQ * 8)), "r"(rbar) : "memory");
+            }
+        }
+        bool got = true;
+        if (take_part) got = warp_wait(bar_merge, 0, s_abort);
+        if (take_part && !__any_sync(0xffffffffu, !got)) {
+            // ---- this CTA's columns of the row (every lane takes part in the tensor-memory loads; rows past the end store nothing): every source scaled to the common base, added, divided, stored
+            float M = -INFINITY, L = 0.f, f[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int sp = 0; sp < S; ++sp) M = fmaxf(M, ml_recv[sp * BQ + tid].x);
+            for (int sp = 0; sp < S; ++sp) {
+                const float2 v = ml_recv[sp * BQ + tid];
+                f[sp] = v.x == -INFINITY ? 0.f : fast_exp2(v.x - M);
+                L += v.y * f[sp];
+            }
+            const float inv = 1.0f / L;
+            bf16* dst = p.out + (size_t)(tok0 + t0 + tid) * p.nh * DH + (size_t)head * DH + rank * COLS;
+#pragma unroll 1
+            for (int c0 = 0; c0 < COLS; c0 += 32) {
+                float acc[32];
+                if (n_tiles > 0) {
+                    uint32_t v[32];
+                    tmem_ld16_nowait(lane_addr + O_COL + rank * COLS + c0, v);
+                    tmem_ld16_nowait(lane_addr + O_COL + rank * COLS + c0 + 16, v + 16);
+                    tmem_wait();
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) acc[e] = __uint_as_float(v[e]) * f[rank];
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) acc[e] = 0.f;
+                }
+                for (int sp = 0; sp < S; ++sp) {
+                    if (sp == (int)rank) continue;
+                    const uint8_t* row = smem + OFF_RECV + (size_t)(sp < (int)rank ? sp : sp - 1) * share_bytes + (size_t)tid * (COLS * 4);
+#pragma unroll
+                    for (int e = 0; e < 32; e += 4) {
+                        const float4 x = *reinterpret_cast<const float4*>(row + (((c0 / 4 + e / 4) ^ (tid & SWZ)) * 16));
+                        acc[e] += x.x * f[sp]; acc[e + 1] += x.y * f[sp]; acc[e + 2] += x.z * f[sp]; acc[e + 3] += x.w * f[sp];
+                    }
+                }
+#pragma unroll
+                for (int d = 0; d < 32; d += 8) {
+                    uint4 w;
+                    w.x = pack_bf16(acc[d] * inv, acc[d + 1] * inv);
+                    w.y = pack_bf16(acc[d + 2] * inv, acc[d + 3] * inv);
+                    w.z = pack_bf16(acc[d + 4] * inv, acc[d + 5] * inv);
+                    w.w = pack_bf16(acc[d + 6] * inv, acc[d + 7] * inv);
+                    if (tid < n_rows) *reinterpret_cast<uint4*>(dst + c0 + d) = w;
+                }
+            }
+        }
+        if (take_part && !got) failed = true;
+        // no CTA may leave while a bulk copy still reads its shared memory: all have received what was sent to them
+        asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
     if (failed) {
         *s_abort = 1;
@@ -517,7 +652,9 @@ LLB_API int llb_attn_tc_prefill(const void* q, int T, int row_stride, const void
     if (B == 0 || max_new == 0) return 0;
     if (p.nkvh <= 0 || p.nh % p.nkvh || !(p.scale > 0.f) || row_stride % 8 || (((uintptr_t)q | (uintptr_t)kpool | (uintptr_t)vpool | (uintptr_t)p.out) & 15))
         return (int)cudaErrorInvalidValue;
-    dim3 grid((max_new + BQ - 1) / BQ, p.nh, B);
+    if (p.n_split != 1 && p.n_split != 2 && p.n_split != 4) return (int)cudaErrorInvalidValue;
+    if (DH / p.n_split < 32) return (int)cudaErrorInvalidValue;          // a column share is whole 32-column pieces
+    dim3 grid(p.nh, ((max_new + BQ - 1) / BQ) * p.n_split, B);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
     CUtensorMap mq, mk, mv;
     int rc = get_map(q, T, p.nh * DH, row_stride, BQ, &mq);
@@ -532,6 +669,30 @@ LLB_API int llb_attn_tc_prefill(const void* q, int T, int row_stride, const void
         if (e != cudaSuccess) return -2000 - (int)e;
         configured = true;
     }
-    llb_launch(attn_tc_prefill_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, mq, mk, mv, p);
+    if (p.n_split == 1) {
+        llb_launch(attn_tc_prefill_kernel, grid, dim3(THREADS), SMEM_BYTES, stream, mq, mk, mv, p);
+        return llb_status();
+    }
+    llb_prefer_max_shared((const void*)attn_tc_prefill_kernel);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (llb_pdl_enabled()) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = 1;
+    attr[n_attr].val.clusterDim.y = (unsigned)p.n_split;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    cudaLaunchKernelEx(&cfg, attn_tc_prefill_kernel, mq, mk, mv, p);
     return llb_status();
 }

@@ -343,7 +343,7 @@ def decode_fusion_ok(dtype: torch.dtype, dh: int) -> bool:
 class _TcAttnParams(ctypes.Structure):
     _fields_ = [("out", c_void_p), ("page_table", c_void_p), ("table_stride", c_int), ("seq_start", c_void_p),
                 ("seq_len_before", c_void_p), ("nh", c_int), ("nkvh", c_int), ("window", c_int), ("scale", c_float),
-                ("err", c_void_p)]
+                ("err", c_void_p), ("n_split", c_int)]
 
 
 TC_ATTENTION = True                          # tests switch the tcgen05 prefill attention off to compare
@@ -383,11 +383,13 @@ def _attn_params(qkv, out, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_sta
 
 
 def attention_prefill(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_start, seq_len_before,
-                      n_seqs: int, max_new: int, window, scale, all_from_cache: bool = False) -> torch.Tensor:
+                      n_seqs: int, max_new: int, window, scale, all_from_cache: bool = False,
+                      tc_split: int = 0) -> torch.Tensor:
     """Attention of the new tokens of each sequence over its cached keys (positions before the
     step) and the step's own keys, read from the packed projections `qkv` [T, (nh + 2 nkvh) dh]
     whose query and key heads are already rotated.  With all_from_cache the step's keys are
-    read from the cache too (they were put there by an earlier call).  Returns [T, nh * dh]."""
+    read from the cache too (they were put there by an earlier call).  Returns [T, nh * dh].
+    tc_split: CTAs per row block of the tcgen05 kernel (1, 2 or 4; 0: chosen by the number of row blocks)."""
     _need_cuda(qkv, kpool, vpool, page_table)
     assert qkv.dtype == kpool.dtype == vpool.dtype
     out = torch.empty((qkv.shape[0], nh * dh), dtype=qkv.dtype, device=qkv.device)
@@ -397,6 +399,11 @@ def attention_prefill(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_sta
         p.seq_start, p.seq_len_before = seq_start.data_ptr(), seq_len_before.data_ptr()
         p.nh, p.nkvh, p.window, p.scale = nh, nkvh, int(window or 0), scale
         p.err = _tc_resources(qkv.device)[2].data_ptr()
+        # few row blocks (up to one and a half per SM): two CTAs share each block's key range, so that the longest
+        # CTA gets shorter (measured at 12 heads: 30.5 vs 33.7 us at 2,048 tokens, 73 vs 64 us at 4,096; four CTAs
+        # per block always lost to the cost of the merge)
+        ctas = -(-max_new // 128) * nh * n_seqs
+        p.n_split = tc_split if tc_split else (2 if ctas * 2 <= 3 * _sm_count(qkv.device) and dh >= 64 else 1)
         f = _fn(load_module("attention_tc.cu", {"LLB_HEAD_DIM": dh}), "llb_attn_tc_prefill",
                 [c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, _TcAttnParams, c_int, c_int, c_void_p])
         _check(f(qkv.data_ptr(), qkv.shape[0], qkv.stride(0), kpool.data_ptr(), vpool.data_ptr(), kpool.shape[0],

@@ -458,6 +458,11 @@ def test_attention_prefill_from_cache_tcgen05(nh, nkvh, dh, window):
     got = kernels.attention_prefill(*args, all_from_cache=True)
     assert kernels.tc_error(DEV) == 0
     _close(got, want, dtype, atol=6e-3)
+    # every way of sharing a row block's keys among the CTAs of a cluster
+    for split in (1, 2, 4):
+        if dh // split >= 32:
+            _close(kernels.attention_prefill(*args, all_from_cache=True, tc_split=split), want, dtype, atol=6e-3)
+            assert kernels.tc_error(DEV) == 0
     # and the same through the mma.sync kernel
     kernels.ops.TC_ATTENTION = False
     try:
