@@ -561,10 +561,12 @@ __global__ void attn_mma_combine_kernel(bf16* __restrict__ out, const float* __r
 __global__ void __launch_bounds__(THREADS, 3) attn_mma_prefill_kernel(MmaAttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int b = blockIdx.z, head = blockIdx.y;
+    // Heads along x, row blocks along y with the last (longest) ones first: blocks are handed out x first, so the
+    // long blocks of every head start first and the short ones fill the end of the launch.
+    const int b = blockIdx.z, head = blockIdx.x;
     llb_grid_dependency_sync();
     const int tok0 = p.seq_start[b], n_new = p.seq_start[b + 1] - tok0, len_before = p.seq_len_before[b];
-    const int t0 = blockIdx.x * 64;
+    const int t0 = (int)(gridDim.y - 1 - blockIdx.y) * 64;
     if (t0 >= n_new) return;
     Ring<STAGES_PREFILL> ring = make_ring<STAGES_PREFILL>(smem_raw);
     const int kvh = head / (p.nh / p.nkvh);
@@ -650,7 +652,7 @@ LLB_API int llb_attn_mma_head_dim() { return DH; }
 LLB_API int llb_attn_mma_prefill(MmaAttnParams p, int B, int max_new, cudaStream_t stream) {
     if (B == 0 || max_new == 0) return 0;
     if (!aligned_ok(p)) return (int)cudaErrorInvalidValue;
-    dim3 grid((max_new + 63) / 64, p.nh, B);
+    dim3 grid(p.nh, (max_new + 63) / 64, B);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
     int rc = configure<0>(attn_mma_prefill_kernel, smem_bytes(STAGES_PREFILL));
     if (rc) return rc;
