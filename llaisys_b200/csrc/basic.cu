@@ -142,6 +142,84 @@ add_rmsnorm_kernel(float* __restrict__ residual, const TD* __restrict__ delta, i
     }
 }
 
+// The same for the common case of the bfloat16 path (bfloat16 delta, weight and output, a width that is a multiple
+// of 8 up to 8192, 16-byte aligned rows): a thread owns groups of eight consecutive columns, so that every access is a
+// 16-byte one (two for the float32 residual).  Sums are formed in the same order as above.
+template <int GROUPS>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_vec_kernel(float* __restrict__ residual, const bf16* __restrict__ delta, int n_part, size_t part_stride,
+                       const bf16* __restrict__ weight, bf16* __restrict__ out, const int* __restrict__ rows, int H,
+                       float eps, int write_back) {
+    __shared__ float red[8];
+    const int r = blockIdx.x, tid = threadIdx.x, n_groups = H >> 3;
+    uint4 w[GROUPS];
+#pragma unroll
+    for (int i = 0; i < GROUPS; ++i) {         // the norm weight depends on no earlier kernel: fetch it first
+        const int gidx = tid + i * 256;
+        w[i] = (gidx < n_groups && out) ? *reinterpret_cast<const uint4*>(weight + gidx * 8) : make_uint4(0, 0, 0, 0);
+    }
+    llb_grid_dependency_sync();
+    const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+    float* res = residual + src * H;
+    float x[GROUPS][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < GROUPS; ++i) {
+        const int gidx = tid + i * 256;
+        if (gidx < n_groups) {
+            const float4 a = *reinterpret_cast<const float4*>(res + gidx * 8), b = *reinterpret_cast<const float4*>(res + gidx * 8 + 4);
+            x[i][0] = a.x; x[i][1] = a.y; x[i][2] = a.z; x[i][3] = a.w; x[i][4] = b.x; x[i][5] = b.y; x[i][6] = b.z; x[i][7] = b.w;
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) x[i][e] = 0.f;
+        }
+    }
+    if (delta) {
+#pragma unroll
+        for (int i = 0; i < GROUPS; ++i) {
+            const int gidx = tid + i * 256;
+            if (gidx >= n_groups) continue;
+            float d[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int q = 0; q < n_part; ++q) {
+                const uint4 v = *reinterpret_cast<const uint4*>(delta + q * part_stride + src * H + gidx * 8);
+                const bf16* e8 = reinterpret_cast<const bf16*>(&v);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) d[e] += to_f32(e8[e]);
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) x[i][e] += d[e];
+            if (write_back) {
+                *reinterpret_cast<float4*>(res + gidx * 8) = make_float4(x[i][0], x[i][1], x[i][2], x[i][3]);
+                *reinterpret_cast<float4*>(res + gidx * 8 + 4) = make_float4(x[i][4], x[i][5], x[i][6], x[i][7]);
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < GROUPS; ++i)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += x[i][e] * x[i][e];
+    ss = warp_sum(ss);
+    const int lane = tid & 31, wp = tid >> 5;
+    if (lane == 0) red[wp] = ss;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) tot += red[i];
+    const float inv = 1.0f / sqrtf(tot / (float)H + eps);
+    if (!out) return;
+#pragma unroll
+    for (int i = 0; i < GROUPS; ++i) {
+        const int gidx = tid + i * 256;
+        if (gidx >= n_groups) continue;
+        const bf16* w8 = reinterpret_cast<const bf16*>(&w[i]);
+        uint4 o;
+        bf16* o8 = reinterpret_cast<bf16*>(&o);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o8[e] = from_f32<bf16>(x[i][e] * to_f32(w8[e]) * inv);
+        *reinterpret_cast<uint4*>(out + (size_t)r * H + gidx * 8) = o;
+    }
+}
+
 template <typename TD, typename TW>
 static int add_rmsnorm_out(float* residual, const void* delta, int n_part, size_t part_stride,
                            const void* weight, void* out, int out_dtype, const int* rows, int R,
@@ -168,6 +246,18 @@ LLB_API int llb_add_rmsnorm(float* residual, const void* delta, int delta_dtype,
     if (R == 0) return 0;
     if ((size_t)H * sizeof(float) > 200 * 1024) return (int)cudaErrorInvalidValue;
     if (rows && write_back) return (int)cudaErrorInvalidValue;
+    // the bfloat16 case with 16-byte accesses
+    if ((!delta || delta_dtype == LLB_BF16) && weight_dtype == LLB_BF16 && (!out || out_dtype == LLB_BF16) && H % 8 == 0 &&
+        H <= 8192 && part_stride % 8 == 0 &&
+        !(((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15)) {
+#define LLB_NV(G) llb_launch(add_rmsnorm_vec_kernel<G>, dim3(R), dim3(256), 0, stream, residual, (const bf16*)delta, n_part, \
+                             (size_t)part_stride, (const bf16*)weight, (bf16*)out, rows, H, eps, write_back)
+        if (H <= 2048) LLB_NV(1);
+        else if (H <= 4096) LLB_NV(2);
+        else LLB_NV(4);
+#undef LLB_NV
+        return llb_status();
+    }
     if (!delta) delta_dtype = LLB_F32;
     LLB_DISPATCH_DTYPE(delta_dtype, TD, {
         LLB_DISPATCH_DTYPE(weight_dtype, TW, {

@@ -51,7 +51,7 @@ def test_embedding(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,H", [(1, 8), (5, 200), (37, 1536), (3, 5000)])
+@pytest.mark.parametrize("T,H", [(1, 8), (5, 200), (37, 1536), (3, 5000), (4, 3584), (2, 8192), (3, 1001)])
 def test_add_rmsnorm(dtype, T, H):
     from llaisys_b200 import kernels
     rng = np.random.default_rng(T * H)
