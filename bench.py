@@ -227,16 +227,14 @@ def main() -> int:
     for _ in range(3):
         prefill_once()
     torch.cuda.synchronize()
-    reps = 9                       # each timed by its own pair of events; the median is reported
-    times = []
+    reps = 8                       # back to back: the host enqueues a step while the device still runs the one before
+    a, b = events()
+    a.record()
     for _ in range(reps):
-        a, b = events()
-        a.record()
         prefill_once()
-        b.record()
-        torch.cuda.synchronize()
-        times.append(a.elapsed_time(b))
-    prefill_ms = statistics.median(times)
+    b.record()
+    torch.cuda.synchronize()
+    prefill_ms = a.elapsed_time(b) / reps
     lin, head = linear_params(cfg_dict, layers)
     dh, nh = cfg.head_dim, cfg.num_attention_heads
     attn_flops = layers * 4 * nh * dh * (PREFILL_TOKENS * (PREFILL_TOKENS + 1) // 2)
