@@ -27,6 +27,7 @@ NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC
 
 _lock = threading.RLock()
 _loaded: dict[str, ctypes.CDLL] = {}
+_loaded_fast: dict = {}      # (source, definitions) -> handle, found without forming the module name
 
 
 class BuildError(RuntimeError):
@@ -123,12 +124,17 @@ def compile_module(source: str, defines: dict | None = None, verbose: bool = Tru
 
 def load_module(source: str, defines: dict | None = None) -> ctypes.CDLL:
     """The ctypes handle of a module, compiling it first if its library is missing or stale."""
+    fast = (source, tuple(sorted(defines.items())) if defines else ())
+    lib = _loaded_fast.get(fast)
+    if lib is not None:
+        return lib
     key = module_name(source, defines)
     with _lock:
         lib = _loaded.get(key)
         if lib is None:
             lib = ctypes.CDLL(str(compile_module(source, defines)))
             _loaded[key] = lib
+        _loaded_fast[fast] = lib
         return lib
 
 

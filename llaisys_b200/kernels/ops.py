@@ -1,6 +1,7 @@
 from __future__ import annotations
 
 import ctypes
+import functools
 from ctypes import c_double, c_float, c_int, c_longlong, c_ulonglong, c_void_p
 from typing import Optional
 
@@ -28,7 +29,8 @@ def _ptr(t: Optional[torch.Tensor]):
 
 
 def _stream():
-    return torch.cuda.current_stream().cuda_stream
+    # the raw handle of torch's current stream on the current device, without the Python layers in between
+    return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
 
 
 def _need_cuda(*ts):
@@ -199,13 +201,20 @@ def tc_error(device) -> int:
     return int(r[2].item()) if r else 0
 
 
+_sm_counts = {}
+
+
 def _sm_count(device) -> int:
-    return torch.cuda.get_device_properties(device).multi_processor_count
+    n = _sm_counts.get(device)
+    if n is None:
+        n = _sm_counts[device] = torch.cuda.get_device_properties(device).multi_processor_count
+    return n
 
 
 _TC_STAGES = {False: {16: 5, 32: 4, 64: 4, 128: 6, 256: 4}, True: {16: 3, 32: 3, 64: 4, 128: 4, 256: 3}}
 
 
+@functools.lru_cache(maxsize=4096)
 def tc_plan(T: int, rows_out: int, K: int, sms: int, dual: bool = False):
     """(tokens per tile, K splits) of a tensor-core launch.
 
