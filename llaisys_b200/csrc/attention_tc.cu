@@ -313,7 +313,7 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                     tma_load_2d(base + OFF_K + blk * (BKV * 128), &map_k, bar_k01, blk * 64, r0);
                     if (n_tiles > 1) tma_load_2d(base + OFF_K + KV_BYTES + blk * (BKV * 128), &map_k, bar_k01, blk * 64, r1);
                 }
-                // tile 0: its values and the keys of tile 2; tile 1: its values (the keys of tile 3 follow in round 0)
+                // tile 0: its values and the keys of tile 2; tile 1: its values (the keys of tile 3 follow at the first tile)
                 issue_v(0, r0, bar_p);
                 if (n_tiles > 2) issue_k(2, r2, bar_p); else mbar_arrive(bar_p);
                 if (n_tiles > 1) issue_v(1, r1, bar_p + 8);

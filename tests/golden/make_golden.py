@@ -97,7 +97,9 @@ def build_reference(src: Path, work: Path) -> Path:
 
 
 def main():
-    src = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        sys.exit("usage: make_golden.py <checkout of xsmccc/llaisys>")
+    src = Path(sys.argv[1])
     with tempfile.TemporaryDirectory() as tmp:
         work = Path(tmp)
         sys.path.insert(0, str(build_reference(src, work)))
