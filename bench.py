@@ -57,6 +57,9 @@ SHAPES = {
                                       max_window_layers=64)),
 }
 PROMPT_LEN, CONTEXT, PREFILL_TOKENS = 2048, 4096, 2048
+# The two larger shapes' own workloads: (requests, shortest prompt, longest prompt, decode steps).  The prompts
+# of unequal lengths go through one prefill step together, then every request decodes that many tokens.
+OWN_WORKLOADS = {"7b": (16, 256, 4096, 256), "32b": (64, 512, 2048, 128)}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -153,6 +156,58 @@ def profile_run(args, model, cfg, rng) -> int:
     return 0
 
 
+def own_workload(args, model, cfg, cfg_dict, layers, full_layers, shape_name, pk, pk_src, rng) -> int:
+    """A shape's own workload through the generation loop (host token ids in and out): prompts of unequal
+    lengths in one prefill step, then the stated number of decode steps.  Run twice; the second run is timed."""
+    import torch
+
+    from llaisys_b200.cache import CacheConfig
+    from llaisys_b200.engine import Engine
+    from llaisys_b200.engine.generate import GenerationLoop
+    from llaisys_b200.sampling import Sampler, SamplingParams
+
+    n_req, lo, hi, steps = OWN_WORKLOADS[args.shape]
+    lengths = rng.integers(lo, hi + 1, size=n_req).tolist()
+    prompts = [rng.integers(0, cfg.vocab_size, size=n).tolist() for n in lengths]
+    room = sum(-(-(n + steps + 1) // 64) * 64 for n in lengths)
+    engine = Engine(model, CacheConfig(max_tokens=room, max_seqs=n_req))
+    for timed in (False, True):
+        loop = GenerationLoop(engine, Sampler(SamplingParams(top_k=1)), stop_ids=[])
+        torch.cuda.synchronize()
+        with ClockSampler() as clk:
+            t0 = time.perf_counter()
+            out = loop.run(prompts, max_new_tokens=steps + 1)
+            marks = loop.step_marks
+        engine.check()
+    assert all(len(g.tokens) == steps + 1 for g in out) and loop.batches_run == 1
+    T = sum(lengths)
+    prefill_s, decode_s = marks[0] - t0, marks[-1] - marks[0]
+    lin, head = linear_params(cfg_dict, layers)
+    attn_flops = layers * 4 * cfg.num_attention_heads * cfg.head_dim * sum(n * (n + 1) // 2 for n in lengths)
+    prefill_flops = 2 * T * lin + 2 * n_req * head + attn_flops
+    weight_bytes = model.weight_bytes() - model.embedding.weight.numel() * 2 + n_req * cfg.hidden_size * 2
+    kv_bytes = (T + n_req * steps // 2) * engine.cache.bytes_per_token()
+    ms = decode_s * 1e3 / steps
+    achieved = (weight_bytes + kv_bytes) / (ms / 1e3) / 1e9
+    print(json.dumps({
+        "metric": f"decode tok/s of the {shape_name}'s own workload, end to end through the generation loop",
+        "value": round(n_req * steps / decode_s, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": steps,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights N(0,0.02), seeded uniform-random token ids",
+        "config": {"model": shape_name, "layers": layers, "layers_of_config": full_layers, "hidden": cfg.hidden_size,
+                   "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": n_req,
+                   "prompt_len_min": min(lengths), "prompt_len_max": max(lengths), "prompt_tokens": T,
+                   "decode_steps": steps, "cache_tokens": room, "parallelism": "single GPU", "peaks": pk_src},
+        "clocks": clk.summary(),
+        "prefill": {"value": round(T / prefill_s, 1), "tokens": T, "ms": round(prefill_s * 1e3, 2),
+                    "frac": round(prefill_flops / prefill_s / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+    }))
+    return 0
+
+
 def reference_arm():
     print(json.dumps({"impl": "reference", "unavailable":
                       "xsmccc/llaisys cannot be installed offline (pip: no setup.py or pyproject.toml at its root; its "
@@ -170,6 +225,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--shape", choices=sorted(SHAPES), default="1.5b", help="layer sizes (default: the benchmark's)")
+    ap.add_argument("--workload", choices=["uniform", "own"], default="uniform",
+                    help="own: the 7b / 32b shape's own workload (unequal prompts in one prefill step, then decoding) "
+                         "through the generation loop, instead of the benchmark's equal 2,048-token prompts")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / batch 64 points and the end-to-end run")
     ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
                     help="for a profiler: warm up, then run two uncaptured steps of this kind between "
@@ -179,6 +237,9 @@ def main() -> int:
         return reference_arm()
     if args.gpus != 1:
         print(f"bench.py: llaisys_b200 is a single-GPU library; --gpus {args.gpus} is not supported (use --gpus 1)")
+        return 2
+    if args.workload == "own" and args.shape not in OWN_WORKLOADS:
+        print(f"bench.py: --workload own needs --shape {' or '.join(sorted(OWN_WORKLOADS))}")
         return 2
     if args.warmup < 3:
         args.warmup = 3
@@ -214,6 +275,8 @@ def main() -> int:
 
     if args.profile:
         return profile_run(args, model, cfg, rng)
+    if args.workload == "own":
+        return own_workload(args, model, cfg, cfg_dict, layers, full_layers, shape_name, pk, pk_src, rng)
 
     # ---- prefill: one step over 2,048 tokens
     engine = Engine(model, CacheConfig(max_tokens=max(64, args.batch) * CONTEXT, max_seqs=max(64, args.batch)))
