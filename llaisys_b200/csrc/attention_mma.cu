@@ -647,8 +647,6 @@ bool aligned_ok(const MmaAttnParams& p) {
 
 }  // namespace
 
-LLB_API int llb_attn_mma_head_dim() { return DH; }
-
 LLB_API int llb_attn_mma_prefill(MmaAttnParams p, int B, int max_new, cudaStream_t stream) {
     if (B == 0 || max_new == 0) return 0;
     if (!aligned_ok(p)) return (int)cudaErrorInvalidValue;

@@ -257,8 +257,6 @@ static int launch_attn(const AttnParams& p, dim3 grid, cudaStream_t stream) {
     return llb_status();
 }
 
-LLB_API int llb_attn_head_dim() { return DH; }
-
 // Prefill and any step with more than one new token in some sequence.  max_new is the largest
 // number of new tokens of a sequence in the batch.
 LLB_API int llb_attn_prefill(AttnParams p, int dtype, int B, int max_new, cudaStream_t stream) {

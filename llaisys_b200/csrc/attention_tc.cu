@@ -643,8 +643,6 @@ int get_map(const void* ptr, long long rows, int cols, int ld, int box_rows, CUt
 
 }  // namespace
 
-LLB_API int llb_attn_tc_head_dim() { return DH; }
-
 // q: the packed projections [T, row_stride] (query heads first, already rotated); kpool / vpool: one call's pages
 // [n_pages, nkvh, 64, DH], already holding the step's keys and values.  max_new: most new tokens of a sequence.
 LLB_API int llb_attn_tc_prefill(const void* q, int T, int row_stride, const void* kpool, const void* vpool, int n_pages,

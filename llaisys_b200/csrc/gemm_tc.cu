@@ -580,11 +580,8 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& g, dim3
 
 }  // namespace
 
-// Largest number of K splits a launch may use for this shape (every split gets at least one k-block).
-LLB_API int llb_gemm_tc_max_splits(int K) { return (K + BK - 1) / BK; }
-
 // float32 elements of scratch a launch needs (0 when splits == 1).
-LLB_API long long llb_gemm_tc_scratch_elems(int T, int N, int bn, int splits, int dual) {
+static long long llb_gemm_tc_scratch_elems(int T, int N, int bn, int splits, int dual) {
     if (splits <= 1) return 0;
     long long tiles = (long long)((N + BM - 1) / BM) * ((T + bn - 1) / bn);
     return tiles * splits * (dual ? 2 : 1) * bn * BM;

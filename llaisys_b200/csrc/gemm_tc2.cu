@@ -1,0 +1,400 @@
+// bfloat16 matrix product for many tokens (prefill) on pairs of SMs:
+//
+//     Y[T, N] = X[T, K] * W[N, K]^T (+ bias[N]),   float32 accumulation, bfloat16 output
+//
+// (the linear operator of xsmccc/llaisys, src/ops/linear/cpu/linear_cpu.cpp:21-40), and with DUAL
+// the fused gate/up product  Y[T, I] = up * gate / (1 + exp(-gate))
+// (src/ops/swiglu/cpu/swiglu_cpu.cpp:13-21) of a [2I, K] matrix whose up rows lie dual_offset
+// rows below the gate rows.
+//
+// Two CTAs on neighbouring SMs (a cluster of two) work on one tile of 256 weight rows x BN tokens
+// with tcgen05.mma.cta_group::2: each CTA holds its own 128 weight rows and HALF of the token
+// tile in shared memory, the tensor cores of both SMs read both halves, and each CTA's tensor
+// memory receives its 128 rows x BN tokens.  An SM thus fills a third (a quarter with DUAL) less
+// shared memory per FLOP than it would alone.  The pair is persistent: it walks over tiles
+// pair, pair + pairs, ...; the accumulator is double-buffered in tensor memory (2 x 256 columns),
+// so the epilogue of a tile (tcgen05.ld, bias or SwiGLU, transposition through shared memory,
+// 16-byte stores) runs while the tensor cores work on the next one.
+//
+//   warp 0      TMA producer (one thread): ring of STAGES k-blocks, both CTAs, completion counted on the
+//               leader CTA's barrier
+//   warp 1      tcgen05.mma issue (one thread of the leader CTA); tcgen05.commit multicast frees the ring
+//               slot in both CTAs and, per tile, hands the accumulator to both epilogues
+//   warps 2-5   epilogue of this CTA's 128 rows
+//
+// Every wait on an mbarrier is bounded; when a bound is hit the role records an error code in
+// *err and stops, the other roles run into their own bounds, and both CTAs meet at the final
+// cluster barrier, free their tensor memory and return.
+#include "common.cuh"
+#include "tma_map.cuh"
+
+namespace {
+
+constexpr int BM = 128;        // weight rows of one CTA (half of the pair's UMMA M)
+constexpr int BK = 64;         // k elements of a stage: one 128-byte swizzled row of bf16
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;
+constexpr int EPI_THREADS = 128;
+constexpr int CHUNK = 32;      // tokens that the epilogue transposes at a time
+constexpr uint32_t WAIT_LIMIT = 1u << 22;
+
+constexpr uint64_t HINT_EVICT_FIRST = 0x12F0000000000000ull;
+constexpr uint64_t HINT_EVICT_LAST = 0x14F0000000000000ull;
+
+enum { ERR_TC2_WAIT_FULL = 111, ERR_TC2_WAIT_EMPTY = 112, ERR_TC2_WAIT_ACC_FULL = 113, ERR_TC2_WAIT_ACC_EMPTY = 114 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t mapa(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// arrival on a barrier of any CTA of the cluster (a shared::cluster address)
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    return done != 0;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (mbar_try(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    return false;
+}
+
+// TMA load of a CTA pair: the data lands in this CTA's shared memory, the bytes are counted on a barrier that
+// may belong to the other CTA of the pair (a shared::cluster address).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t cluster_bar, int x, int y,
+                                                 uint64_t hint) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%3, %4}], [%2], %5;"
+        ::"r"(dst), "l"(map), "r"(cluster_bar), "r"(x), "r"(y), "l"(hint) : "memory");
+}
+
+// K-major tile, 128-byte rows, 128-byte swizzle, 8-row groups 1024 bytes apart (what the TMA box writes).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// kind::f16: bf16 x bf16 -> f32, both operands K-major, M = 256 over the pair, N = n.
+__device__ __forceinline__ uint32_t umma_idesc_pair(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+}
+__device__ __forceinline__ void umma_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on the barrier at this shared-memory offset in both CTAs once the MMAs issued so far are complete
+__device__ __forceinline__ void umma_commit_both(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+struct Gemm2Args {
+    const void* bias;      // [rows_out] or null
+    int bias_dtype;
+    bf16* Y;               // [T, ldy]
+    int T, K, ldy;
+    int rows_out;          // N, or the number of gate rows with DUAL
+    int dual_offset;
+    int tok_tiles, n_tiles, n_pairs;
+    int* err;
+};
+
+template <int BN, int STAGES, bool DUAL>
+struct Smem2 {
+    static constexpr int ACCS = DUAL ? 2 : 1;
+    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int B_BYTES = (BN / 2) * BK * 2;             // this CTA's half of the token tile
+    static constexpr int STAGE_BYTES = ACCS * A_BYTES + B_BYTES;
+    static constexpr int STG_OFFSET = STAGES * STAGE_BYTES;
+    static constexpr int STG_BYTES = 2 * CHUNK * BM * 2;          // two transposition buffers [32 tokens][128 rows]
+    static constexpr int BAR_OFFSET = STG_OFFSET + STG_BYTES;
+    static constexpr int N_BARS = 2 * STAGES + 4;
+    static constexpr int TOTAL = BAR_OFFSET + N_BARS * 8 + 16 + 1024;   // + slack to align the base
+    static constexpr int ACC_COLS = ACCS * BN;                    // tensor-memory columns of one accumulator buffer
+    static constexpr int NBUF = 512 / ACC_COLS;                   // buffers in the 512 columns of tensor memory: 2 or 1
+    static_assert(ACC_COLS == 256 || ACC_COLS == 512, "an accumulator buffer is a half or the whole of tensor memory");
+};
+
+template <int BN, int STAGES, bool DUAL>
+__global__ void __launch_bounds__(THREADS)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, Gemm2Args g) {
+    using S = Smem2<BN, STAGES, DUAL>;
+    constexpr int ACCS = S::ACCS, ACC_COLS = S::ACC_COLS, NBUF = S::NBUF;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bar_full = base + S::BAR_OFFSET, bar_empty = bar_full + 8 * STAGES;
+    const uint32_t bar_acc_full = bar_empty + 8 * STAGES, bar_acc_empty = bar_acc_full + 16, tmem_slot = bar_acc_empty + 16;
+    volatile uint32_t* tmem_slot_ptr = (volatile uint32_t*)(gen_base + S::BAR_OFFSET + S::N_BARS * 8);
+    __shared__ int s_abort, s_epi_abort;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1;
+    const int kblocks = (g.K + BK - 1) / BK;
+
+    if (tid == 0) {
+        s_abort = 0;
+        s_epi_abort = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(bar_full + 8 * s, 1);          // the leader's is used: its producer's expect_tx, bytes of both CTAs
+            mbar_init(bar_empty + 8 * s, 1);         // one multicast commit
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(bar_acc_full + 8 * b, 1);      // one multicast commit per tile
+            mbar_init(bar_acc_empty + 8 * b, 8);     // the leader's is used: four epilogue warps of each CTA
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 2) {                                 // the same warp of both CTAs allocates, and frees at the end
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    // both CTAs' barriers and tensor memory stand before either touches the other's
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot_ptr;
+
+    llb_grid_dependency_sync();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // ---- producer: this CTA's weight rows and its half of the tokens, k-block after k-block, tile after tile
+            const uint32_t full0 = mapa(bar_full, 0);
+            int it = 0;
+            for (int t = pair; t < g.n_tiles && !s_abort; t += g.n_pairs) {
+                const int m0 = ((t / g.tok_tiles) * 2 + (int)rank) * BM;
+                const int n0 = (t % g.tok_tiles) * BN + (int)rank * (BN / 2);
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait(bar_empty + 8 * s, (uint32_t)(it / STAGES - 1) & 1u, &s_abort)) {
+                        if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC2_WAIT_EMPTY); }
+                        break;
+                    }
+                    const uint32_t dst = base + s * S::STAGE_BYTES, bar = full0 + 8 * s;
+                    if (leader) mbar_expect_tx(bar_full + 8 * s, 2u * S::STAGE_BYTES);
+                    tma_load_2d_pair(dst, &map_w, bar, kb * BK, m0, HINT_EVICT_FIRST);
+                    if (DUAL) tma_load_2d_pair(dst + S::A_BYTES, &map_w, bar, kb * BK, m0 + g.dual_offset, HINT_EVICT_FIRST);
+                    tma_load_2d_pair(dst + ACCS * S::A_BYTES, &map_x, bar, kb * BK, n0, HINT_EVICT_LAST);
+                }
+            }
+            if (s_abort && leader) {
+                // copies in flight (of both CTAs) must land before the pair gives up its shared memory
+                int first = it > STAGES ? it - STAGES : 0;
+                for (int i = first; i < it; ++i)
+                    for (uint32_t w = 0; w < WAIT_LIMIT && !mbar_try(bar_full + 8 * (i % STAGES), (uint32_t)(i / STAGES) & 1u); ++w) {}
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            // ---- tensor-core issue for both SMs
+            const uint32_t idesc = umma_idesc_pair(BN);
+            int it = 0, ti = 0;
+            for (int t = pair; t < g.n_tiles && !s_abort; t += g.n_pairs, ++ti) {
+                const int buf = ti % NBUF;
+                if (ti >= NBUF && !mbar_wait(bar_acc_empty + 8 * buf, (uint32_t)(ti / NBUF - 1) & 1u, &s_abort)) {
+                    if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC2_WAIT_ACC_EMPTY); }
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t acc = tmem + buf * ACC_COLS;
+                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(bar_full + 8 * s, (uint32_t)(it / STAGES) & 1u, &s_abort)) {
+                        if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC2_WAIT_FULL); }
+                        break;
+                    }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a = base + s * S::STAGE_BYTES, b = a + ACCS * S::A_BYTES;
+                    const uint64_t ad = umma_desc(a), bd = umma_desc(b), ad2 = umma_desc(a + S::A_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+                        const uint64_t step = (uint64_t)(k * UMMA_K * 2 >> 4);      // the start address field counts 16 bytes
+                        umma_pair(acc, ad + step, bd + step, idesc, accumulate);
+                        if (DUAL) umma_pair(acc + BN, ad2 + step, bd + step, idesc, accumulate);
+                    }
+                    umma_commit_both(bar_empty + 8 * s);
+                }
+                if (s_abort) break;
+                umma_commit_both(bar_acc_full + 8 * buf);
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---- epilogue: warp w may read tensor-memory lanes 32 (w mod 4) .. + 31; a thread owns one weight row
+        const int et = tid - 64;                                  // 0..127
+        const int row = (warp & 3) * 32 + lane;
+        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        const uint32_t acc_empty0 = mapa(bar_acc_empty, 0);
+        bf16* stg = reinterpret_cast<bf16*>(gen_base + S::STG_OFFSET);
+        const int sub = et & 15;
+        int ti = 0, chunk_i = 0;
+        for (int t = pair; t < g.n_tiles; t += g.n_pairs, ++ti) {
+            const int buf = ti % NBUF;
+            const int m0 = ((t / g.tok_tiles) * 2 + (int)rank) * BM;
+            const int n0 = (t % g.tok_tiles) * BN;
+            const int m = m0 + row;
+            float bias_v = 0.f;
+            if (g.bias && m < g.rows_out)
+                bias_v = g.bias_dtype == LLB_F32 ? ((const float*)g.bias)[m] : to_f32(((const bf16*)g.bias)[m]);
+            if (!mbar_wait(bar_acc_full + 8 * buf, (uint32_t)(ti / NBUF) & 1u, &s_abort)) {
+                s_epi_abort = 1;
+                if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC2_WAIT_ACC_FULL); }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (s_epi_abort) break;                               // written before the barrier only: the same for all
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t acc = lane_addr + buf * ACC_COLS;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += CHUNK, ++chunk_i) {
+                bf16* sb = stg + (chunk_i & 1) * (CHUNK * BM);
+#pragma unroll
+                for (int h = 0; h < CHUNK; h += 16) {
+                    float v0[16], v1[16];
+                    tmem_ld16(acc + c + h, v0);
+                    if (DUAL) tmem_ld16(acc + BN + c + h, v1);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        float v = v0[j];
+                        if (DUAL) v = v1[j] * __fdividef(v, 1.0f + __expf(-v));   // fast division: the result is rounded to bfloat16
+                        sb[(h + j) * BM + row] = __float2bfloat16_rn(v + bias_v);
+                    }
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                // 16 threads move one token's 128 outputs (256 bytes); 8 tokens per pass.  The other buffer is
+                // written next, and this one only after the next barrier, which every thread passes after its reads.
+                if (m0 + sub * 8 < g.rows_out) {
+#pragma unroll
+                    for (int j = et >> 4; j < CHUNK; j += EPI_THREADS / 16) {
+                        const int n = n0 + c + j;
+                        if (n < g.T)
+                            *reinterpret_cast<uint4*>(g.Y + (size_t)n * g.ldy + m0 + sub * 8) =
+                                *reinterpret_cast<const uint4*>(sb + j * BM + sub * 8);
+                    }
+                }
+            }
+            // this buffer may be overwritten by the tile after the next
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(acc_empty0 + 8 * buf);
+        }
+    }
+
+    // Neither CTA leaves while the other may still signal its barriers, read its shared memory or write its
+    // tensor memory.
+    __syncthreads();
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (warp == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
+}
+
+template <int BN, int STAGES, bool DUAL>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Gemm2Args& g, cudaStream_t stream) {
+    auto k = gemm_tc2_kernel<BN, STAGES, DUAL>;
+    constexpr int smem = Smem2<BN, STAGES, DUAL>::TOTAL;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return -2000 - (int)e;
+        configured = true;
+    }
+    llb_prefer_max_shared((const void*)k);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * g.n_pairs);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (llb_pdl_enabled()) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = 2;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
+    cfg.attrs = attr;
+    cfg.numAttrs = n_attr;
+    cudaLaunchKernelEx(&cfg, k, mw, mx, g);
+    return llb_status();
+}
+
+}  // namespace
+
+// X [T, K] bf16 with row stride ldx; W [N, K] bf16 dense ([2 * dual_offset, K] when dual_offset > 0); Y [T, ldy]
+// bf16; bias [N] or null.  max_pairs: how many CTA pairs may run at once (SMs / 2).  Returns
+// cudaErrorInvalidValue for what this kernel does not take (the caller then uses the one-CTA kernel).
+LLB_API int llb_gemm_tc2(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int T, int N, int K,
+                         int ldx, int ldy, int dual_offset, int max_pairs, int variant, int* err, cudaStream_t stream) {
+    if (T == 0 || N == 0) return 0;
+    const int dual = dual_offset > 0;
+    const int rows_out = dual ? dual_offset : N;
+    if (K <= 0 || K % 8 || ldx % 8 || ldy % 8 || rows_out % 8 || max_pairs < 1 ||
+        (((uintptr_t)X | (uintptr_t)W | (uintptr_t)Y) & 15) || (dual && N != 2 * dual_offset))
+        return (int)cudaErrorInvalidValue;
+    const int bn = dual && variant == 0 ? 128 : 256;
+    Gemm2Args g;
+    g.bias = bias; g.bias_dtype = bias_dtype; g.Y = (bf16*)Y;
+    g.T = T; g.K = K; g.ldy = ldy; g.rows_out = rows_out; g.dual_offset = dual_offset;
+    g.tok_tiles = (T + bn - 1) / bn;
+    const long long tiles = (long long)((rows_out + 2 * BM - 1) / (2 * BM)) * g.tok_tiles;
+    if (tiles > (1 << 30)) return (int)cudaErrorInvalidValue;
+    g.n_tiles = (int)tiles;
+    g.n_pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
+    g.err = err;
+    CUtensorMap mw, mx;
+    int rc = llb_tma::bf16_map_64(W, N, K, K, BM, &mw);
+    if (rc) return rc;
+    rc = llb_tma::bf16_map_64(X, T, K, ldx, bn / 2, &mx);
+    if (rc) return rc;
+    if (dual) return variant == 0 ? launch<128, 5, true>(mw, mx, g, stream) : launch<256, 4, true>(mw, mx, g, stream);
+    return launch<256, 6, false>(mw, mx, g, stream);
+}

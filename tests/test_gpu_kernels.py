@@ -362,6 +362,37 @@ def test_linear_tensor_cores(T, N, K):
     _tc_check(ref, want, K)
 
 
+@pytest.mark.parametrize("T,N,K", [(257, 256, 64), (300, 520, 200), (700, 1000, 776), (1030, 136, 96), (2048, 1536, 1536)])
+def test_linear_on_paired_sms_and_on_single_ones(T, N, K):
+    """More than 256 tokens run on pairs of SMs (csrc/gemm_tc2.cu); a plan sends them to the one-CTA kernel."""
+    from llaisys_b200 import kernels
+    x, w, b = _tc_case(T, N, K, T + N + K, bias=torch.bfloat16)
+    want = plain.linear(x.double().cpu().numpy(), w.double().cpu().numpy(), b.double().cpu().numpy())
+    outs = [kernels.linear(x, w, b, plan=plan) for plan in (None, ("pair",), (256, 1))]
+    for got in outs:
+        _close(got, want, torch.bfloat16, atol=5e-3)
+    assert torch.equal(outs[0], outs[1])
+    wide = torch.zeros((T, K + 16), dtype=torch.bfloat16, device=DEV)
+    wide[:, 8:8 + K] = x
+    _close(kernels.linear(wide[:, 8:8 + K], w, None, plan=("pair",)), plain.linear(x.double().cpu().numpy(), w.double().cpu().numpy()),
+           torch.bfloat16, atol=5e-3)
+    assert kernels.tc_error(DEV) == 0
+
+
+@pytest.mark.parametrize("T,I,K", [(300, 264, 200), (257, 128, 64), (1000, 136, 96), (1500, 1000, 520)])
+@pytest.mark.parametrize("plan", [None, ("pair", 0), ("pair", 1), (256, 1)])
+def test_linear_swiglu_on_paired_sms_and_on_single_ones(T, I, K, plan):
+    from llaisys_b200 import kernels
+    x, w, _ = _tc_case(T, 2 * I, K, T + I)
+    w = (w.float() * 4).to(torch.bfloat16)
+    gu = plain.linear(x.double().cpu().numpy(), w.double().cpu().numpy())
+    want = plain.swiglu(gu[:, :I], gu[:, I:])
+    got = kernels.linear_swiglu(x, w, plan=plan)
+    assert got.shape == (T, I)
+    _close(got, want, torch.bfloat16, atol=5e-3)
+    assert kernels.tc_error(DEV) == 0
+
+
 @pytest.mark.parametrize("bn", [16, 32, 64, 128, 256])
 @pytest.mark.parametrize("splits,cluster", [(1, 0), (2, 0), (5, 0), (2, 1), (4, 1), (8, 1)])
 def test_linear_tensor_cores_every_tile_and_split(bn, splits, cluster):
