@@ -20,7 +20,7 @@
 //               leader CTA's barrier
 //   warp 1      tcgen05.mma issue (one thread of the leader CTA); tcgen05.commit multicast frees the ring
 //               slot in both CTAs and, per tile, hands the accumulator to both epilogues
-//   warps 2-5   epilogue of this CTA's 128 rows
+//   warps 2-9   epilogue of this CTA's 128 rows: two warps per 32 rows, each with half of the columns
 //
 // Every wait on an mbarrier is bounded; when a bound is hit the role records an error code in
 // *err and stops, the other roles run into their own bounds, and both CTAs meet at the final
@@ -33,8 +33,8 @@ namespace {
 constexpr int BM = 128;        // weight rows of one CTA (half of the pair's UMMA M)
 constexpr int BK = 64;         // k elements of a stage: one 128-byte swizzled row of bf16
 constexpr int UMMA_K = 16;
-constexpr int THREADS = 192;
-constexpr int EPI_THREADS = 128;
+constexpr int THREADS = 320;
+constexpr int EPI_THREADS = 256;
 constexpr int CHUNK = 32;      // tokens that the epilogue transposes at a time
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
@@ -112,16 +112,13 @@ __device__ __forceinline__ void umma_commit_both(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                  ::"r"(bar), "h"((uint16_t)3) : "memory");
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
-    uint32_t r[16];
+// One row of 16 accumulator columns; the registers hold the values after the next tcgen05.wait::ld.
+__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t* r) {
     asm volatile(
         "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+        : "r"(taddr) : "memory");
 }
 
 struct Gemm2Args {
@@ -134,6 +131,21 @@ struct Gemm2Args {
     int tok_tiles, n_tiles, n_pairs;
     int* err;
 };
+
+// The loads issued so far have arrived.  The registers pass through the statement so that no use of them is
+// scheduled ahead of it (the compiler sees no other dependence between the load, the wait and the use).
+__device__ __forceinline__ void tmem_wait_ld(uint32_t* r) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+                 :: "memory");
+}
+__device__ __forceinline__ void pin16(uint32_t* r) {
+    asm volatile(""
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+                 :: "memory");
+}
 
 template <int BN, int STAGES, bool DUAL>
 struct Smem2 {
@@ -180,7 +192,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_acc_full + 8 * b, 1);      // one multicast commit per tile
-            mbar_init(bar_acc_empty + 8 * b, 8);     // the leader's is used: four epilogue warps of each CTA
+            mbar_init(bar_acc_empty + 8 * b, 16);    // the leader's is used: eight epilogue warps of each CTA
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -264,8 +276,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         }
         __syncwarp();
     } else {
-        // ---- epilogue: warp w may read tensor-memory lanes 32 (w mod 4) .. + 31; a thread owns one weight row
-        const int et = tid - 64;                                  // 0..127
+        // ---- epilogue: warp w may read tensor-memory lanes 32 (w mod 4) .. + 31; a thread owns one weight row and,
+        // of every 32 columns, the first or the second 16
+        const int et = tid - 64;                                  // 0..255
+        const int h = ((warp - 2) >> 2) * 16;
         const int row = (warp & 3) * 32 + lane;
         const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t acc_empty0 = mapa(bar_acc_empty, 0);
@@ -284,27 +298,37 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 s_epi_abort = 1;
                 if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC2_WAIT_ACC_FULL); }
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, 256;" ::: "memory");
             if (s_epi_abort) break;                               // written before the barrier only: the same for all
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t acc = lane_addr + buf * ACC_COLS;
+            // the next 16 columns are on their way from tensor memory while these are worked on
+            uint32_t nxt0[16], nxt1[16];
+            tmem_ld16_nowait(acc + h, nxt0);
+            if (DUAL) tmem_ld16_nowait(acc + BN + h, nxt1);
 #pragma unroll 1
             for (int c = 0; c < BN; c += CHUNK, ++chunk_i) {
                 bf16* sb = stg + (chunk_i & 1) * (CHUNK * BM);
+                float v0[16], v1[16];
+                tmem_wait_ld(nxt0);
+                if (DUAL) pin16(nxt1);
 #pragma unroll
-                for (int h = 0; h < CHUNK; h += 16) {
-                    float v0[16], v1[16];
-                    tmem_ld16(acc + c + h, v0);
-                    if (DUAL) tmem_ld16(acc + BN + c + h, v1);
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        float v = v0[j];
-                        if (DUAL) v = v1[j] * __fdividef(v, 1.0f + __expf(-v));   // fast division: the result is rounded to bfloat16
-                        sb[(h + j) * BM + row] = __float2bfloat16_rn(v + bias_v);
-                    }
+                for (int j = 0; j < 16; ++j) {
+                    v0[j] = __uint_as_float(nxt0[j]);
+                    if (DUAL) v1[j] = __uint_as_float(nxt1[j]);
                 }
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                // 16 threads move one token's 128 outputs (256 bytes); 8 tokens per pass.  The other buffer is
+                if (c + CHUNK < BN) {
+                    tmem_ld16_nowait(acc + c + CHUNK + h, nxt0);
+                    if (DUAL) tmem_ld16_nowait(acc + BN + c + CHUNK + h, nxt1);
+                }
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    float v = v0[j];
+                    if (DUAL) v = v1[j] * __fdividef(v, 1.0f + __expf(-v));       // fast division: the result is rounded to bfloat16
+                    sb[(h + j) * BM + row] = __float2bfloat16_rn(v + bias_v);
+                }
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                // 16 threads move one token's 128 outputs (256 bytes); 16 tokens per pass.  The other buffer is
                 // written next, and this one only after the next barrier, which every thread passes after its reads.
                 if (m0 + sub * 8 < g.rows_out) {
 #pragma unroll
@@ -373,14 +397,14 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Gemm2Args& g, cud
 // bf16; bias [N] or null.  max_pairs: how many CTA pairs may run at once (SMs / 2).  Returns
 // cudaErrorInvalidValue for what this kernel does not take (the caller then uses the one-CTA kernel).
 LLB_API int llb_gemm_tc2(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int T, int N, int K,
-                         int ldx, int ldy, int dual_offset, int max_pairs, int variant, int* err, cudaStream_t stream) {
+                         int ldx, int ldy, int dual_offset, int max_pairs, int* err, cudaStream_t stream) {
     if (T == 0 || N == 0) return 0;
     const int dual = dual_offset > 0;
     const int rows_out = dual ? dual_offset : N;
     if (K <= 0 || K % 8 || ldx % 8 || ldy % 8 || rows_out % 8 || max_pairs < 1 ||
         (((uintptr_t)X | (uintptr_t)W | (uintptr_t)Y) & 15) || (dual && N != 2 * dual_offset))
         return (int)cudaErrorInvalidValue;
-    const int bn = dual && variant == 0 ? 128 : 256;
+    const int bn = 256;
     Gemm2Args g;
     g.bias = bias; g.bias_dtype = bias_dtype; g.Y = (bf16*)Y;
     g.T = T; g.K = K; g.ldy = ldy; g.rows_out = rows_out; g.dual_offset = dual_offset;
@@ -395,6 +419,5 @@ LLB_API int llb_gemm_tc2(const void* X, const void* W, const void* bias, int bia
     if (rc) return rc;
     rc = llb_tma::bf16_map_64(X, T, K, ldx, bn / 2, &mx);
     if (rc) return rc;
-    if (dual) return variant == 0 ? launch<128, 5, true>(mw, mx, g, stream) : launch<256, 4, true>(mw, mx, g, stream);
-    return launch<256, 6, false>(mw, mx, g, stream);
+    return dual ? launch<256, 4, true>(mw, mx, g, stream) : launch<256, 6, false>(mw, mx, g, stream);
 }

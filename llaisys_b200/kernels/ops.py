@@ -253,16 +253,15 @@ def _pair_ok(out, rows_out) -> bool:
     return out.dtype == torch.bfloat16 and rows_out % 8 == 0 and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0
 
 
-def _gemm_tc_pair(x, weight, bias, out, dual_offset=0, variant=1):
-    """The product on pairs of SMs (csrc/gemm_tc2.cu): persistent, for many tokens, bfloat16 output.
-    variant (gate/up only): 1: tiles of 256 tokens, one accumulator buffer; 0: 128 tokens, two buffers."""
+def _gemm_tc_pair(x, weight, bias, out, dual_offset=0):
+    """The product on pairs of SMs (csrc/gemm_tc2.cu): persistent, for many tokens, bfloat16 output."""
     M, K = x.shape
     N = weight.shape[0]
     err = _tc_resources(x.device)[2]
     f = _fn(load_module("gemm_tc2.cu"), "llb_gemm_tc2",
-            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(f(_ptr(x), _ptr(weight), _ptr(bias), _dt(bias) if bias is not None else 0, _ptr(out), M, N, K,
-             x.stride(0), out.stride(0), dual_offset, _sm_count(x.device) // 2, variant, _ptr(err), _stream()),
+             x.stride(0), out.stride(0), dual_offset, _sm_count(x.device) // 2, _ptr(err), _stream()),
            "linear (tensor cores, paired SMs)")
 
 
@@ -270,9 +269,9 @@ def _gemm_tc(x, weight, bias, out, dual_offset=0, plan=None):
     M, K = x.shape
     N = weight.shape[0]
     if plan is None and M > 256 and _pair_ok(out, dual_offset or N):
-        plan = ("pair", 1)
+        plan = ("pair",)
     if plan is not None and plan[0] == "pair":
-        return _gemm_tc_pair(x, weight, bias, out, dual_offset, plan[1] if len(plan) > 1 else 1)
+        return _gemm_tc_pair(x, weight, bias, out, dual_offset)
     scratch, counters, err = _tc_resources(x.device)
     plan = plan or tc_plan(M, dual_offset or N, K, _sm_count(x.device), bool(dual_offset))
     bn, splits = plan[0], plan[1]
