@@ -18,6 +18,11 @@ A "step" is one decode step.  The run times K decode steps of a batch of 8 seque
              requests) over its time, against the measured copy bandwidth
   points     decode tokens a second at batch 1 and batch 64
 
+`--shape 7b|32b` runs the same measurement at the two larger shapes, and `--workload own` runs
+such a shape's own workload (16 prompts of 256..4096 tokens and 256 decode steps; 64 prompts of
+512..2048 tokens and 128 steps) end to end through the generation loop; the reported metric of
+the default run does not change.
+
 Between timed steps nothing flushes L2: each decode step streams the 3.1 GB of weights, which
 is larger than L2 (126 MB), so no step finds its inputs cached.  Peaks come from
 MEASURED_PEAKS.json beside this file when it exists, else from the fallback figures below.
