@@ -32,10 +32,7 @@
 // common base, adds them up, divides and stores.
 // Every mbarrier wait is bounded; a wait that runs out sets *err and the CTA leaves in order.
 #include "common.cuh"
-
-#include <cuda.h>
-#include <mutex>
-#include <unordered_map>
+#include "tma_map.cuh"
 
 #ifndef LLB_HEAD_DIM
 #error "compile with -DLLB_HEAD_DIM=<64 or 128>"
@@ -591,56 +588,6 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
 }
 
-// ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* q = nullptr;
-        cudaDriverEntryPointQueryResult r;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &q, cudaEnableDefault, &r) == cudaSuccess &&
-            r == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)q;
-    });
-    return fn;
-}
-struct MapKey {
-    const void* ptr; long long rows; int cols, ld, box_rows;
-    bool operator==(const MapKey& o) const { return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows; }
-};
-struct MapKeyHash {
-    size_t operator()(const MapKey& k) const {
-        size_t h = (size_t)k.ptr ^ (size_t)k.rows * 1000003u;
-        for (int v : {k.cols, k.ld, k.box_rows}) h = h * 1000003u ^ (size_t)v;
-        return h;
-    }
-};
-// Row-major bf16 matrix [rows, cols], row stride ld elements; boxes of {64 columns, box_rows rows}, 128-byte swizzle.
-int get_map(const void* ptr, long long rows, int cols, int ld, int box_rows, CUtensorMap* out) {
-    static std::mutex mu;
-    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-    MapKey key{ptr, rows, cols, ld, box_rows};
-    std::lock_guard<std::mutex> lock(mu);
-    auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return 0; }
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return (int)cudaErrorNotSupported;
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {64, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return -1000 - (int)r;
-    if (cache.size() > 4096) cache.clear();
-    cache.emplace(key, *out);
-    return 0;
-}
-
 }  // namespace
 
 // q: the packed projections [T, row_stride] (query heads first, already rotated); kpool / vpool: one call's pages
@@ -655,11 +602,11 @@ LLB_API int llb_attn_tc_prefill(const void* q, int T, int row_stride, const void
     dim3 grid(p.nh, ((max_new + BQ - 1) / BQ) * p.n_split, B);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
     CUtensorMap mq, mk, mv;
-    int rc = get_map(q, T, p.nh * DH, row_stride, BQ, &mq);
+    int rc = llb_tma::bf16_map_64(q, T, p.nh * DH, row_stride, BQ, &mq);
     if (rc) return rc;
-    rc = get_map(kpool, (long long)n_pages * p.nkvh * BKV, DH, DH, BKV, &mk);
+    rc = llb_tma::bf16_map_64(kpool, (long long)n_pages * p.nkvh * BKV, DH, DH, BKV, &mk);
     if (rc) return rc;
-    rc = get_map(vpool, (long long)n_pages * p.nkvh * BKV, DH, DH, BKV, &mv);
+    rc = llb_tma::bf16_map_64(vpool, (long long)n_pages * p.nkvh * BKV, DH, DH, BKV, &mv);
     if (rc) return rc;
     static bool configured = false;
     if (!configured) {

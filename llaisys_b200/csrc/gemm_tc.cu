@@ -32,10 +32,7 @@
 // *err, stops issuing, waits (bounded) for the copies it has in flight, frees its tensor
 // memory and returns.
 #include "common.cuh"
-
-#include <cuda.h>
-#include <mutex>
-#include <unordered_map>
+#include "tma_map.cuh"
 
 namespace {
 
@@ -487,61 +484,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 }
 
 // ------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* p = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-            q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
-    });
-    return fn;
-}
-
-struct MapKey {
-    const void* ptr; int rows, cols, ld, box_rows;
-    bool operator==(const MapKey& o) const {
-        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
-    }
-};
-struct MapKeyHash {
-    size_t operator()(const MapKey& k) const {
-        size_t h = (size_t)k.ptr;
-        for (int v : {k.rows, k.cols, k.ld, k.box_rows}) h = h * 1000003u ^ (size_t)v;
-        return h;
-    }
-};
-
-// A 2-D map over a row-major bf16 matrix [rows, cols] with row stride ld (elements); boxes of
-// {64 columns, box_rows rows}, 128-byte swizzle, zero fill outside.
-int get_map(const void* ptr, int rows, int cols, int ld, int box_rows, CUtensorMap* out) {
-    static std::mutex mu;
-    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-    MapKey key{ptr, rows, cols, ld, box_rows};
-    std::lock_guard<std::mutex> lock(mu);
-    auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return 0; }
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return (int)cudaErrorNotSupported;
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return -1000 - (int)r;          // tensor-map encoding refused: -(1000 + CUresult)
-    if (cache.size() > 4096) cache.clear();
-    cache.emplace(key, *out);
-    return 0;
-}
-
 template <int BN, int STAGES, bool DUAL>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& g, dim3 grid, cudaStream_t stream) {
     auto k = gemm_tc_kernel<BN, STAGES, DUAL>;
@@ -619,9 +561,9 @@ LLB_API int llb_gemm_tc(const void* X, const void* W, const void* bias, int bias
             return (int)cudaErrorInvalidValue;
     }
     CUtensorMap mw, mx;
-    int rc = get_map(W, N, K, K, BM, &mw);
+    int rc = llb_tma::bf16_map_64(W, N, K, K, BM, &mw);
     if (rc) return rc;
-    rc = get_map(X, T, K, ldx, bn, &mx);
+    rc = llb_tma::bf16_map_64(X, T, K, ldx, bn, &mx);
     if (rc) return rc;
     GemmArgs g{bias, bias_dtype, Y, y_dtype, T, N, K, ldy, dual_offset, splits, cluster, scratch, counters, err};
 #define LLB_TC(BN_, ST_, STD_) \
@@ -676,20 +618,6 @@ int noalloc_setup(NoAllocPtrs* out) {
     return 0;
 }
 
-// Like get_map, but encodes into caller storage every time: no cache, no heap.
-int encode_map_uncached(const void* ptr, int rows, int cols, int ld, int box_rows, CUtensorMap* out) {
-    EncodeTiledFn fn = encode_fn();
-    if (!fn) return (int)cudaErrorNotSupported;
-    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-    cuuint32_t elem[2] = {1, 1};
-    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : -1000 - (int)r;
-}
-
 }  // namespace
 
 int llb_gemm_tc_noalloc(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int y_dtype,
@@ -714,9 +642,9 @@ int llb_gemm_tc_noalloc(const void* X, const void* W, const void* bias, int bias
     int rc = noalloc_setup(&ptrs);
     if (rc) return rc;
     CUtensorMap mw, mx;
-    rc = encode_map_uncached(W, N, K, K, BM, &mw);
+    rc = llb_tma::encode_bf16_map_64(W, N, K, K, BM, &mw);
     if (rc) return rc;
-    rc = encode_map_uncached(X, T, K, ldx, bn, &mx);
+    rc = llb_tma::encode_bf16_map_64(X, T, K, ldx, bn, &mx);
     if (rc) return rc;
     GemmArgs g{bias, bias_dtype, Y, y_dtype, T, N, K, ldy, 0, splits, 0, ptrs.scratch, ptrs.counters, ptrs.err};
     switch (bn) {

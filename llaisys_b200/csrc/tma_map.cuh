@@ -44,14 +44,8 @@ struct MapKeyHash {
 // A 2-D map over a row-major bf16 matrix [rows, cols] with row stride ld (elements): boxes of
 // {64 columns, box_rows rows}, 128-byte swizzle, zero fill outside.  The base must be 16-byte
 // aligned and ld a multiple of 8.  Returns 0, cudaErrorNotSupported, or -(1000 + CUresult) when
-// the encoding is refused.
-static inline int bf16_map_64(const void* ptr, long long rows, int cols, int ld, int box_rows, CUtensorMap* out) {
-    static std::mutex mu;
-    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
-    MapKey key{ptr, rows, cols, ld, box_rows};
-    std::lock_guard<std::mutex> lock(mu);
-    auto it = cache.find(key);
-    if (it != cache.end()) { *out = it->second; return 0; }
+// the encoding is refused.  Encodes into the caller's storage: no cache, no heap.
+static inline int encode_bf16_map_64(const void* ptr, long long rows, int cols, int ld, int box_rows, CUtensorMap* out) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return (int)cudaErrorNotSupported;
     cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -61,7 +55,19 @@ static inline int bf16_map_64(const void* ptr, long long rows, int cols, int ld,
     CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return -1000 - (int)r;
+    return r == CUDA_SUCCESS ? 0 : -1000 - (int)r;
+}
+
+// The same through a cache keyed by pointer and shape.
+static inline int bf16_map_64(const void* ptr, long long rows, int cols, int ld, int box_rows, CUtensorMap* out) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    MapKey key{ptr, rows, cols, ld, box_rows};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    int rc = encode_bf16_map_64(ptr, rows, cols, ld, box_rows, out);
+    if (rc) return rc;
     if (cache.size() > 4096) cache.clear();
     cache.emplace(key, *out);
     return 0;
