@@ -141,8 +141,8 @@ def load_module(source: str, defines: dict | None = None) -> ctypes.CDLL:
 # Every module with the definitions that the tests, the benchmark and the command line use.
 DEFAULT_MODULES = [
     ("basic.cu", {}), ("gemm_simt.cu", {}), ("gemm_tc.cu", {}), ("gemm_tc2.cu", {}), ("sampling.cu", {}),
-    *[("attention_simt.cu", {"LLB_HEAD_DIM": d}) for d in (16, 24, 32, 48, 64, 128)],
-    *[("attention_mma.cu", {"LLB_HEAD_DIM": d}) for d in (16, 32, 48, 64, 128)],
+    *[("attention_simt.cu", {"LLB_HEAD_DIM": d}) for d in (16, 20, 24, 32, 48, 64, 80, 128, 160)],
+    *[("attention_mma.cu", {"LLB_HEAD_DIM": d}) for d in (16, 32, 48, 64, 80, 128)],
     *[("attention_tc.cu", {"LLB_HEAD_DIM": d}) for d in (64, 128)],
 ]
 
