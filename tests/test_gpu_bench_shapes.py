@@ -58,3 +58,12 @@ def test_tail_by_one_in_bfloat16(shape):
     engine = build_engine(folder, torch.bfloat16, max_tokens=192)
     compare(run_tail_by_one(engine, requests[:1], tail=8), oracle, requests[:1], torch.bfloat16, SHAPES[name],
             f"{name} tail-by-one")
+
+
+def test_a_prompt_of_some_hundred_tokens_in_bfloat16(shape):
+    """More than 256 tokens in a step: the products run on pairs of SMs, attention over several row blocks."""
+    name, folder, oracle, _ = shape
+    requests = random_requests(SHAPES[name], [600 if name == "1.5b" else 300, 70], seed=31)
+    engine = build_engine(folder, torch.bfloat16, max_tokens=sum(-(-len(r) // 64) * 64 for r in requests))
+    got = run_batches(engine, requests, [[0, 1]], [len(r) - 2 for r in requests])
+    compare(got, oracle, requests, torch.bfloat16, SHAPES[name], f"{name} long prompt")
