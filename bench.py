@@ -161,6 +161,77 @@ def profile_run(args, model, cfg, rng) -> int:
     return 0
 
 
+def timeline_run(args, model, cfg, rng) -> int:
+    """Per-kernel timeline of whole steps as the device ran them (torch.profiler / CUPTI, no ncu): decode steps
+    are replayed from their CUDA graph with programmatic dependent launch, as in serving.  Prints each kernel's
+    total, and one layer's launches with their start offsets and durations; a kernel's own share of the layer
+    is its end minus its predecessor's end (kernels start early and wait)."""
+    import collections
+    import tempfile
+
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    from llaisys_b200.cache import CacheConfig
+    from llaisys_b200.engine import Engine, StepEntry
+    V, B = cfg.vocab_size, max(args.batch, 1)
+    engine = Engine(model, CacheConfig(max_tokens=B * CONTEXT, max_seqs=B))
+    if args.timeline == "prefill":
+        prompt = rng.integers(0, V, size=PREFILL_TOKENS).tolist()
+
+        def once():
+            s = engine.acquire()
+            engine.step([StepEntry(s, prompt, [PREFILL_TOKENS - 1])])
+            engine.release(s)
+    else:
+        slots = [engine.acquire() for _ in range(B)]
+        for s in slots:
+            engine.cache.book.reserve(s, PROMPT_LEN)
+            engine.cache.book.commit(s, PROMPT_LEN)
+        for pool in engine.cache.k_pools + engine.cache.v_pools:
+            pool.normal_(0, 1)
+
+        def once():
+            engine.step([StepEntry(s, [int(rng.integers(0, V))], [0]) for s in slots])
+    for _ in range(4):
+        once()
+    torch.cuda.synchronize()
+    steps = 3
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(steps):
+            once()
+        torch.cuda.synchronize()
+    with tempfile.TemporaryDirectory() as tmp:
+        path = os.path.join(tmp, "trace.json")
+        prof.export_chrome_trace(path)
+        with open(path) as f:
+            events = [e for e in json.load(f)["traceEvents"] if e.get("cat") == "kernel"]
+    engine.check()
+    events.sort(key=lambda e: e["ts"])
+    last = events[-(len(events) // steps):]                  # the last step's kernels
+    totals = collections.defaultdict(lambda: [0, 0.0])
+    busy_end, gaps = last[0]["ts"], 0.0
+    for e in last:
+        name = e["name"].replace("(anonymous namespace)::", "").replace("void ", "")[:64]
+        totals[name][0] += 1
+        totals[name][1] += e["dur"]
+        gaps += max(0.0, e["ts"] - busy_end)
+        busy_end = max(busy_end, e["ts"] + e["dur"])
+    print(f"{args.timeline} step: {len(last)} kernels, span {busy_end - last[0]['ts']:.1f} us, idle gaps {gaps:.1f} us")
+    for name, (n, t) in sorted(totals.items(), key=lambda kv: -kv[1][1]):
+        print(f"{t:9.1f} us  n={n:4d}  avg {t / n:7.2f}  {name}")
+    per_layer = max(1, (len(last) - 3) // max(1, cfg.num_hidden_layers))
+    start = min(len(last) - 1, 1 + per_layer * (cfg.num_hidden_layers // 2))
+    print("one layer from the middle of the step: start offset, duration, end, own share (end - previous end), kernel")
+    t0, prev_end = last[start]["ts"], None
+    for e in last[start:start + per_layer + 1]:
+        end = e["ts"] + e["dur"] - t0
+        own = "" if prev_end is None else f"{end - prev_end:7.2f}"
+        print(f"  +{e['ts'] - t0:7.2f} {e['dur']:7.2f} {end:8.2f} {own:>7}  {e['name'].replace('(anonymous namespace)::', '')[:60]}  grid={e['args'].get('grid')}")
+        prev_end = end
+    return 0
+
+
 def own_workload(args, model, cfg, cfg_dict, layers, full_layers, shape_name, pk, pk_src, rng) -> int:
     """A shape's own workload through the generation loop (host token ids in and out): prompts of unequal
     lengths in one prefill step, then the stated number of decode steps.  Run twice; the second run is timed."""
@@ -237,6 +308,8 @@ def main() -> int:
     ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
                     help="for a profiler: warm up, then run two uncaptured steps of this kind between "
                          "cudaProfilerStart and cudaProfilerStop, print nothing else")
+    ap.add_argument("--timeline", choices=["decode", "prefill"], default=None,
+                    help="print the per-kernel timeline of a step (torch.profiler, no ncu) instead of measuring")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -280,6 +353,8 @@ def main() -> int:
 
     if args.profile:
         return profile_run(args, model, cfg, rng)
+    if args.timeline:
+        return timeline_run(args, model, cfg, rng)
     if args.workload == "own":
         return own_workload(args, model, cfg, cfg_dict, layers, full_layers, shape_name, pk, pk_src, rng)
 
