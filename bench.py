@@ -232,6 +232,62 @@ def timeline_run(args, model, cfg, rng) -> int:
     return 0
 
 
+def products_run(args, cfg) -> int:
+    """The four matrix products of a layer timed alone at --tokens tokens, with every kernel that takes them:
+    the one-CTA tcgen05 kernel and, for more than 256 tokens, the paired-SM kernel (which the library chooses)."""
+    import torch
+
+    from llaisys_b200.kernels import ops
+    dev = torch.device("cuda:0")
+    T, H, I = args.tokens, cfg.hidden_size, cfg.intermediate_size
+    qkv = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
+
+    reps = 20
+
+    def graph_of(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        return g
+
+    def replay_us(g):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / reps * 1e3
+
+    print(f"{SHAPES[args.shape][0]}, {T} tokens: microseconds per launch (TFLOP/s); {reps} launches in a CUDA graph, "
+          "the kernels taking turns five times, median")
+    for name, N, K, dual in (("q/k/v", qkv, H, False), ("output", H, cfg.num_attention_heads * cfg.head_dim, False),
+                             ("gate/up + SwiGLU", 2 * I, H, True), ("down", H, I, False)):
+        x = (torch.randn(T, K, device=dev) * 0.5).to(torch.bfloat16)
+        w = (torch.randn(N, K, device=dev) * 0.05).to(torch.bfloat16)
+        run = (lambda plan: ops.linear_swiglu(x, w, plan=plan)) if dual else (lambda plan: ops.linear(x, w, None, plan=plan))
+        plans = [("one CTA per tile", ops.tc_plan(T, N // 2 if dual else N, K, ops._sm_count(dev), dual))]
+        if T > 256:
+            plans.append(("paired SMs", ("pair",)))
+        graphs = [(label, graph_of(lambda plan=plan: run(plan))) for label, plan in plans]
+        times = {label: [] for label, _ in graphs}
+        for _ in range(5):
+            for label, g in graphs:
+                times[label].append(replay_us(g))
+        cells = []
+        for label, _ in graphs:
+            us = statistics.median(times[label])
+            cells.append(f"{label} {us:.1f} ({2 * T * N * K / us / 1e6:.0f})")
+        print(f"  {name:18s} " + "   ".join(cells))
+    print("error word", ops.tc_error(dev))
+    return 0
+
+
 def own_workload(args, model, cfg, cfg_dict, layers, full_layers, shape_name, pk, pk_src, rng) -> int:
     """A shape's own workload through the generation loop (host token ids in and out): prompts of unequal
     lengths in one prefill step, then the stated number of decode steps.  Run twice; the second run is timed."""
@@ -308,6 +364,9 @@ def main() -> int:
     ap.add_argument("--profile", choices=["decode", "prefill"], default=None,
                     help="for a profiler: warm up, then run two uncaptured steps of this kind between "
                          "cudaProfilerStart and cudaProfilerStop, print nothing else")
+    ap.add_argument("--products", action="store_true",
+                    help="time a layer's four matrix products alone at --tokens tokens, with each kernel that takes them")
+    ap.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="tokens for --products")
     ap.add_argument("--timeline", choices=["decode", "prefill"], default=None,
                     help="print the per-kernel timeline of a step (torch.profiler, no ncu) instead of measuring")
     args = ap.parse_args()
@@ -342,6 +401,8 @@ def main() -> int:
     layers = args.layers or full_layers
     cfg_dict["num_hidden_layers"] = layers
     cfg = config_from_dict(cfg_dict)
+    if args.products:
+        return products_run(args, cfg)
     model = DecoderModel(cfg.to_spec(), BuildEnv(torch.bfloat16, dev))
     load_weights(model, RandomSource(model.expected_tensors(), seed=0, dtype=torch.bfloat16, device=dev))
     pk, pk_src = peaks()
