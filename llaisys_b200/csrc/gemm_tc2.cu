@@ -12,9 +12,11 @@
 // tile in shared memory, the tensor cores of both SMs read both halves, and each CTA's tensor
 // memory receives its 128 rows x BN tokens.  An SM thus fills a third (a quarter with DUAL) less
 // shared memory per FLOP than it would alone.  The pair is persistent: it walks over tiles
-// pair, pair + pairs, ...; the accumulator is double-buffered in tensor memory (2 x 256 columns),
-// so the epilogue of a tile (tcgen05.ld, bias or SwiGLU, transposition through shared memory,
-// 16-byte stores) runs while the tensor cores work on the next one.
+// pair, pair + pairs, ....  With one accumulator (256 tokens = 256 columns) tensor memory holds
+// two buffers, so the epilogue of a tile (tcgen05.ld, bias, transposition through shared memory,
+// 16-byte stores) runs while the tensor cores work on the next one; the two accumulators of DUAL
+// (2 x 256 columns) fill tensor memory, and the next tile's products wait for the epilogue
+// (measured faster than 128-token tiles with two buffers, whose products are slower per FLOP).
 //
 //   warp 0      TMA producer (one thread): ring of STAGES k-blocks, both CTAs, completion counted on the
 //               leader CTA's barrier
