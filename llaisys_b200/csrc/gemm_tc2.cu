@@ -210,17 +210,35 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot_ptr;
 
-    llb_grid_dependency_sync();
+    // The weight does not depend on any earlier kernel of the step: the first tile's first STAGES k-blocks of it are
+    // requested before the grid dependency resolves, while the predecessor is still running.
+    const int prefetched = min(STAGES, kblocks);
+    if (warp == 0 && lane == 0) {
+        const uint32_t full0 = mapa(bar_full, 0);
+        const int m0 = ((pair / g.tok_tiles) * 2 + (int)rank) * BM;
+        for (int i = 0; i < prefetched; ++i) {
+            const uint32_t dst = base + i * S::STAGE_BYTES, bar = full0 + 8 * i;
+            if (leader) mbar_expect_tx(bar_full + 8 * i, 2u * S::STAGE_BYTES);
+            tma_load_2d_pair(dst, &map_w, bar, i * BK, m0, HINT_EVICT_FIRST);
+            if (DUAL) tma_load_2d_pair(dst + S::A_BYTES, &map_w, bar, i * BK, m0 + g.dual_offset, HINT_EVICT_FIRST);
+        }
+    }
+    llb_grid_dependency_sync();      // from here on memory written by earlier kernels is touched
 
     if (warp == 0) {
         if (lane == 0) {
             // ---- producer: this CTA's weight rows and its half of the tokens, k-block after k-block, tile after tile
             const uint32_t full0 = mapa(bar_full, 0);
-            int it = 0;
+            {   // the activations of the k-blocks whose weight is on its way already
+                const int n0 = (pair % g.tok_tiles) * BN + (int)rank * (BN / 2);
+                for (int i = 0; i < prefetched; ++i)
+                    tma_load_2d_pair(base + i * S::STAGE_BYTES + ACCS * S::A_BYTES, &map_x, full0 + 8 * i, i * BK, n0, HINT_EVICT_LAST);
+            }
+            int it = prefetched;
             for (int t = pair; t < g.n_tiles && !s_abort; t += g.n_pairs) {
                 const int m0 = ((t / g.tok_tiles) * 2 + (int)rank) * BM;
                 const int n0 = (t % g.tok_tiles) * BN + (int)rank * (BN / 2);
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                for (int kb = (t == pair ? prefetched : 0); kb < kblocks; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !mbar_wait(bar_empty + 8 * s, (uint32_t)(it / STAGES - 1) & 1u, &s_abort)) {
                         if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC2_WAIT_EMPTY); }
