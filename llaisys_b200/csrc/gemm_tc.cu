@@ -16,7 +16,7 @@
 //
 // With `splits` > 1 the K range is divided over gridDim.z CTAs, and their float32 partial tiles
 // are added in split order (so the sum does not depend on arrival order) in one of two ways:
-//   * cluster (splits 2, 4 or 8, tiles up to 128 tokens): the CTAs of a tile form a thread-block
+//   * cluster (splits 2, 4, 8 or 16, tiles up to 128 tokens): the CTAs of a tile form a thread-block
 //     cluster; each leaves its partial tile in its own shared memory, and after a cluster
 //     barrier each adds one slice of the rows of all partials through distributed shared
 //     memory, applies the bias and stores.  No global memory round trip.
@@ -492,6 +492,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& g, dim3
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return -2000 - (int)e;       // shared-memory opt-in refused: -(2000 + cudaError)
+        cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);      // clusters of sixteen
         configured = true;
     }
     llb_prefer_max_shared((const void*)k);
@@ -532,7 +533,7 @@ static long long llb_gemm_tc_scratch_elems(int T, int N, int bn, int splits, int
 // X [T, K] bf16 with row stride ldx; W [N, K] bf16 dense ([2 * dual_offset, K] when dual_offset > 0,
 // giving Y [T, dual_offset]); bias bf16/f32 or null; Y bf16 or f32 with row stride ldy.
 // bn: tokens per tile (16, 32, 64, 128, 256).  cluster: reduce the splits through a thread-block cluster where
-// that applies (splits 2, 4 or 8 and bn <= 128), else through `scratch`.  Requirements: K and ldx multiples of 8, X and W 16-byte
+// that applies (splits 2, 4, 8 or 16 and bn <= 128), else through `scratch`.  Requirements: K and ldx multiples of 8, X and W 16-byte
 // aligned.  Returns 0, a cudaError, or cudaErrorInvalidValue for a shape it does not take.
 LLB_API int llb_gemm_tc(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int y_dtype,
                         int T, int N, int K, int ldx, int ldy, int bn, int splits, int cluster, int dual_offset,
@@ -553,7 +554,7 @@ LLB_API int llb_gemm_tc(const void* X, const void* W, const void* bias, int bias
     }
     dim3 grid((rows_out + BM - 1) / BM, (T + bn - 1) / bn, splits);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
-    if (cluster && !(splits == 2 || splits == 4 || splits == 8) ) cluster = 0;
+    if (cluster && !(splits == 2 || splits == 4 || splits == 8 || splits == 16)) cluster = 0;
     if (cluster && bn > 128) cluster = 0;
     if (splits > 1 && !cluster) {
         long long need = llb_gemm_tc_scratch_elems(T, rows_out, bn, splits, dual);

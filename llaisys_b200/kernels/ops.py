@@ -219,7 +219,7 @@ def tc_plan(T: int, rows_out: int, K: int, sms: int, dual: bool = False):
     """(tokens per tile, K splits) of a tensor-core launch.
 
     The tile is the smallest that holds the tokens.  When the weight has fewer row blocks than
-    the device can run CTAs (decode), K is split 2, 4 or 8 ways over a thread-block cluster that
+    the device can run CTAs (decode), K is split 2, 4, 8 or 16 ways over a thread-block cluster that
     reduces through shared memory.  The split minimises a cost fitted to measurements on a B200
     (microseconds): k-blocks per CTA times 0.0155 per KB of a pipeline stage, plus, when split,
     1.2 + 0.0015 * tile tokens * accumulators * splits for the cluster reduction; the CTAs must
@@ -235,8 +235,10 @@ def tc_plan(T: int, rows_out: int, K: int, sms: int, dual: bool = False):
     capacity = (sms * 2 * 280) // 296 if two_per_sm else (sms * 112) // 148
     best, best_cost = 1, kblocks * stage_kb * 0.0155
     if bn <= 128:
-        for s in (2, 4, 8):
-            if s > kblocks // 2 or tiles * s > capacity:
+        # sixteen (a cluster of non-portable size) only for 64-token tiles: measured in the whole step, +2.7 % at
+        # batch 64, but -1 % at batch 8 and 32, although the product alone is faster there too
+        for s in (2, 4, 8, 16):
+            if s > kblocks // 2 or tiles * s > capacity or (s == 16 and bn != 64):
                 break
             cost = -(-kblocks // s) * stage_kb * 0.0155 + 1.2 + 0.0015 * bn * accs * s
             if cost < best_cost:

@@ -410,6 +410,17 @@ def test_linear_tensor_cores_every_tile_and_split(bn, splits, cluster):
     assert kernels.tc_error(DEV) == 0
 
 
+@pytest.mark.parametrize("bn,T", [(16, 9), (64, 50), (128, 70)])
+def test_linear_tensor_cores_sixteen_splits_in_one_cluster(bn, T):
+    from llaisys_b200 import kernels
+    N, K = 300, 4096                            # 64 k-blocks: four for each of sixteen CTAs
+    x, w, b = _tc_case(T, N, K, bn + T, bias=torch.float32)
+    want = plain.linear(x.double().cpu().numpy(), w.double().cpu().numpy(), b.double().cpu().numpy())
+    for _ in range(2):
+        _tc_check(kernels.linear(x, w, b, out_dtype=torch.float32, plan=(bn, 16, 1)), want, K)
+    assert kernels.tc_error(DEV) == 0
+
+
 @pytest.mark.parametrize("T,I,K,plan", [(8, 8960, 1536, None), (3, 200, 72, None), (70, 136, 96, None), (300, 264, 200, None),
                                         (20, 300, 712, (32, 3)), (20, 300, 712, (256, 2)), (130, 300, 712, (128, 4)),
                                         (130, 300, 712, (128, 4, 0)), (9, 300, 1096, (16, 8)), (40, 136, 520, (64, 2))])
