@@ -240,6 +240,8 @@ def tc_plan(T: int, rows_out: int, K: int, sms: int, dual: bool = False):
         for s in (2, 4, 8, 16):
             if s > kblocks // 2 or tiles * s > capacity or (s == 16 and bn != 64):
                 break
+            if (s - 1) * -(-kblocks // s) >= kblocks:      # a CTA of the cluster would be left without a k-block
+                continue
             cost = -(-kblocks // s) * stage_kb * 0.0155 + 1.2 + 0.0015 * bn * accs * s
             if cost < best_cost:
                 best, best_cost = s, cost
