@@ -235,10 +235,11 @@ def tc_plan(T: int, rows_out: int, K: int, sms: int, dual: bool = False):
     capacity = (sms * 2 * 280) // 296 if two_per_sm else (sms * 112) // 148
     best, best_cost = 1, kblocks * stage_kb * 0.0155
     if bn <= 128:
-        # sixteen (a cluster of non-portable size) only for 64-token tiles: measured in the whole step, +2.7 % at
-        # batch 64, but -1 % at batch 8 and 32, although the product alone is faster there too
+        # sixteen (a cluster of non-portable size) for 64-token tiles and for up to four tokens: measured in the
+        # whole step, +2.7 % at batch 64, +1.5 % at batch 1 and 2, +4 % at batch 4, nothing at batch 6, but -1 % at
+        # batch 8 and 32, although the product alone is faster there too
         for s in (2, 4, 8, 16):
-            if s > kblocks // 2 or tiles * s > capacity or (s == 16 and bn != 64):
+            if s > kblocks // 2 or tiles * s > capacity or (s == 16 and bn != 64 and T > 4):
                 break
             if (s - 1) * -(-kblocks // s) >= kblocks:      # a CTA of the cluster would be left without a k-block
                 continue

@@ -63,4 +63,4 @@ def test_launch_plans_are_launchable(T, rows, K, dual):
         tiles = math.ceil(rows / 128) * math.ceil(T / bn)
         assert tiles * splits <= 2 * 148                             # all resident at once, at most two per SM
     if splits == 16:
-        assert bn == 64
+        assert bn == 64 or T <= 4
