@@ -275,6 +275,10 @@ def products_run(args, cfg) -> int:
         if T > 256:
             plans.append(("paired SMs", ("pair",)))
         graphs = [(label, graph_of(lambda plan=plan: run(plan))) for label, plan in plans]
+        # for scale only: the library's product of the same operands (cuBLAS through torch.matmul; for gate/up
+        # without the SwiGLU, writing [T, 2I])
+        wt = w.t()
+        graphs.append(("cuBLAS, for scale", graph_of(lambda: torch.matmul(x, wt))))
         times = {label: [] for label, _ in graphs}
         for _ in range(5):
             for label, g in graphs:
