@@ -1,12 +1,13 @@
 """Device storage of the cache and the per-step views the mixers get.
 
-Storage is paged: a page holds `PAGE` consecutive tokens of one sequence, for every call of its
+Storage is paged: a page holds `PAGE` consecutive tokens of one sequence, for every user of its
 group, laid out [page, kv head, token, dim] so that one head's keys of a page are contiguous.
-Calls (entries of the model's run order) whose mixers need the same head count, head size and
-ring length form a group and share one page numbering; a group that keeps every key and a
-group that keeps a window have pools and page tables of their own.
+A user is one mixer of one entry of the model's run order.  Users that need the same head
+count, key width, value width and ring length form a group and share one page numbering; a group
+that keeps every key and a group that keeps a window have pools and page tables of their own,
+and a window group's pool holds no more pages than its rings can use.
 
-Beside the pages each slot owns a fixed-size float32 state row per call that asks for one
+Beside the pages each slot owns a fixed-size float32 state row per user that asks for one
 (`Mixer.state_size()`), zeroed when the slot is acquired.
 """
 from __future__ import annotations
@@ -17,10 +18,11 @@ from typing import Dict, List, Optional
 import numpy as np
 import torch
 
+from ..csrc.build import page_tokens
 from ..parts.base import KVNeed
 from .slots import CacheError, CacheFull, SlotBook
 
-PAGE = 64
+PAGE = page_tokens()      # LLB_PAGE of csrc/common.cuh: also the attention kernels' key tile
 
 
 @dataclass(frozen=True)
@@ -42,8 +44,8 @@ def ring_pages(window: Optional[int]) -> Optional[int]:
 @dataclass
 class KVView:
     """What a mixer sees of the cache in one step: its call's pools and the batch's page table."""
-    k: torch.Tensor                 # [pages, kv heads, PAGE, dim]
-    v: torch.Tensor
+    k: torch.Tensor                 # [pages, kv heads, PAGE, key_dim]
+    v: Optional[torch.Tensor]       # [pages, kv heads, PAGE, value_dim]; None when the mixer keeps no values
     page_table: torch.Tensor        # int32 [n_seqs, width]
     ring: int
     writable: bool
@@ -52,8 +54,8 @@ class KVView:
 class PagedCache:
     def __init__(self, needs: List[Optional[KVNeed]], cache_of: List[Optional[int]], state_sizes: List[int],
                  config: CacheConfig, dtype: torch.dtype, device, allocate: bool = True):
-        """needs[c], state_sizes[c]: what call c's mixer asks for; cache_of[c]: an earlier call
-        whose keys and values call c reads instead of keeping its own."""
+        """needs[u], state_sizes[u]: what user u (a mixer of the run order) asks for; cache_of[u]:
+        an earlier user whose keys and values user u reads instead of keeping its own."""
         self.config, self.dtype, self.device = config, dtype, torch.device(device)
         n_pages = max(1, -(-config.max_tokens // PAGE))
         self.n_pages = n_pages
@@ -72,7 +74,8 @@ class PagedCache:
                 if needs[owner].window is not None:
                     raise CacheError(f"call {c} reads the cache of call {owner}, which keeps a window only; "
                                      f"a shared cache has to keep every key")
-                if need is not None and (need.num_kv_heads, need.head_dim) != (needs[owner].num_kv_heads, needs[owner].head_dim):
+                if need is not None and (need.num_kv_heads, need.key_dim, need.value_dim) != (
+                        needs[owner].num_kv_heads, needs[owner].key_dim, needs[owner].value_dim):
                     raise CacheError(f"call {c} reads the cache of call {owner} but their head shapes differ")
                 self.call_group.append(self.call_group[owner])
                 self.call_entry.append(self.call_entry[owner])
@@ -83,7 +86,7 @@ class PagedCache:
                 self.call_group.append(None)
                 self.call_entry.append(None)
                 continue
-            key = (need.num_kv_heads, need.head_dim, ring_pages(need.window))
+            key = (need.num_kv_heads, need.key_dim, need.value_dim, ring_pages(need.window))
             if key not in self.group_keys:
                 self.group_keys.append(key)
                 entries_per_group.append(0)
@@ -91,18 +94,20 @@ class PagedCache:
             self.call_group.append(g)
             self.call_entry.append(entries_per_group[g])
             entries_per_group[g] += 1
-        self.rings = [k[2] for k in self.group_keys]
-        self.book = SlotBook(self.n_slots, [n_pages] * len(self.group_keys), self.rings, PAGE)
+        self.rings = [k[3] for k in self.group_keys]
+        # a sequence never holds more pages of a window group than its ring has
+        self.group_pages = [n_pages if r is None else min(n_pages, r * self.n_slots) for r in self.rings]
+        self.book = SlotBook(self.n_slots, self.group_pages, self.rings, PAGE)
         # ---- storage
         self.k_pools: List[torch.Tensor] = []
         self.v_pools: List[torch.Tensor] = []
         self.state: Dict[int, torch.Tensor] = {}
         self.state_sizes = list(state_sizes)
         if allocate:
-            for (nkvh, dh, _), n_entries in zip(self.group_keys, entries_per_group):
-                shape = (n_entries, n_pages, nkvh, PAGE, dh)
-                self.k_pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
-                self.v_pools.append(torch.zeros(shape, dtype=dtype, device=self.device))
+            for (nkvh, dk, dv, _), n_entries, pages in zip(self.group_keys, entries_per_group, self.group_pages):
+                self.k_pools.append(torch.zeros((n_entries, pages, nkvh, PAGE, dk), dtype=dtype, device=self.device))
+                self.v_pools.append(torch.zeros((n_entries, pages, nkvh, PAGE, dv), dtype=dtype, device=self.device)
+                                    if dv > 0 else None)
             for c, n in enumerate(state_sizes):
                 if n > 0:
                     self.state[c] = torch.zeros((self.n_slots, n), dtype=torch.float32, device=self.device)
@@ -126,7 +131,7 @@ class PagedCache:
 
     def bytes_per_token(self) -> int:
         es = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * p.shape[0] * p.shape[2] * p.shape[4] * es for p in self.k_pools)
+        return sum(p.shape[0] * p.shape[2] * p.shape[4] * es for p in self.k_pools + self.v_pools if p is not None)
 
     # ---- per-step tables
     def table_width(self, group: int, slots: List[int]) -> int:
@@ -152,7 +157,8 @@ class PagedCache:
             raise CacheError(f"call {call} keeps no keys and values")
         table = tables[g]
         e = self.call_entry[call]
-        return KVView(self.k_pools[g][e], self.v_pools[g][e], table, self.ring_of(g, table.shape[1]),
+        v = self.v_pools[g]
+        return KVView(self.k_pools[g][e], v[e] if v is not None else None, table, self.ring_of(g, table.shape[1]),
                       writable=self.call_owner[call] is None)
 
 

@@ -135,8 +135,8 @@ class Qwen2Config:
             ffn = PartSpec("swiglu_mlp", {"hidden_size": H, "intermediate_size": self.intermediate_size},
                            prefix=f"{p}.mlp")
             norm = {"size": H, "eps": self.rms_norm_eps}
-            layers.append(LayerSpec(
-                block="pre_norm_residual", mixer=mixer, ffn=ffn,
+            layers.append(LayerSpec.pair(
+                "pre_norm_residual", mixer=mixer, ffn=ffn,
                 mixer_norm=PartSpec("rms_norm", norm, prefix=f"{p}.input_layernorm"),
                 ffn_norm=PartSpec("rms_norm", norm, prefix=f"{p}.post_attention_layernorm")))
         return ModelSpec(

@@ -23,20 +23,36 @@ class PartSpec:
 
 
 @dataclass(frozen=True)
+class SubLayerSpec:
+    """One step of a layer: a part of category `category` ("mixer" or "ffn") behind an optional norm."""
+    category: str
+    part: PartSpec
+    norm: Optional[PartSpec] = None
+
+
+@dataclass(frozen=True)
 class LayerSpec:
-    """A layer is an arrangement (`block`) of a mixer and a feed-forward, each behind a norm."""
+    """A layer is an arrangement (`block`) of sub-layers around the residual stream: as many as
+    the architecture has (mixer then feed-forward here; a mixer alone, or a mixer and two
+    feed-forwards, are other layers of the same kind)."""
     block: str
-    mixer: PartSpec
-    mixer_norm: PartSpec
-    ffn: PartSpec
-    ffn_norm: PartSpec
+    sublayers: Tuple[SubLayerSpec, ...]
+
+    @classmethod
+    def pair(cls, block: str, mixer: PartSpec, mixer_norm: PartSpec, ffn: PartSpec, ffn_norm: PartSpec) -> "LayerSpec":
+        """The usual layer: norm, mixer, norm, feed-forward."""
+        return cls(block, (SubLayerSpec("mixer", mixer, mixer_norm), SubLayerSpec("ffn", ffn, ffn_norm)))
+
+    def mixers(self) -> Tuple[PartSpec, ...]:
+        return tuple(s.part for s in self.sublayers if s.category == "mixer")
 
 
 @dataclass(frozen=True)
 class CallSpec:
     """One entry of the run order.  `layer` indexes `ModelSpec.layers` and may repeat.
-    `cache_of` names an earlier entry of the order whose cache this call reads instead of
-    keeping one of its own (it then appends nothing)."""
+    `cache_of` names an earlier entry of the order whose cache this call's mixers read instead of
+    keeping one of their own (they then append nothing); the mixers of the two entries pair up in
+    sub-layer order."""
     layer: int
     cache_of: Optional[int] = None
 

@@ -34,6 +34,16 @@ class BuildError(RuntimeError):
     pass
 
 
+def page_tokens() -> int:
+    """Tokens of a cache page: the one constant LLB_PAGE of common.cuh, read from the source so that
+    the host side and the kernels cannot disagree."""
+    import re
+    m = re.search(r"constexpr\s+int\s+LLB_PAGE\s*=\s*(\d+)\s*;", (SRC_DIR / "common.cuh").read_text())
+    if not m:
+        raise BuildError("common.cuh does not define LLB_PAGE")
+    return int(m.group(1))
+
+
 def find_nvcc() -> str:
     for cand in (os.environ.get("LLAISYS_NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
         if cand and Path(cand).exists():
@@ -140,7 +150,7 @@ def load_module(source: str, defines: dict | None = None) -> ctypes.CDLL:
 
 # Every module with the definitions that the tests, the benchmark and the command line use.
 DEFAULT_MODULES = [
-    ("basic.cu", {}), ("gemm_simt.cu", {}), ("gemm_tc.cu", {}), ("gemm_tc2.cu", {}), ("sampling.cu", {}),
+    ("basic.cu", {}), ("gemm_simt.cu", {}), ("gemm_tc.cu", {}), ("gemm_tc2.cu", {}), ("sampling.cu", {}), ("random_init.cu", {}),
     *[("attention_simt.cu", {"LLB_HEAD_DIM": d}) for d in (16, 20, 24, 32, 48, 64, 80, 128, 160)],
     *[("attention_mma.cu", {"LLB_HEAD_DIM": d}) for d in (16, 32, 48, 64, 80, 128)],
     *[("attention_tc.cu", {"LLB_HEAD_DIM": d}) for d in (64, 128)],

@@ -93,25 +93,3 @@ class StepContext:
     def state(self, call: int) -> torch.Tensor:
         """float32 [n_slots, state_size] of this call; row seq_slot[b] belongs to sequence b."""
         return self.cache.state[call]
-
-    def decode_splits(self, n_kv_heads: int, clusters16: int = 0) -> int:
-        """Slices of the key range in decode attention: enough blocks to fill the device, at
-        most one slice per page the widest page table of the step can hold (a function of the
-        step's shape alone, so a captured step stays valid as sequences grow).  clusters16: how
-        many clusters of sixteen blocks of the kernel the device holds at once (0: none)."""
-        pages = max(self.widths) if self.widths else 1
-        # two blocks fit an SM; more blocks than that would run as a second, mostly empty wave
-        want = (2 * self.sm_count) // max(1, self.n_seqs * n_kv_heads)
-        splits = max(1, min(want, pages, 64))
-        # Sixteen slices in one (non-portable) cluster for small batches: a block then walks three pages at most
-        # at contexts up to 3,000 tokens, all of them requested before the step's earlier kernels have finished.
-        # Only while the blocks leave every second place on the SMs free: at batch 8 (two blocks on every SM)
-        # the step was measured 1.3 % slower than with eight slices, at batch 1 it is 2.3 % faster.
-        n_clusters = self.n_seqs * n_kv_heads
-        if splits >= 16 and pages > 16 and n_clusters <= clusters16 and n_clusters * 16 <= self.sm_count:
-            return 16
-        # up to eight slices merge inside a thread-block cluster, which is cheaper than a second kernel:
-        # prefer that while a block then still has at most sixteen pages to walk
-        if splits > 8 and pages <= 8 * 16:
-            splits = 8
-        return splits

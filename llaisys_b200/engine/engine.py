@@ -61,7 +61,13 @@ class Engine:
         self.sm_count = torch.cuda.get_device_properties(self.env.device).multi_processor_count
         self.err = torch.zeros(1, dtype=torch.int32, device=self.env.device)
         self.use_graphs = use_graphs and model.capturable()
-        model.prepare(min(self.spec.max_positions, self.cache.n_pages * self.page))
+        # The longest sequence a slot can reach: the model's limit, and the cache's room unless every
+        # group keeps a window only (rings never run out of pages).  Parts size their tables for it once;
+        # a captured step has their addresses, so they must not move afterwards.
+        self.position_limit = self.spec.max_positions
+        if any(r is None for r in self.cache.rings):
+            self.position_limit = min(self.position_limit, self.cache.n_pages * self.page)
+        model.prepare(self.position_limit)
         # the last sampled token of every slot, for steps that take their tokens from the device (see feed())
         self.fed_tokens = torch.zeros(self.cache.n_slots, dtype=torch.int32, device=self.env.device)
         self._last_ctx = None
@@ -163,28 +169,38 @@ class Engine:
                                 f"{self.spec.max_positions}")
         # reserve pages for all sequences or for none
         before = {s: [list(p) for p in book.seqs[s].pages] for s in slots}
-        try:
-            for s, n in zip(slots, n_new):
-                book.reserve(s, n)
-        except CacheError:
+
+        def give_back():
             for s in slots:
                 for g, old in enumerate(before[s]):
                     for p in book.seqs[s].pages[g][len(old):]:
                         book.pools[g].give_back(p)
                     book.seqs[s].pages[g] = old
+
+        try:
+            for s, n in zip(slots, n_new):
+                book.reserve(s, n)
+        except CacheError:
+            give_back()
             raise
         with torch.cuda.device(self.env.device):
             graphed = self.use_graphs and max(n_new) == 1
             shape = StepContext.shape_of(self.cache, slots, n_new, out_rows, bucket=graphed)
-            if graphed:
-                logits = self._graphed_step(shape, slots, n_new, tokens, out_rows, fed)
-            else:
-                ctx = StepContext(self.cache, self.env.device, *shape, self.err, self.sm_count)
-                buf, ev = self._staging(ctx.meta.numel())
-                ctx.load(slots, n_new, tokens, out_rows, buf)
-                ev.record()
-                logits = self._forward(ctx, fed)
-                self._last_ctx = ctx
+            try:
+                if graphed:
+                    logits = self._graphed_step(shape, slots, n_new, tokens, out_rows, fed)
+                else:
+                    ctx = StepContext(self.cache, self.env.device, *shape, self.err, self.sm_count)
+                    buf, ev = self._staging(ctx.meta.numel())
+                    ctx.load(slots, n_new, tokens, out_rows, buf)
+                    ev.record()
+                    logits = self._forward(ctx, fed)
+                    self._last_ctx = ctx
+            except Exception:
+                # a launch was refused (or a kernel could not be built): lengths stay as they were and the pages
+                # reserved for this step go back, so the sequences can be stepped again or released
+                give_back()
+                raise
             for s, n in zip(slots, n_new):
                 book.commit(s, n)
             self.steps_run += 1
@@ -206,10 +222,17 @@ class Engine:
         if entry[1] is None:
             logits = self._forward(ctx, fed)          # the real step, uncaptured; this also loads every kernel
             from ..kernels import ops
-            graph = torch.cuda.CUDAGraph()
             n0 = ops.launch_count()
-            with torch.cuda.graph(graph):
-                captured = self._forward(ctx, fed)    # recorded, not run
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    captured = self._forward(ctx, fed)    # recorded, not run
+            except Exception:
+                # The step itself has run; only its recording failed.  This shape goes on uncaptured.
+                ops._launches = n0
+                self._graphs.pop(shape, None)
+                self.use_graphs = False
+                return logits
             entry[1], entry[2] = graph, captured
             entry.append(ops.launch_count() - n0)     # kernels a replay launches
             ops._launches = n0                        # the capture itself launched nothing
@@ -224,13 +247,23 @@ class Engine:
         """Waits for the device and raises if a kernel flagged an error since the last check."""
         from ..kernels import tc_error
         code = int(self.err.item())
-        tc = tc_error(self.env.device)
+        if code:
+            self.err.zero_()
+        tc = tc_error(self.env.device)            # read and cleared
         if tc:
             raise StepError(f"a tensor-core kernel gave up a bounded wait (code {tc}); its output is not valid")
         if code:
-            self.err.zero_()
             what = {1: "a token id outside the embedding table", 2: "a position outside the rotary table"}
             raise StepError(f"device-side check failed: {what.get(code, code)}")
+
+
+def resolve_device(device) -> torch.device:
+    """`device` with its index filled in ("cuda" -> the current CUDA device), so that everything keyed by
+    device (kernel resources, error words) sees one spelling."""
+    device = torch.device(device)
+    if device.type == "cuda" and device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    return device
 
 
 def build_engine(spec: ModelSpec, dtype: torch.dtype, device, cache_config: CacheConfig, source,
@@ -238,7 +271,8 @@ def build_engine(spec: ModelSpec, dtype: torch.dtype, device, cache_config: Cach
     """Builds the model of `spec`, binds its weights from `source` (see weights.loader) and
     wraps it with a cache."""
     from ..weights.loader import load_weights
-    device = torch.device(device)
+    _require_cuda(torch.device(device))
+    device = resolve_device(device)
     model = DecoderModel(spec, BuildEnv(dtype=dtype, device=device))
     load_weights(model, source)
     return Engine(model, cache_config, use_graphs=use_graphs)

@@ -6,7 +6,7 @@ from typing import Dict, List, Optional
 import torch
 
 from ..config.spec import ModelSpec
-from ..parts.base import BuildEnv, KVNeed, Part, TensorDecl, build_part, part_class
+from ..parts.base import BuildEnv, KVNeed, Part, SubLayer, TensorDecl, build_part, part_class
 
 
 class DecoderModel:
@@ -15,26 +15,55 @@ class DecoderModel:
         self.embedding = build_part("embedding", spec.embedding, env)
         self.blocks = []
         for ls in spec.layers:
-            mixer = build_part("mixer", ls.mixer, env)
-            ffn = build_part("ffn", ls.ffn, env)
-            n1, n2 = build_part("norm", ls.mixer_norm, env), build_part("norm", ls.ffn_norm, env)
-            self.blocks.append(part_class("block", ls.block)(mixer, n1, ffn, n2, env))
+            subs = []
+            for sub in ls.sublayers:
+                if sub.category not in ("mixer", "ffn"):
+                    raise ValueError(f"a sub-layer is a 'mixer' or an 'ffn', not {sub.category!r}")
+                norm = build_part("norm", sub.norm, env) if sub.norm is not None else None
+                subs.append(SubLayer(sub.category, build_part(sub.category, sub.part, env), norm))
+            self.blocks.append(part_class("block", ls.block)(subs, env))
+        # Every mixer of every entry of the run order is a user of the cache with an index of its own.
+        self.users: List[tuple] = []                 # user -> (order entry, layer, sub-layer index)
+        self.call_users: List[tuple] = []            # order entry -> its users, in sub-layer order
         for c, call in enumerate(spec.order):
             if not (0 <= call.layer < len(self.blocks)):
                 raise ValueError(f"run order entry {c} names layer {call.layer}, which does not exist")
+            mine = []
+            for i, sub in enumerate(self.blocks[call.layer].sublayers):
+                if sub.category == "mixer":
+                    mine.append(len(self.users))
+                    self.users.append((c, call.layer, i))
+            self.call_users.append(tuple(mine))
         self.final_norm = build_part("norm", spec.final_norm, env)
         self.head = build_part("head", spec.head, env)
         self._loaded = False
 
-    # ---- what the cache has to provide, per call of the run order
+    def _mixer(self, user: int):
+        _, layer, i = self.users[user]
+        return self.blocks[layer].sublayers[i].part
+
+    # ---- what the cache has to provide, per user (a mixer of an entry of the run order)
     def kv_needs(self) -> List[Optional[KVNeed]]:
-        return [self.blocks[c.layer].mixer.kv_need() for c in self.spec.order]
+        return [self._mixer(u).kv_need() for u in range(len(self.users))]
 
     def cache_of(self) -> List[Optional[int]]:
-        return [c.cache_of for c in self.spec.order]
+        out: List[Optional[int]] = []
+        for u, (c, _, _) in enumerate(self.users):
+            owner = self.spec.order[c].cache_of
+            if owner is None:
+                out.append(None)
+                continue
+            if not (0 <= owner < c):
+                raise ValueError(f"run order entry {c} reads the cache of entry {owner}, which does not come before it")
+            k = self.call_users[c].index(u)
+            theirs = self.call_users[owner]
+            if k >= len(theirs):
+                raise ValueError(f"run order entry {c} reads the cache of entry {owner}, which has fewer mixers")
+            out.append(theirs[k])
+        return out
 
     def state_sizes(self) -> List[int]:
-        return [self.blocks[c.layer].mixer.state_size() for c in self.spec.order]
+        return [self._mixer(u).state_size() for u in range(len(self.users))]
 
     def capturable(self) -> bool:
         """True when every part's forward only enqueues device work (no host read-back), so that
@@ -50,7 +79,8 @@ class DecoderModel:
     def parts(self) -> List[Part]:
         ps: List[Part] = [self.embedding]
         for b in self.blocks:
-            ps += [b.mixer_norm, b.mixer, b.ffn_norm, b.ffn]
+            for sub in b.sublayers:
+                ps += ([sub.norm] if sub.norm is not None else []) + [sub.part]
         return ps + [self.final_norm, self.head]
 
     def expected_tensors(self) -> Dict[str, TensorDecl]:
@@ -94,7 +124,7 @@ class DecoderModel:
         residual = self.embedding.forward(ctx)
         pending = None
         for c, call in enumerate(self.spec.order):
-            residual, pending = self.blocks[call.layer].forward(residual, pending, ctx, c)
+            residual, pending = self.blocks[call.layer].forward(residual, pending, ctx, self.call_users[c])
         if ctx.out_rows.numel() == 0:
             return None
         h = self.final_norm.forward(residual, pending, rows=ctx.out_rows)

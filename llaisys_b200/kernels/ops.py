@@ -7,9 +7,9 @@ from typing import Optional
 
 import torch
 
-from ..csrc.build import load_module
+from ..csrc.build import load_module, page_tokens
 
-PAGE = 64                      # tokens of a cache page (LLB_PAGE in csrc/common.cuh)
+PAGE = page_tokens()           # tokens of a cache page (LLB_PAGE in csrc/common.cuh)
 DT = {torch.float32: 0, torch.bfloat16: 1}
 
 
@@ -175,6 +175,17 @@ def rope_append(qkv: torch.Tensor, nh: int, nkvh: int, dh: int, *, cos=None, sin
              _ptr(pt), pt.shape[1] if do_app else 0, a.get("ring", 1), _ptr(err), _stream()), "rope_append")
 
 
+def fill_normal(out: torch.Tensor, key: int, mean: float, std: float, first: int = 0):
+    """out (contiguous, float32 or bfloat16) <- mean + std * z(key, first + i): the counter-based
+    normal numbers of csrc/random_init.cu, whose host twin is weights/rng.py."""
+    _need_cuda(out)
+    assert out.is_contiguous()
+    f = _fn(load_module("random_init.cu"), "llb_fill_normal",
+            [c_void_p, c_int, c_longlong, c_longlong, c_ulonglong, c_double, c_double, c_void_p])
+    with torch.cuda.device(out.device):
+        _check(f(_ptr(out), _dt(out), out.numel(), first, key & 0xFFFFFFFFFFFFFFFF, mean, std, _stream()), "fill_normal")
+
+
 # ------------------------------------------------------------------ matrix products
 _TC_SCRATCH_ELEMS = 16 * 1024 * 1024        # float32 partial tiles of split-K launches (64 MB)
 _TC_COUNTERS = 1 << 16
@@ -186,6 +197,7 @@ def _tc_resources(device):
     """Per device: the scratch of split-K partial tiles, the tile counters (zero between
     launches) and the error word of the tensor-core kernels.  Allocated once, so launches inside
     a CUDA graph capture allocate nothing."""
+    device = _dev_key(device)
     r = _tc_res.get(device)
     if r is None:
         r = (torch.empty(_TC_SCRATCH_ELEMS, dtype=torch.float32, device=device),
@@ -195,10 +207,24 @@ def _tc_resources(device):
     return r
 
 
-def tc_error(device) -> int:
-    """Error word of the tensor-core kernels on `device` (0: none; 101-103: a bounded wait ran out)."""
-    r = _tc_res.get(torch.device(device))
-    return int(r[2].item()) if r else 0
+def _dev_key(device) -> torch.device:
+    device = torch.device(device)
+    if device.type == "cuda" and device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    return device
+
+
+def tc_error(device, clear: bool = True) -> int:
+    """Error word of the tensor-core kernels on `device` (0: none; 101-104, 111-114, 121-122: a bounded
+    wait ran out).  Reading it waits for the device; a code that was found is cleared, so that it is
+    reported once."""
+    r = _tc_res.get(_dev_key(device))
+    if not r:
+        return 0
+    code = int(r[2].item())
+    if code and clear:
+        r[2].zero_()
+    return code
 
 
 _sm_counts = {}
@@ -389,13 +415,20 @@ def prefill_tc_ok(dtype: torch.dtype, dh: int) -> bool:
     return TC_ATTENTION and dtype == torch.bfloat16 and dh in (64, 128)
 
 
+def require_head_dim(dh: int) -> None:
+    """Raises unless some attention kernel of this package takes heads of `dh` elements: the CUDA-core
+    kernel (both precisions) takes any even size up to 256; the tensor-core kernels take multiples of
+    16 up to 128 (mma.sync) and 64 or 128 (tcgen05) and are chosen where they apply."""
+    if dh <= 0 or dh % 2 or dh > 256:
+        raise KernelError(f"attention: head size {dh} is not supported (even, at most 256)")
+
+
 def _mma_lib(dh: int):
     return load_module("attention_mma.cu", {"LLB_HEAD_DIM": dh})
 
 
 def _attn_lib(dh: int):
-    if dh % 2 or dh > 256:
-        raise KernelError(f"attention: head size {dh} is not supported (even, at most 256)")
+    require_head_dim(dh)
     return load_module("attention_simt.cu", {"LLB_HEAD_DIM": dh})
 
 

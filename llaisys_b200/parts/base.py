@@ -6,7 +6,8 @@ A model is put together from parts of five categories:
   ffn       position-wise feed-forward (dense here; a routed one would register the same way)
   norm      normalisation of one activation row
   position  position encoding applied by a mixer to its queries and keys
-  block     the arrangement of a mixer, a feed-forward and their norms around the residual stream
+  block     the arrangement of a layer's sub-layers (a mixer or a feed-forward, each behind its
+            norm) around the residual stream
 
 plus the token embedding and the output head.  Every part is built from a `PartSpec` (its sizes
 and constants) and a `BuildEnv` (activation dtype, device); it declares the tensors it wants by
@@ -65,17 +66,25 @@ class BuildEnv:
 @dataclass(frozen=True)
 class TensorDecl:
     """A tensor a part wants from the weights file.  kind: "float" or "int".  init: how the
-    random-weights mode fills it ("normal": N(0, 0.02); "one_plus_normal": 1 + N(0, 0.02))."""
+    random-weights mode fills it ("normal": N(0, 0.02); "one_plus_normal": 1 + N(0, 0.02)).
+    use: "matrix" for an operand of a matrix product or a table of rows (kept in the model's
+    dtype, whatever the file stores, so that it can feed the tensor cores), "vector" for what
+    enters 32-bit arithmetic only (a norm's weight, a bias: under a bfloat16 model such a tensor
+    stays float32 if the file stores it in 32 bits)."""
     shape: Tuple[int, ...]
     kind: str = "float"
     init: str = "normal"
+    use: str = "matrix"
 
 
 @dataclass(frozen=True)
 class KVNeed:
-    """Keys and values a mixer keeps per token: `window` None keeps all, else the last `window`."""
+    """What a mixer keeps per token: `num_kv_heads` rows of `key_dim` elements in the key pool and
+    of `value_dim` elements in the value pool (value_dim 0: no value pool, e.g. one latent row
+    per token).  `window` None keeps every token, else the last `window`."""
     num_kv_heads: int
-    head_dim: int
+    key_dim: int
+    value_dim: int
     window: Optional[int] = None
 
 
@@ -107,11 +116,20 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    def apply(self, qkv: torch.Tensor, num_heads: int, num_kv_heads: int, ctx, append=None) -> None:
+    """Encodes positions into the query and key heads.  It never touches the cache: storing keys
+    and values is the mixer's business."""
+
+    def apply(self, qkv: torch.Tensor, num_heads: int, num_kv_heads: int, ctx) -> None:
         """Encodes the positions ctx.tok_pos into the query and key heads of the packed
-        projections, in place; `append` (see kernels.rope_append) asks it to also store keys
-        and values in the cache, which saves a pass over them."""
+        projections [T, (num_heads + 2 num_kv_heads) head_dim], in place."""
         raise NotImplementedError
+
+    def rotation_tables(self, positions: int) -> Optional[Tuple[torch.Tensor, torch.Tensor]]:
+        """An encoding that is a rotation of the pairs (j, j + head_dim / 2) by angles that depend
+        on position and j alone may hand out its float32 tables (cos, sin), each
+        [rows >= positions, head_dim / 2]: a mixer's kernels can then rotate on the fly (and store
+        the rotated key in the same pass) instead of calling apply().  None: apply() is the only way."""
+        return None
 
 
 class Mixer(Part):
@@ -125,8 +143,9 @@ class Mixer(Part):
 
     def forward(self, x: torch.Tensor, ctx, call: int) -> torch.Tensor:
         """x: normalised activations [T, H] of the step's packed tokens.  Returns what is to be
-        added to the residual stream: [T, H] or [parts, T, H].  `ctx.kv(call)` is this call's
-        cache view, `ctx.state(call)` its state rows [n_slots, state_size]."""
+        added to the residual stream: [T, H] or [parts, T, H].  `call` is this mixer's index
+        among the mixers of the run order: `ctx.kv(call)` is its cache view, `ctx.state(call)`
+        its state rows [n_slots, state_size]."""
         raise NotImplementedError
 
 
@@ -135,14 +154,23 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
-class Block(Part):
-    """Arrangement of one layer.  Built with the layer's parts instead of a PartSpec."""
+@dataclass
+class SubLayer:
+    """A built sub-layer: the part, its category ("mixer" or "ffn") and the norm before it (or None)."""
+    category: str
+    part: Part
+    norm: Optional[Norm]
 
-    def __init__(self, mixer: Mixer, mixer_norm: Norm, ffn: FeedForward, ffn_norm: Norm, env: BuildEnv):
-        self.mixer, self.mixer_norm, self.ffn, self.ffn_norm, self.env = mixer, mixer_norm, ffn, ffn_norm, env
+
+class Block(Part):
+    """Arrangement of one layer.  Built with the layer's sub-layers instead of a PartSpec."""
+
+    def __init__(self, sublayers, env: BuildEnv):
+        self.sublayers, self.env = list(sublayers), env
         self.spec = None
 
-    def forward(self, residual: torch.Tensor, pending: Optional[torch.Tensor], ctx, call: int):
-        """residual: float32 [T, H]; pending: a delta not yet added to it (or None).
+    def forward(self, residual: torch.Tensor, pending: Optional[torch.Tensor], ctx, users):
+        """residual: float32 [T, H]; pending: a delta not yet added to it (or None); users: for
+        each mixer of the layer, in sub-layer order, its index for ctx.kv() / ctx.state().
         Returns (residual, pending) for the next block."""
         raise NotImplementedError

@@ -5,14 +5,25 @@ from .base import Block, register_part
 
 @register_part("block", "pre_norm_residual")
 class PreNormResidual(Block):
-    """x -> norm -> mixer -> +x -> norm -> feed-forward -> +   (xsmccc/llaisys
+    """x -> norm -> part -> + for every sub-layer in turn; with a mixer and a feed-forward that is
+    x -> norm -> mixer -> +x -> norm -> feed-forward -> +   (xsmccc/llaisys
     src/models/qwen2/layer.hpp:47-84).  Each residual add is done by the norm that follows it,
-    so the block hands its last delta on to the next block (or to the final norm)."""
+    so the block hands its last delta on to the next block (or to the final norm).  A sub-layer
+    without a norm of its own gets the residual stream as it is (the pending delta added)."""
     capturable = True
 
-
-    def forward(self, residual, pending, ctx, call):
-        h = self.mixer_norm.forward(residual, pending)
-        d = self.mixer.forward(h, ctx, call)
-        h = self.ffn_norm.forward(residual, d)
-        return residual, self.ffn.forward(h, ctx)
+    def forward(self, residual, pending, ctx, users):
+        from .. import kernels
+        mixers = iter(users)
+        for sub in self.sublayers:
+            if sub.norm is not None:
+                h = sub.norm.forward(residual, pending)
+            else:
+                if pending is not None:
+                    kernels.residual_add(residual, pending)
+                h = residual.to(self.env.dtype)
+            if sub.category == "mixer":
+                pending = sub.part.forward(h, ctx, next(mixers))
+            else:
+                pending = sub.part.forward(h, ctx)
+        return residual, pending

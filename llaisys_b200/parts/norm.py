@@ -18,7 +18,7 @@ class RMSNorm(Norm):
         self.weight = None
 
     def tensors(self):
-        return {"weight": TensorDecl((self.size,), init="one_plus_normal")}
+        return {"weight": TensorDecl((self.size,), init="one_plus_normal", use="vector")}
 
     def load(self, tensors):
         self.weight = tensors["weight"].contiguous()

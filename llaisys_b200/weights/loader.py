@@ -6,13 +6,16 @@ does not know (python/llaisys/models/qwen2.py:99-210).  Here the model's parts d
 tensors they want; the file must hold exactly those, with those shapes, or loading stops with
 one error that lists everything that is missing, unexpected or mis-shaped.
 
-Kept dtypes: under a float32 model every floating tensor becomes float32.  Under a bfloat16
-model a tensor stored in 16 bits is kept as bfloat16 and a tensor stored in 32 (or 64) bits
-stays float32 (the kernels take either); integer tensors are kept as int32.
+Kept dtypes.  xsmccc/llaisys converts every tensor to the one dtype of its model
+(python/llaisys/models/qwen2.py:118-119, 141).  Here: under a float32 model every floating
+tensor becomes float32.  Under a bfloat16 model the operands of matrix products and the
+embedding table (declared use="matrix") become bfloat16 whatever the file stores, so that a
+checkpoint stored in 32 bits runs on the tensor cores like any other; tensors that only enter
+32-bit arithmetic (use="vector": norm weights, biases) are kept as bfloat16 when stored in 16
+bits and stay float32 when stored in 32 (or 64) bits.  Integer tensors are kept as int32.
 """
 from __future__ import annotations
 
-import hashlib
 from pathlib import Path
 from typing import Dict, Tuple
 
@@ -71,9 +74,11 @@ class FolderSource:
 
 class RandomSource:
     """Seeded random tensors for a model's declarations: matrices, embeddings and biases
-    N(0, 0.02), norm weights 1 + N(0, 0.02), drawn in float32 and rounded to `dtype`.  Every
-    tensor has a generator of its own, keyed by (seed, name), so its values do not depend on
-    which other tensors exist."""
+    N(0, 0.02), norm weights 1 + N(0, 0.02), drawn in float32 and rounded to `dtype`.  The
+    generator is counter-based (weights/rng.py): element i of a tensor is a function of (seed,
+    tensor name, i) alone, so a tensor does not depend on which other tensors exist, and a
+    source on the CPU and a source on a CUDA device (filled there by a kernel, which is what a
+    65 GB model needs) hold the same values."""
 
     def __init__(self, decls, seed: int, dtype: torch.dtype = torch.bfloat16, device="cpu", std: float = 0.02):
         self.decls, self.seed, self.dtype, self.device, self.std = dict(decls), int(seed), dtype, torch.device(device), std
@@ -86,22 +91,31 @@ class RandomSource:
         return {n: (NAMES[self.dtype] if d.kind == "float" else "I32", tuple(d.shape)) for n, d in self.decls.items()}
 
     def get(self, name: str) -> torch.Tensor:
+        from .rng import normal, tensor_key
         d = self.decls[name]
-        key = int.from_bytes(hashlib.sha256(f"{self.seed}:{name}".encode()).digest()[:8], "little") >> 1
-        gen = torch.Generator(device=self.device).manual_seed(key)
         if d.kind == "int":
             return torch.zeros(d.shape, dtype=torch.int32, device=self.device)
-        x = torch.randn(d.shape, generator=gen, dtype=torch.float32, device=self.device) * self.std
-        if d.init == "one_plus_normal":
-            x += 1.0
+        key = tensor_key(self.seed, name)
+        mean = 1.0 if d.init == "one_plus_normal" else 0.0
+        n = 1
+        for s in d.shape:
+            n *= s
+        if self.device.type == "cuda":
+            from .. import kernels
+            out = torch.empty(d.shape, dtype=self.dtype, device=self.device)
+            kernels.fill_normal(out, key, mean, self.std)
+            return out
+        x = torch.from_numpy(normal(key, n, 0, mean, self.std)).view(d.shape)
         return x.to(self.dtype)
 
 
-def kept_dtype(stored: str, compute: torch.dtype) -> torch.dtype:
+def kept_dtype(stored: str, compute: torch.dtype, use: str = "matrix") -> torch.dtype:
     if stored in _INT:
         return torch.int32
     if compute == torch.float32:
         return torch.float32
+    if use == "matrix":
+        return compute
     return torch.bfloat16 if stored in ("F16", "BF16") else torch.float32
 
 
@@ -131,7 +145,7 @@ def load_weights(model, source) -> None:
     have = source.entries()
     env = model.env
     tensors = {}
-    for name in model.expected_tensors():
+    for name, decl in model.expected_tensors().items():
         t = source.get(name)
-        tensors[name] = t.to(device=env.device, dtype=kept_dtype(have[name][0], env.dtype))
+        tensors[name] = t.to(device=env.device, dtype=kept_dtype(have[name][0], env.dtype, decl.use))
     model.bind(tensors)

@@ -11,7 +11,7 @@ from ..config.registry import config_from_dict
 from ..engine.model import DecoderModel
 from ..parts.base import BuildEnv
 from .loader import RandomSource
-from .safetensors_io import write_safetensors
+from .safetensors_io import Deferred, write_safetensors
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "bf16": torch.bfloat16, "f32": torch.float32}
 
@@ -27,6 +27,8 @@ def write_random_model(folder, config: dict, seed: int, dtype="bfloat16") -> Pat
     out = dict(config)
     out["torch_dtype"] = "bfloat16" if store == torch.bfloat16 else "float32"
     (folder / "config.json").write_text(json.dumps(out, indent=1))
-    write_safetensors(folder / "model.safetensors", ((n, src.get(n)) for n in sorted(src.decls)),
+    kept = {n: (store if d.kind == "float" else torch.int32) for n, d in src.decls.items()}
+    write_safetensors(folder / "model.safetensors",
+                      [(n, Deferred(kept[n], src.decls[n].shape, lambda n=n: src.get(n))) for n in sorted(src.decls)],
                       metadata={"format": "pt", "seed": seed})
     return folder

@@ -75,18 +75,34 @@ class SafetensorsFile:
         self._fh.close()
 
 
-def write_safetensors(path, tensors: Iterable[Tuple[str, torch.Tensor]], metadata: dict | None = None):
-    """Writes (name, tensor) pairs in the given order.  Tensors are taken one at a time, so an
-    iterator that makes them lazily keeps memory at one tensor."""
+class Deferred:
+    """A tensor that is made only when its bytes are written: dtype and shape are known
+    beforehand (the header needs them), `make()` returns the tensor."""
+
+    def __init__(self, dtype: torch.dtype, shape, make):
+        self.dtype, self.shape, self.make = dtype, tuple(shape), make
+
+    def numel(self) -> int:
+        n = 1
+        for s in self.shape:
+            n *= s
+        return n
+
+
+def write_safetensors(path, tensors, metadata: dict | None = None):
+    """Writes (name, tensor) pairs (a dict, or a sequence of pairs) in the given order.  A value may
+    be a `Deferred`: it is made when its turn comes and dropped once written, so a file larger than
+    the host's memory can be written one tensor at a time (the header, which comes first in the
+    file, is laid out from the declared dtypes and shapes)."""
     path = Path(path)
-    items = list(tensors) if not isinstance(tensors, dict) else list(tensors.items())
+    items = list(tensors.items()) if isinstance(tensors, dict) else list(tensors)
     header, off = {}, 0
     if metadata:
         header["__metadata__"] = {str(k): str(v) for k, v in metadata.items()}
     for name, t in items:
         if t.dtype not in NAMES:
             raise SafetensorsError(f"tensor {name!r}: dtype {t.dtype} cannot be stored")
-        n = t.numel() * t.element_size()
+        n = t.numel() * t.dtype.itemsize
         header[name] = {"dtype": NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [off, off + n]}
         off += n
     raw = json.dumps(header, separators=(",", ":")).encode("utf-8")
@@ -94,6 +110,17 @@ def write_safetensors(path, tensors: Iterable[Tuple[str, torch.Tensor]], metadat
     with open(path, "wb") as f:
         f.write(struct.pack("<Q", len(raw)))
         f.write(raw)
-        for _, t in items:
+        for i in range(len(items)):
+            name, t = items[i]
+            items[i] = None                       # nothing keeps the tensor once it is written
+            if isinstance(t, Deferred):
+                made = t.make()
+                if made.dtype != t.dtype or tuple(made.shape) != t.shape:
+                    raise SafetensorsError(f"tensor {name!r} was declared {t.dtype} {list(t.shape)} but made "
+                                           f"{made.dtype} {list(made.shape)}")
+                t = made
+                del made
             c = t.detach().to("cpu").contiguous()
-            f.write(c.view(torch.uint8).numpy().tobytes() if c.numel() else b"")
+            if c.numel():
+                f.write(c.view(torch.uint8).numpy().data)
+            del c, t

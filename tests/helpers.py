@@ -162,6 +162,60 @@ def run_batches(engine, requests, batches, prompt_lens):
     return got
 
 
+def run_chunked(engine, requests, cuts):
+    """Each request alone, its tokens fed in several multi-token steps: `cuts` lists the portion
+    lengths tried in turn (the last one is repeated until the request is used up), so a portion
+    meets history in the slot and, on a window layer, a ring that has already wrapped."""
+    from llaisys_b200.engine import StepEntry
+    got = {}
+    for r, toks in enumerate(requests):
+        slot = engine.acquire()
+        at, i = 0, 0
+        while at < len(toks):
+            n = min(cuts[min(i, len(cuts) - 1)], len(toks) - at)
+            out = engine.step([StepEntry(slot, toks[at:at + n], list(range(n)))]).cpu().numpy()
+            for p in range(n):
+                got[(r, at + p)] = out[p]
+            at, i = at + n, i + 1
+        engine.check()
+        engine.release(slot)
+    return got
+
+
+def run_mixed(engine, requests, plans):
+    """All requests live together; plans[r] lists the portion lengths request r brings step by
+    step (0: it sits this step out).  In one step some requests bring a single token onto
+    history, others a fresh prompt, others a further portion.  A request whose plan is used up
+    ends and frees its slot while the others go on."""
+    from llaisys_b200.engine import StepEntry
+    got = {}
+    slot = {r: engine.acquire() for r in range(len(requests))}
+    fed = {r: 0 for r in slot}
+    step = 0
+    while slot:
+        entries, who = [], []
+        for r in sorted(slot):
+            plan = plans[r]
+            n = plan[step] if step < len(plan) else 1
+            n = min(n, len(requests[r]) - fed[r])
+            if n > 0:
+                entries.append(StepEntry(slot[r], requests[r][fed[r]:fed[r] + n], list(range(n))))
+                who.append((r, n))
+        if entries:
+            out = engine.step(entries).cpu().numpy()
+            row = 0
+            for r, n in who:
+                for p in range(n):
+                    got[(r, fed[r] + p)] = out[row]
+                    row += 1
+                fed[r] += n
+        for r in [r for r in slot if fed[r] >= len(requests[r])]:
+            engine.release(slot.pop(r))
+        step += 1
+    engine.check()
+    return got
+
+
 def compare(got, oracle: Oracle, requests, dtype, config, what=""):
     """Asserts every logits row against the plain implementation; reports the first wrong place."""
     worst, worst_at = 0.0, None

@@ -92,17 +92,40 @@ def _cache(needs, cache_of=None, state=None, max_tokens=640, **kw):
 
 
 def test_groups_have_storage_of_their_own():
-    full, win = KVNeed(2, 16, None), KVNeed(2, 16, 8)
-    c = _cache([full, win, win, full, KVNeed(1, 32, None), None], state=[0, 0, 0, 0, 0, 12])
-    assert c.group_keys == [(2, 16, None), (2, 16, 2), (1, 32, None)]
+    full, win = KVNeed(2, 16, 16, None), KVNeed(2, 16, 16, 8)
+    c = _cache([full, win, win, full, KVNeed(1, 32, 32, None), None], state=[0, 0, 0, 0, 0, 12])
+    assert c.group_keys == [(2, 16, 16, None), (2, 16, 16, 2), (1, 32, 32, None)]
     assert c.call_group == [0, 1, 1, 0, 2, None] and c.call_entry == [0, 0, 1, 1, 0, None]
     assert c.k_pools[0].shape == (2, 10, 2, 64, 16) and c.k_pools[2].shape == (1, 10, 1, 64, 32)
     assert c.state[5].shape == (10, 12)
     assert c.bytes_per_token() == 2 * 4 * (2 * 2 * 16 + 2 * 2 * 16 + 1 * 32)
 
 
+def test_keys_and_values_of_different_widths_and_a_mixer_without_values():
+    c = _cache([KVNeed(2, 24, 8, None), KVNeed(1, 40, 0, None), KVNeed(2, 24, 8, None)])
+    assert c.group_keys == [(2, 24, 8, None), (1, 40, 0, None)] and c.call_entry == [0, 0, 1]
+    assert c.k_pools[0].shape == (2, 10, 2, 64, 24) and c.v_pools[0].shape == (2, 10, 2, 64, 8)
+    assert c.k_pools[1].shape == (1, 10, 1, 64, 40) and c.v_pools[1] is None
+    assert c.bytes_per_token() == 4 * (2 * 2 * (24 + 8) + 40)
+    s = c.acquire()
+    c.book.reserve(s, 3); c.book.commit(s, 3)
+    tables = {g: torch.from_numpy(c.page_table(g, [s])) for g in range(2)}
+    v0, v1 = c.view(0, tables), c.view(1, tables)
+    assert v0.k.shape == (10, 2, 64, 24) and v0.v.shape == (10, 2, 64, 8) and v1.v is None and v1.writable
+
+
+def test_a_window_group_holds_no_more_pages_than_its_rings_use():
+    c = _cache([KVNeed(1, 8, 8, None), KVNeed(1, 8, 8, 70)], max_tokens=64 * 40, max_seqs=4)
+    assert c.rings == [None, 3] and c.group_pages == [40, 12]
+    assert c.k_pools[0].shape[1] == 40 and c.k_pools[1].shape[1] == 12
+    slots = [c.acquire() for _ in range(4)]
+    for s in slots:                                  # every slot can fill its ring, whatever the others hold
+        c.book.reserve(s, 600); c.book.commit(s, 600)
+    assert c.book.pools[1].available == 0 and all(len(c.book.pages(s, 1)) == 3 for s in slots)
+
+
 def test_shared_cache_and_state_reset():
-    need = KVNeed(2, 16, None)
+    need = KVNeed(2, 16, 16, None)
     c = _cache([need, need, None], cache_of=[None, 0, None], state=[0, 0, 4], max_seqs=3)
     assert c.call_group == [0, 0, None] and c.call_entry == [0, 0, None] and c.call_owner == [None, 0, None]
     assert c.k_pools[0].shape[0] == 1 and c.n_slots == 3
@@ -113,11 +136,11 @@ def test_shared_cache_and_state_reset():
     with pytest.raises(CacheError):
         _cache([need, need], cache_of=[1, None])
     with pytest.raises(CacheError):
-        _cache([need, KVNeed(1, 16, None)], cache_of=[None, 0])
+        _cache([need, KVNeed(1, 16, 16, None)], cache_of=[None, 0])
 
 
 def test_page_tables():
-    c = _cache([KVNeed(1, 8, None), KVNeed(1, 8, 8)], max_tokens=64 * 8)
+    c = _cache([KVNeed(1, 8, 8, None), KVNeed(1, 8, 8, 8)], max_tokens=64 * 8)
     a, b = c.acquire(), c.acquire()
     for s, n in ((a, 200), (b, 3)):
         c.book.reserve(s, n); c.book.commit(s, n)

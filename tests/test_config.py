@@ -32,12 +32,15 @@ def test_window_layers():
 def test_spec_chooses_parts_layer_by_layer():
     spec = config_from_dict(TINY_B).to_spec()
     assert len(spec.layers) == 3 and [c.layer for c in spec.order] == [0, 1, 2]
-    assert [l.mixer.params["window"] for l in spec.layers] == [None, 8, 8]
-    m = spec.layers[1].mixer
+    assert [[sub.category for sub in l.sublayers] for l in spec.layers] == [["mixer", "ffn"]] * 3
+    assert [l.mixers()[0].params["window"] for l in spec.layers] == [None, 8, 8]
+    m = spec.layers[1].sublayers[0].part
+    assert spec.layers[1].sublayers[0].norm.prefix == "model.layers.1.input_layernorm"
     assert m.kind == "gqa_attention" and m.prefix == "model.layers.1.self_attn"
     assert m.params["position"].kind == "rope_half_split" and m.params["position"].params["theta"] == 1e6
     assert abs(m.params["scale"] - 24 ** -0.5) < 1e-12
-    assert spec.layers[0].ffn.kind == "swiglu_mlp" and spec.layers[0].ffn.params["intermediate_size"] == 232
+    ffn = spec.layers[0].sublayers[1].part
+    assert ffn.kind == "swiglu_mlp" and ffn.params["intermediate_size"] == 232
     assert spec.final_norm.params["eps"] == 1e-5 and spec.head.params["tied_to"] is None
     assert config_from_dict(TINY_A).to_spec().head.params["tied_to"] == "model.embed_tokens.weight"
     assert spec.stop_token_ids == (383, 382)

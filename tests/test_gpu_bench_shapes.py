@@ -7,7 +7,8 @@ model within seconds; every size of a layer is the shape's own."""
 import pytest
 import torch
 
-from helpers import Oracle, build_engine, compare, make_folder, random_requests, run_batches, run_tail_by_one
+from helpers import (Oracle, build_engine, compare, make_folder, random_requests, run_batches, run_chunked, run_mixed,
+                     run_tail_by_one)
 
 pytestmark = pytest.mark.gpu
 
@@ -51,6 +52,19 @@ def test_unequal_batch_then_decoding(shape, dtype):
     got = run_batches(engine, requests, [[0, 1, 2]], prompt_lens)
     worst = compare(got, oracle, requests, dtype, cfg, f"{name} batch")
     print(f"{name} {dtype} batch: worst error/tolerance {worst}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_portions_and_mixed_steps(shape, dtype):
+    """A prompt fed in portions across a page edge, and steps that mix single tokens, a fresh prompt
+    and a further portion, at the benchmark's layer sizes."""
+    name, folder, oracle, requests = shape
+    cfg = SHAPES[name]
+    engine = build_engine(folder, dtype, max_tokens=sum(-(-len(r) // 64) * 64 for r in requests), max_seqs=3)
+    compare(run_chunked(engine, requests, [30, 35, 1, 64]), oracle, requests, dtype, cfg, f"{name} portions")
+    plans = [[40, 1, 1, 30, 1], [0, 0, 20], [1, 1, 33, 0, 20]]
+    compare(run_mixed(engine, requests, plans), oracle, requests, dtype, cfg, f"{name} mixed steps")
+    assert not engine.cache.live_slots
 
 
 def test_tail_by_one_in_bfloat16(shape):

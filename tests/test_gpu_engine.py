@@ -4,7 +4,7 @@ import pytest
 import torch
 
 from helpers import (CONFIGS, Oracle, build_engine, compare, make_folder, random_requests, run_batches,
-                     run_tail_by_one, run_whole)
+                     run_chunked, run_mixed, run_tail_by_one, run_whole)
 
 pytestmark = pytest.mark.gpu
 DTYPES = [torch.float32, torch.bfloat16]
@@ -81,6 +81,65 @@ def test_unequal_batches_with_slot_reuse(model, dtype):
     got = run_batches(engine, requests, batches[::-1], prompt_lens)
     compare(got, oracle, requests, dtype, CONFIGS[name], f"{name} batches again")
     print(f"{name} {dtype} batches: worst error/tolerance {worst}")
+
+
+# portions a prompt is fed in: page edges (63, 64, 65), a portion that starts inside the window's ring
+# after it has wrapped (B: 2 pages, C: 3), a portion longer than the whole ring, a portion of two
+CUTS = [[70, 60, 1000], [63, 1, 64, 65, 2, 1000], [2, 200, 1000], [64]]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_prompt_fed_in_several_portions(model, dtype):
+    """A multi-token step on a slot that already holds tokens: the step's queries see the cached
+    keys (through a ring that may have wrapped) and the step's own."""
+    name = model.name
+    folder, oracle = model.at(dtype)
+    cfg = CONFIGS[name]
+    requests = random_requests(cfg, [200, 300, 129, 9], seed=41)
+    engine = build_engine(folder, dtype, max_tokens=320)
+    for cuts in CUTS:
+        compare(run_chunked(engine, requests, cuts), oracle, requests, dtype, cfg, f"{name} portions {cuts}")
+    assert not engine.cache.live_slots
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_steps_that_mix_single_tokens_prompts_and_portions(model, dtype):
+    """In one step one sequence decodes a token onto its history, a second brings a fresh prompt, a
+    third a further portion of its prompt, and one sits the step out; run twice over the same
+    engine so that slots and pages are used again."""
+    name = model.name
+    folder, oracle = model.at(dtype)
+    cfg = CONFIGS[name]
+    requests = random_requests(cfg, [120, 100, 210, 33], seed=43)
+    plans = [[50, 1, 1, 1, 40, 1, 0, 1],          # prompt, single tokens, a portion onto history, a pause
+             [0, 0, 90],                          # joins at the third step with a 90-token prompt
+             [70, 60, 0, 40, 1, 1, 30],           # portions with a pause between them
+             [1, 1, 1]]                           # single tokens from an empty slot
+    engine = build_engine(folder, dtype, max_tokens=sum(-(-len(r) // 64) * 64 for r in requests), max_seqs=4)
+    for turn in range(2):
+        got = run_mixed(engine, requests, plans)
+        compare(got, oracle, requests, dtype, cfg, f"{name} mixed steps, turn {turn}")
+        assert not engine.cache.live_slots
+        requests, plans = requests[::-1], plans[::-1]
+
+
+def test_decoding_past_the_cache_room_of_an_all_window_model():
+    """A model whose layers all keep a window can grow past max_tokens positions (its rings never run
+    out of pages): the rotary table must cover the model's limit, also for steps replayed from a
+    captured graph."""
+    import tempfile
+    from pathlib import Path
+    cfg = CONFIGS["C"]
+    with tempfile.TemporaryDirectory() as tmp:
+        for dtype in DTYPES:
+            folder = make_folder(Path(tmp) / str(dtype), cfg, seed=3, attn_gain=GAIN[dtype])
+            oracle = Oracle(folder)
+            reqs = random_requests(cfg, [330, 20], seed=2)
+            engine = build_engine(folder, dtype, max_tokens=192 + 64, max_seqs=2)      # 256 tokens of room, 330 positions
+            assert engine.position_limit == cfg["max_position_embeddings"] and engine.use_graphs
+            got = run_batches(engine, reqs, [[0, 1]], [5, 3])
+            compare(got, oracle, reqs, dtype, cfg, "all-window model beyond the cache room")
+            assert engine.graph_replays > 200
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -1,5 +1,5 @@
-"""Each part alone, and parts that are not in the package: a mixer with state of its own, defined
-here, is registered, built into a model next to attention layers, loaded and stepped."""
+"""Each part of a layer alone, against the plain function of the same part.  (Parts that are not in
+the package, and a whole architecture made of them, are in test_gpu_toy_arch.py.)"""
 import math
 
 import numpy as np
@@ -7,7 +7,6 @@ import pytest
 import torch
 
 import plain_qwen2 as plain
-from helpers import TINY_B
 
 pytestmark = pytest.mark.gpu
 DEV = torch.device("cuda:0")
@@ -116,123 +115,3 @@ def test_rope_part_table_grows():
     ang = 499 / np.power(1e4, 2 * j / 16)
     assert np.abs(c2[499].double().cpu().numpy() - np.cos(ang)).max() < 1e-7
     assert np.abs(s2[499].double().cpu().numpy() - np.sin(ang)).max() < 1e-7
-
-
-# ----------------------------------------------------------------------------- a toy architecture
-def _register_toys():
-    """A mixer whose only memory is a running sum per sequence (fixed-size state, no keys), a
-    feed-forward with a routed choice between two matrices, and a position encoding that adds a
-    learned vector per position to the queries and keys.  All defined here, in torch."""
-    from llaisys_b200.parts import FeedForward, Mixer, PositionEncoding, TensorDecl, register_part
-
-    @register_part("mixer", "toy_running_sum")
-    class RunningSum(Mixer):
-        def __init__(self, spec, env):
-            super().__init__(spec, env)
-            self.h = spec.params["hidden_size"]
-
-        def state_size(self):
-            return self.h
-
-        def tensors(self):
-            return {"mix.weight": TensorDecl((self.h, self.h))}
-
-        def load(self, tensors):
-            self.w = tensors["mix.weight"]
-
-        def forward(self, x, ctx, call):
-            state = ctx.state(call)
-            out = torch.empty_like(x)
-            for b, (slot, n, start) in enumerate(zip(ctx.slots, ctx.n_new, ctx.seq_start.tolist())):
-                run = state[slot] + torch.cumsum(x[start:start + n].float(), dim=0)
-                state[slot] = run[-1]
-                pos = torch.arange(ctx.lens_before[b] + 1, ctx.lens_before[b] + n + 1, device=x.device)[:, None]
-                out[start:start + n] = ((run / pos) @ self.w.float().T).to(x.dtype)
-            return out
-
-    @register_part("ffn", "toy_routed")
-    class Routed(FeedForward):
-        def __init__(self, spec, env):
-            super().__init__(spec, env)
-            self.h = spec.params["hidden_size"]
-
-        def tensors(self):
-            return {"router.weight": TensorDecl((2, self.h)), "experts.0.weight": TensorDecl((self.h, self.h)),
-                    "experts.1.weight": TensorDecl((self.h, self.h))}
-
-        def load(self, tensors):
-            self.t = tensors
-
-        def forward(self, x, ctx):
-            choice = (x.float() @ self.t["router.weight"].float().T).argmax(-1)
-            y0, y1 = (x.float() @ self.t[f"experts.{i}.weight"].float().T for i in (0, 1))
-            return torch.where(choice[:, None] == 0, y0, y1).to(x.dtype)
-
-    @register_part("position", "toy_learned_offset")
-    class LearnedOffset(PositionEncoding):
-        def __init__(self, spec, env):
-            super().__init__(spec, env)
-            self.dh = spec.params["head_dim"]
-
-        def apply(self, qkv, num_heads, num_kv_heads, ctx, append=None):
-            from llaisys_b200 import kernels
-            T = qkv.shape[0]
-            qk = qkv[:, :(num_heads + num_kv_heads) * self.dh].view(T, -1, self.dh)
-            qk += (0.01 * ctx.tok_pos.to(qkv.dtype))[:, None, None]
-            if append is not None:
-                kernels.rope_append(qkv, num_heads, num_kv_heads, self.dh, tok_pos=ctx.tok_pos, append=append, err=ctx.err)
-
-
-def _toy_spec():
-    """Layer 0: running-sum mixer + routed feed-forward.  Layer 1: attention with the toy position
-    encoding.  Run order 0, 1, 0, 1: both layers run twice, and the second attention call reads
-    the first one's cache."""
-    from llaisys_b200.config import CallSpec, LayerSpec, ModelSpec, PartSpec
-    H = 32
-    norm = lambda p: PartSpec("rms_norm", {"size": H, "eps": 1e-5}, prefix=p)
-    l0 = LayerSpec("pre_norm_residual", PartSpec("toy_running_sum", {"hidden_size": H}, prefix="l0.mixer"), norm("l0.n1"),
-                   PartSpec("toy_routed", {"hidden_size": H}, prefix="l0.ffn"), norm("l0.n2"))
-    l1 = LayerSpec("pre_norm_residual",
-                   PartSpec("gqa_attention", {"hidden_size": H, "num_heads": 4, "num_kv_heads": 1, "head_dim": 8,
-                                              "qkv_bias": False, "scale": 0.3, "window": None,
-                                              "position": PartSpec("toy_learned_offset", {"head_dim": 8})}, prefix="l1.attn"),
-                   norm("l1.n1"), PartSpec("swiglu_mlp", {"hidden_size": H, "intermediate_size": 24}, prefix="l1.mlp"), norm("l1.n2"))
-    return ModelSpec("ToyForCausalLM", vocab_size=50, hidden_size=H, max_positions=256,
-                     embedding=PartSpec("token_embedding", {"vocab_size": 50, "hidden_size": H}, prefix="emb"),
-                     layers=(l0, l1), order=(CallSpec(0), CallSpec(1), CallSpec(0), CallSpec(1, cache_of=1)),
-                     final_norm=norm("fn"), head=PartSpec("lm_head", {"vocab_size": 50, "hidden_size": H, "tied_to": "emb.weight"}, prefix="head"))
-
-
-def test_toy_parts_register_build_and_step():
-    from llaisys_b200.cache import CacheConfig
-    from llaisys_b200.engine import DecoderModel, Engine, StepEntry
-    from llaisys_b200.parts import BuildEnv, known_parts
-    from llaisys_b200.weights import RandomSource, load_weights
-    _register_toys()
-    assert "toy_running_sum" in known_parts("mixer") and "toy_routed" in known_parts("ffn")
-    model = DecoderModel(_toy_spec(), BuildEnv(torch.float32, DEV))
-    names = set(model.expected_tensors())
-    assert {"l0.mixer.mix.weight", "l0.ffn.experts.1.weight", "l1.attn.q_proj.weight"} <= names and "head.weight" not in names
-    assert model.state_sizes() == [32, 0, 32, 0] and [n is not None for n in model.kv_needs()] == [False, True, False, True]
-    load_weights(model, RandomSource(model.expected_tensors(), seed=3, dtype=torch.float32, std=0.3))
-    engine = Engine(model, CacheConfig(max_tokens=256, max_seqs=3))
-    assert len(engine.cache.k_pools) == 1 and engine.cache.k_pools[0].shape[0] == 1        # one cache for both attention calls
-    assert set(engine.cache.state) == {0, 2}
-    assert not engine.use_graphs                     # the toy parts read back from the device: never captured
-    toks = np.random.default_rng(0).integers(0, 50, size=90).tolist()
-    a = engine.acquire()
-    whole = engine.step([StepEntry(a, toks, list(range(90)))])
-    engine.release(a)
-    # the same tokens cut differently, next to another sequence, in a slot whose state was used before
-    b, c = engine.acquire(), engine.acquire()
-    assert b == a
-    rows = [engine.step([StepEntry(b, toks[:70], list(range(70))), StepEntry(c, [1, 2, 3], [])])]
-    for t in range(70, 90):
-        entries = [StepEntry(b, [toks[t]], [0])] + ([StepEntry(c, [4], [])] if t < 75 else [])
-        rows.append(engine.step(entries))
-        if t == 74:
-            engine.release(c)
-    engine.check()
-    cut = torch.cat(rows)
-    assert torch.isfinite(whole).all() and float((whole - cut).abs().max()) < 1e-4
-    assert float(whole.std()) > 1e-3
