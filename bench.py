@@ -126,6 +126,16 @@ def linear_params(cfg, layers):
     return per_layer * layers, cfg["vocab_size"] * H
 
 
+def filled_slots(engine, batch, rng, vocab):
+    """`batch` slots that hold PROMPT_LEN cached tokens each, put there by real prefill steps of up to
+    eight sequences (the cache is filled the way serving fills it, through the step function)."""
+    from llaisys_b200.engine import StepEntry
+    slots = [engine.acquire() for _ in range(batch)]
+    for i in range(0, batch, 8):
+        engine.step([StepEntry(s, rng.integers(0, vocab, size=PROMPT_LEN).tolist(), []) for s in slots[i:i + 8]])
+    return slots
+
+
 def profile_run(args, model, cfg, rng) -> int:
     """Two uncaptured steps inside a cudaProfilerStart/Stop range, after a warm-up outside it."""
     import torch
@@ -140,12 +150,7 @@ def profile_run(args, model, cfg, rng) -> int:
             engine.step([StepEntry(s, rng.integers(0, V, size=PREFILL_TOKENS).tolist(), [PREFILL_TOKENS - 1])])
             engine.release(s)
     else:
-        slots = [engine.acquire() for _ in range(args.batch)]
-        for s in slots:
-            engine.cache.book.reserve(s, PROMPT_LEN)
-            engine.cache.book.commit(s, PROMPT_LEN)
-        for pool in engine.cache.k_pools + engine.cache.v_pools:
-            pool.normal_(0, 1)
+        slots = filled_slots(engine, args.batch, rng, V)
 
         def once():
             engine.step([StepEntry(s, [int(rng.integers(0, V))], [0]) for s in slots])
@@ -184,12 +189,7 @@ def timeline_run(args, model, cfg, rng) -> int:
             engine.step([StepEntry(s, prompt, [PREFILL_TOKENS - 1])])
             engine.release(s)
     else:
-        slots = [engine.acquire() for _ in range(B)]
-        for s in slots:
-            engine.cache.book.reserve(s, PROMPT_LEN)
-            engine.cache.book.commit(s, PROMPT_LEN)
-        for pool in engine.cache.k_pools + engine.cache.v_pools:
-            pool.normal_(0, 1)
+        slots = filled_slots(engine, B, rng, V)
 
         def once():
             engine.step([StepEntry(s, [int(rng.integers(0, V))], [0]) for s in slots])
@@ -451,23 +451,8 @@ def main() -> int:
                "frac": round(prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
 
     # ---- decode at a given batch: sequences that already hold PROMPT_LEN tokens each
-    def fill(batch):
-        """Slots with PROMPT_LEN cached tokens.  Up to batch 8 the cache is filled by a real prefill;
-        larger batches get pages of random keys and values (decode timing does not depend on the
-        values, only on how many there are)."""
-        slots = [engine.acquire() for _ in range(batch)]
-        if batch <= 8:
-            engine.step([StepEntry(s, rng.integers(0, V, size=PROMPT_LEN).tolist(), []) for s in slots])
-        else:
-            for s in slots:
-                engine.cache.book.reserve(s, PROMPT_LEN)
-                engine.cache.book.commit(s, PROMPT_LEN)
-            for pool in engine.cache.k_pools + engine.cache.v_pools:
-                pool.normal_(0, 1)
-        return slots
-
     def decode(batch, steps, warmup):
-        slots = fill(batch)
+        slots = filled_slots(engine, batch, rng, V)
         toks = rng.integers(0, V, size=(warmup + steps, batch)).tolist()
         sampler = Sampler(SamplingParams(top_k=1))
         for i in range(warmup):
