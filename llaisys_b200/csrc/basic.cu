@@ -498,5 +498,30 @@ LLB_API int llb_swiglu(void* out, const void* gate_up, int dtype, int T, int I, 
     return llb_status();
 }
 
+// ------------------------------------------------------------------ the same on dense operands
+// out = up * gate / (1 + exp(-gate)) and c = a + b on dense tensors of one dtype: the operators
+// swiglu and add of xsmccc/llaisys (src/ops/swiglu/cpu/swiglu_cpu.cpp:13-21, src/ops/add/cpu/add_cpu.cpp:8-16)
+// as the op-level interface exposes them; float32 arithmetic, one rounding at the output.
+template <typename T, bool SWIGLU>
+__global__ void dense_binary_kernel(T* __restrict__ out, const T* __restrict__ a, const T* __restrict__ b, size_t n) {
+    llb_grid_dependency_sync();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float x = to_f32(a[i]), y = to_f32(b[i]);
+    out[i] = from_f32<T>(SWIGLU ? y * (x / (1.0f + expf(-x))) : x + y);
+}
+
+// op 0: out = a + b;  op 1: out = b * a / (1 + exp(-a))  (a the gate, b the up projection)
+LLB_API int llb_dense_binary(void* out, const void* a, const void* b, int dtype, long long n, int op, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    if (op != 0 && op != 1) return (int)cudaErrorInvalidValue;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    LLB_DISPATCH_DTYPE(dtype, TT, {
+        if (op == 0) llb_launch(dense_binary_kernel<TT, false>, dim3(blocks), dim3(256), 0, stream, (TT*)out, (const TT*)a, (const TT*)b, (size_t)n);
+        else llb_launch(dense_binary_kernel<TT, true>, dim3(blocks), dim3(256), 0, stream, (TT*)out, (const TT*)a, (const TT*)b, (size_t)n);
+    });
+    return llb_status();
+}
+
 // ------------------------------------------------------------------ misc
 LLB_API const char* llb_error_string(int code) { return cudaGetErrorString((cudaError_t)code); }

@@ -152,6 +152,16 @@ def swiglu(gate_up: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def dense_binary(out: torch.Tensor, a: torch.Tensor, b: torch.Tensor, op: str):
+    """out = a + b (op "add") or out = b * a / (1 + exp(-a)) (op "swiglu": a the gate, b the up
+    projection) on contiguous tensors of one dtype and one shape."""
+    _need_cuda(out, a, b)
+    assert out.dtype == a.dtype == b.dtype and out.shape == a.shape == b.shape
+    assert out.is_contiguous() and a.is_contiguous() and b.is_contiguous()
+    f = _fn(_lib_basic(), "llb_dense_binary", [c_void_p, c_void_p, c_void_p, c_int, c_longlong, c_int, c_void_p])
+    _check(f(_ptr(out), _ptr(a), _ptr(b), _dt(out), out.numel(), {"add": 0, "swiglu": 1}[op], _stream()), op)
+
+
 def rope_append(qkv: torch.Tensor, nh: int, nkvh: int, dh: int, *, cos=None, sin=None, tok_pos=None,
                 append=None, err=None):
     """In place on the packed projections [T, (nh + 2 nkvh) dh]: rotate the query and key heads

@@ -131,19 +131,32 @@ def test_sampling_generation_is_reproducible_and_batch_independent(folders):
 
 def test_command_line(folders, tmp_path):
     env = dict(os.environ, PYTHONPATH=str(ROOT))
-    out = subprocess.run([sys.executable, "-m", "llaisys_b200.cli", "--model", str(folders["A"]), "--tokens", "5,17,3,200",
-                          "--max_steps", "6", "--test", "--dtype", "float32"], env=env, capture_output=True, text=True, timeout=600)
-    assert out.returncode == 0, out.stderr[-2000:]
-    assert "Test passed" in out.stdout and "Tokens:" in out.stdout
+    # --test: the engine's tokens against the CPU model's, in both precisions
+    for dtype in ("float32", "bfloat16"):
+        out = subprocess.run([sys.executable, "-m", "llaisys_b200.cli", "--model", str(folders.get("A", dtype)), "--tokens", "5,17,3,200",
+                              "--max_steps", "6", "--test", "--dtype", dtype], env=env, capture_output=True, text=True, timeout=600)
+        assert out.returncode == 0, out.stderr[-2000:]
+        assert "Test passed" in out.stdout and "Tokens:" in out.stdout
     cfg = tmp_path / "cfg.json"
     cfg.write_text(json.dumps(CONFIGS["B"]))
     out = subprocess.run([sys.executable, "-m", "llaisys_b200.cli", "--random-weights", str(cfg), "--seed", "3", "--tokens", "1,2,3",
                           "--max_steps", "4", "--temperature", "0.9", "--top_k", "20", "--top_p", "0.9"],
                          env=env, capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stderr[-2000:]
-    out = subprocess.run([sys.executable, "-m", "llaisys_b200.cli", "--device", "cpu", "--model", str(folders["A"]), "--tokens", "1"],
-                         env=env, capture_output=True, text=True, timeout=600)
-    assert out.returncode != 0 and "no CPU path" in out.stderr
+    # a file of requests of unequal lengths, generated as a batch and checked against the CPU model
+    (tmp_path / "batch.txt").write_text("5,17,3,200,7,7,7,7,7\n[9, 8]\n1\n")
+    out = subprocess.run([sys.executable, "-m", "llaisys_b200.cli", "--model", str(folders["B"]), "--batch-file", str(tmp_path / "batch.txt"),
+                          "--max_steps", "5", "--test", "--dtype", "float32"], env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert out.stdout.count("Tokens:") == 3 and "Test passed" in out.stdout
+    # the same request on the CPU device gives the same tokens
+    gpu = subprocess.run([sys.executable, "-m", "llaisys_b200.cli", "--model", str(folders["A"]), "--tokens", "5,17,3", "--max_steps", "4",
+                          "--top_k", "1", "--dtype", "float32"], env=env, capture_output=True, text=True, timeout=600)
+    cpu = subprocess.run([sys.executable, "-m", "llaisys_b200.cli", "--device", "cpu", "--model", str(folders["A"]), "--tokens", "5,17,3",
+                          "--max_steps", "4", "--top_k", "1"], env=env, capture_output=True, text=True, timeout=600)
+    assert gpu.returncode == 0 and cpu.returncode == 0, gpu.stderr[-1000:] + cpu.stderr[-1000:]
+    line = lambda o: o.stdout.split("Tokens:")[1].splitlines()[1]
+    assert line(gpu) == line(cpu)
 
 
 # ----------------------------------------------------------------------------- bin/trace_run
