@@ -11,12 +11,12 @@ import plain_qwen2 as plain
 GOLDEN = Path(__file__).with_name("golden")
 
 
-def _golden():
+def _golden(name="tiny_a"):
     spec = importlib.util.spec_from_file_location("make_golden", GOLDEN / "make_golden.py")
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
-    rec = json.loads((GOLDEN / "tiny_a_reference.json").read_text())
-    weights = {k: v.astype(np.float64) for k, v in mod.tiny_weights(rec["config"], rec["seed"]).items()}
+    rec = json.loads((GOLDEN / f"{name}_reference.json").read_text())
+    weights = {k: v.astype(np.float64) for k, v in mod.tiny_weights(rec["config"], rec["seed"], rec.get("gain", 1.0)).items()}
     return rec, weights
 
 
@@ -32,6 +32,28 @@ def test_greedy_tokens_match_reference_model():
     n = len(rec["prompt"])
     assert rec["generated"][:n] == rec["prompt"]
     got = plain.generate_greedy(rec["prompt"], rec["config"], w, max_new_tokens=8)
+    assert got == rec["generated"][n:]
+
+
+def test_window_layers_match_the_reference_operator_on_sliced_keys():
+    """Case B: theta 1e6, eps 1e-5, head size 24, 6 heads on 2, an untied head, and a window of 8 keys
+    from layer 1 on, where the recorded logits come from that project's own self_attention called per
+    query row on keys and values sliced to the window.  21 tokens: most rows have lost keys to the window."""
+    rec, w = _golden("tiny_b")
+    cfg = rec["config"]
+    assert cfg["sliding_window"] == 8 and cfg["max_window_layers"] == 1 and len(rec["prompt"]) > 2 * cfg["sliding_window"]
+    want = np.array(rec["logits"]).reshape(rec["logits_shape"])
+    got = plain.forward_logits(rec["prompt"], cfg, w)
+    # that project computes in float32: with scores spread over +-10 (the gain) its own rounding is a few 1e-6 of
+    # logits near 1; a window that is off by one key moves the logits by 0.5
+    assert np.abs(got - want).max() < 1e-5
+    # the window matters in this case: without it, or one key longer or shorter, the logits are other logits
+    for other in (dict(cfg, use_sliding_window=False), dict(cfg, sliding_window=9), dict(cfg, sliding_window=7),
+                  dict(cfg, max_window_layers=2)):
+        assert np.abs(plain.forward_logits(rec["prompt"], other, w) - want).max() > 1e-3
+    # that project's model applies no window: its greedy tokens are those of the plain model without one
+    n = len(rec["prompt"])
+    got = plain.generate_greedy(rec["prompt"], dict(cfg, use_sliding_window=False), w, max_new_tokens=8)
     assert got == rec["generated"][n:]
 
 
