@@ -344,11 +344,120 @@ def own_workload(args, model, cfg, cfg_dict, layers, full_layers, shape_name, pk
     return 0
 
 
-def reference_arm():
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "xsmccc/llaisys cannot be installed offline (pip: no setup.py or pyproject.toml at its root; its "
-                      "python package needs libllaisys.so built by xmake, which is not installed) and it has no CUDA "
-                      "path: every NVIDIA entry point is TO_BE_IMPLEMENTED, and it serves one sequence on the CPU"}))
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+REF_SOURCES = ["src/utils/*.cpp", "src/device/*.cpp", "src/device/cpu/*.cpp", "src/core/*/*.cpp", "src/tensor/*.cpp",
+               "src/ops/*/*.cpp", "src/ops/*/cpu/*.cpp", "src/llaisys/*.cc", "src/models/qwen2/*.cpp"]
+
+
+def build_reference(src: str) -> str:
+    """Copies an unmodified checkout of xsmccc/llaisys to baseline/_ref and compiles its C++ sources with g++ into
+    the shared library that its Python package loads (the project builds with xmake, which is not installed; the
+    compiler, the optimisation level and the source list are those of tests/golden/make_golden.py).  Returns the
+    folder to put on sys.path."""
+    import glob
+    import shutil
+    if os.path.exists(REF_DIR):
+        shutil.rmtree(REF_DIR)
+    shutil.copytree(src, REF_DIR, ignore=shutil.ignore_patterns(".git"))
+    srcs = []
+    for pat in REF_SOURCES:
+        srcs += sorted(glob.glob(os.path.join(REF_DIR, pat)))
+    lib = os.path.join(REF_DIR, "python", "llaisys", "libllaisys", "libllaisys.so")
+    subprocess.check_call(["g++", "-std=c++17", "-O2", "-fPIC", "-shared", f"-I{os.path.join(REF_DIR, 'include')}", *srcs, "-o", lib])
+    return os.path.join(REF_DIR, "python")
+
+
+def reference_arm(args) -> int:
+    """xsmccc/llaisys itself, unmodified, through its own public API (`llaisys.models.Qwen2(folder).generate`,
+    python/llaisys/models/qwen2.py:212-283) on the one device it implements, the CPU.
+
+    What can and cannot be the same as our arm: the layer sizes and the layer count are the benchmark's
+    (Qwen2-1.5B shape, random weights), but that project serves ONE sequence, feeds it ONE token per call of its
+    C function (prompt included, src/models/qwen2/qwen2.cpp:53-87) in float32 through scalar loops on one core, and
+    has no CUDA path (every NVIDIA entry point is TO_BE_IMPLEMENTED).  A 2,048-token prompt would take hours, a
+    batch does not exist.  So this arm measures decode tokens a second at batch 1, float32, after a prompt of
+    `warmup` tokens, and says so in `config` (same_config: false); the ratio of the two arms is not a speed-up at
+    equal work."""
+    import glob
+    import tempfile
+    lib = os.path.join(REF_DIR, "python", "llaisys", "libllaisys", "libllaisys.so")
+    why = None
+    try:
+        if args.reference_src:
+            build_reference(args.reference_src)
+        if not os.path.exists(lib):
+            why = ("baseline/_ref holds no built copy of xsmccc/llaisys (pip cannot install it: no setup.py or pyproject.toml; "
+                   "build it with: python bench.py --impl reference --reference-src <checkout>)")
+    except (OSError, subprocess.CalledProcessError) as e:
+        why = f"building xsmccc/llaisys with g++ failed: {type(e).__name__}: {e}"
+    if why:
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+
+    import numpy as np
+    steps, prompt_len = min(args.steps, 32), max(args.warmup, 3)
+    cfg = dict(QWEN2_1_5B)
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    L, H, I, V = cfg["num_hidden_layers"], cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkvh = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    dh = H // nh
+    shapes = {"model.embed_tokens.weight": (V, H), "model.norm.weight": (H,), "lm_head.weight": (V, H)}
+    for l in range(L):
+        q = f"model.layers.{l}."
+        shapes.update({q + "input_layernorm.weight": (H,), q + "post_attention_layernorm.weight": (H,),
+                       q + "self_attn.q_proj.weight": (nh * dh, H), q + "self_attn.q_proj.bias": (nh * dh,),
+                       q + "self_attn.k_proj.weight": (nkvh * dh, H), q + "self_attn.k_proj.bias": (nkvh * dh,),
+                       q + "self_attn.v_proj.weight": (nkvh * dh, H), q + "self_attn.v_proj.bias": (nkvh * dh,),
+                       q + "self_attn.o_proj.weight": (H, nh * dh), q + "mlp.gate_proj.weight": (I, H),
+                       q + "mlp.up_proj.weight": (I, H), q + "mlp.down_proj.weight": (H, I)})
+    try:
+        with tempfile.TemporaryDirectory() as tmp:
+            # float32 N(0, 0.02) weights (norm weights 1 + N), written tensor by tensor
+            import struct
+            header, off = {}, 0
+            for name, shape in shapes.items():
+                n = int(np.prod(shape)) * 4
+                header[name] = {"dtype": "F32", "shape": list(shape), "data_offsets": [off, off + n]}
+                off += n
+            raw = json.dumps(header).encode()
+            raw += b" " * (-len(raw) % 8)
+            rng = np.random.default_rng(0)
+            with open(os.path.join(tmp, "model.safetensors"), "wb") as f:
+                f.write(struct.pack("<Q", len(raw)) + raw)
+                for name, shape in shapes.items():
+                    x = rng.standard_normal(size=shape, dtype=np.float32) * np.float32(0.02)
+                    if name.endswith("norm.weight"):
+                        x += np.float32(1.0)
+                    f.write(x.tobytes())
+            cfg_out = dict(cfg, torch_dtype="float32")
+            cfg_out["max_position_embeddings"] = 4096           # its cache has this many rows per layer
+            with open(os.path.join(tmp, "config.json"), "w") as f:
+                json.dump(cfg_out, f)
+            sys.path.insert(0, os.path.join(REF_DIR, "python"))
+            import llaisys
+            model = llaisys.models.Qwen2(tmp, llaisys.DeviceType.CPU)
+            prompt = rng.integers(0, V, size=prompt_len).tolist()
+            out = model.generate(prompt, max_new_tokens=1)       # the prompt, one token per call, and the first new token
+            t0 = time.perf_counter()
+            more = model.generate([out[-1]], max_new_tokens=steps)      # goes on in the same cache: `steps` calls of one token
+            dt = time.perf_counter() - t0
+            done = len(more) - 1
+    except Exception as e:              # no room for the 7 GB folder, a missing package: say which
+        print(json.dumps({"impl": "reference", "unavailable": f"running xsmccc/llaisys on the CPU failed: {type(e).__name__}: {e}"}))
+        return 0
+    print(json.dumps({
+        "impl": "reference",
+        "metric": "decode tok/s @ batch 1 (Qwen2-1.5B shape, float32, CPU: the only device and batch xsmccc/llaisys serves)",
+        "value": round(done / dt, 4), "unit": "tokens/s", "n_gpus": 0, "steps": done, "warmup": prompt_len,
+        "ms_per_step": round(dt / done * 1e3, 2), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic: seeded random weights N(0,0.02), seeded uniform-random token ids",
+        "config": {"model": SHAPES["1.5b"][0], "layers": L, "layers_of_config": QWEN2_1_5B["num_hidden_layers"], "hidden": H,
+                   "heads": nh, "kv_heads": nkvh, "head_dim": dh, "intermediate": I, "vocab": V, "global_batch": 1,
+                   "prompt_len": prompt_len, "device": "cpu", "same_config": False,
+                   "why_not_same": "no batching, one token per call, no CUDA path: batch 8 and 2,048-token prompts do not exist there",
+                   "build": "g++ -std=c++17 -O2 of the unmodified sources under baseline/_ref"},
+    }))
     return 0
 
 
@@ -359,6 +468,8 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has")
+    ap.add_argument("--reference-src", default=os.environ.get("LLAISYS_REFERENCE_SRC"),
+                    help="with --impl reference: a checkout of xsmccc/llaisys to copy to baseline/_ref and build there first")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--shape", choices=sorted(SHAPES), default="1.5b", help="layer sizes (default: the benchmark's)")
     ap.add_argument("--workload", choices=["uniform", "own"], default="uniform",
@@ -375,7 +486,7 @@ def main() -> int:
                     help="print the per-kernel timeline of a step (torch.profiler, no ncu) instead of measuring")
     args = ap.parse_args()
     if args.impl == "reference":
-        return reference_arm()
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py: llaisys_b200 is a single-GPU library; --gpus {args.gpus} is not supported (use --gpus 1)")
         return 2

@@ -40,7 +40,15 @@ constexpr int BM = 128;        // weight rows of a tile (UMMA M)
 constexpr int BK = 64;         // k elements of a stage: one 128-byte swizzled row of bf16
 constexpr int UMMA_K = 16;     // k elements of one tcgen05.mma of kind::f16
 constexpr int THREADS = 128;
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
+#ifndef LLB_WAIT_LIMIT
+#define LLB_WAIT_LIMIT (1u << 22)
+#endif
+constexpr uint32_t WAIT_LIMIT = LLB_WAIT_LIMIT;      // tries of a bounded wait (a test build makes it small)
+// A test build (-DLLB_TEST_STALL=1) can make a wait run out without any fault: a launch that finds TEST_STALL_ARMED
+// in its error word arms the first stage's "full" barrier for sixteen bytes more than are ever requested, so that
+// the barrier's phase never completes, the issuing thread's wait gives up, and the block leaves by the abort path
+// (error word, wait for the copies that are in flight, tensor memory freed).  Not compiled into the product.
+constexpr int TEST_STALL_ARMED = -7;
 
 constexpr uint64_t HINT_EVICT_FIRST = 0x12F0000000000000ull;
 constexpr uint64_t HINT_EVICT_LAST = 0x14F0000000000000ull;
@@ -211,6 +219,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // CTA's share of the weight is already on its way into shared memory.
     const int prefetched = min(STAGES, kb1 - kb0);
     if (warp == 0 && lane == 0) {
+#ifdef LLB_TEST_STALL
+        if (*(volatile int*)g.err == TEST_STALL_ARMED)       // sixteen bytes that nothing will ever bring (no arrival)
+            asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar_full), "r"(16u) : "memory");
+#endif
         for (int i = 0; i < prefetched; ++i) {
             uint32_t dst = base + i * S::STAGE_BYTES;
             mbar_expect_tx(bar_full + 8 * i, S::STAGE_BYTES);
@@ -433,6 +445,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
         }
     }
+    if (aborted && g.splits > 1 && !push && tid == 0) {
+        // A block that gave up still arrives at its tile's counter, so that the counter is back at zero when the
+        // launch is over whatever happened (the tile's output is not valid; the error word says so).
+        const int tile = blockIdx.y * gridDim.x + blockIdx.x;
+        if (atomicAdd(&g.counters[tile], 1) == g.splits - 1) g.counters[tile] = 0;
+    }
     if (push) {
         if (aborted && !S::OWN_RECV) {      // pairs with the arrivals of the peers
             asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
@@ -488,12 +506,15 @@ template <int BN, int STAGES, bool DUAL>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& g, dim3 grid, cudaStream_t stream) {
     auto k = gemm_tc_kernel<BN, STAGES, DUAL>;
     constexpr int smem = Smem<BN, STAGES, DUAL>::TOTAL;
-    static bool configured = false;
-    if (!configured) {
+    // function attributes belong to a device's copy of the kernel: set them once on every device that launches it
+    static bool configured[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+    if (!configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return -2000 - (int)e;       // shared-memory opt-in refused: -(2000 + cudaError)
         cudaFuncSetAttribute(k, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);      // clusters of sixteen
-        configured = true;
+        configured[dev] = true;
     }
     llb_prefer_max_shared((const void*)k);
     cudaLaunchConfig_t cfg = {};
@@ -620,6 +641,24 @@ int noalloc_setup(NoAllocPtrs* out) {
 }
 
 }  // namespace
+
+int llb_gemm_tc_noalloc_status(cudaStream_t stream) {
+    NoAllocPtrs ptrs;
+    int rc = noalloc_setup(&ptrs);
+    if (rc) return rc;
+    int code = 0;                                   // caller-side storage on the stack: nothing is allocated
+    if (cudaMemcpyAsync(&code, ptrs.err, sizeof(int), cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+        cudaStreamSynchronize(stream) != cudaSuccess) {
+        cudaGetLastError();
+        return LLB_NOALLOC_SETUP_FAILED;
+    }
+    if (code != 0) {
+        // a block gave up a wait: clear the word, and the tile counters in case a launch was cut short
+        cudaMemsetAsync(ptrs.err, 0, sizeof(int), stream);
+        cudaMemsetAsync(ptrs.counters, 0, sizeof(int) * LLB_NOALLOC_TILES, stream);
+    }
+    return code;
+}
 
 int llb_gemm_tc_noalloc(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int y_dtype,
                         int T, int N, int K, int ldx, int ldy, int bn, int splits, cudaStream_t stream) {

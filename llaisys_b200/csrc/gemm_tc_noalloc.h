@@ -24,8 +24,15 @@
 // Sharing.  All calls on a device use the same scratch.  Calls on one stream follow one another
 // and are safe.  Two calls that may run on the GPU at the same time (different streams) race on
 // the scratch and give wrong results: do not overlap them.  The counters are back at zero when
-// a call's kernel ends, and a partial tile is always written before it is read, so nothing has
-// to be cleared between calls.
+// a call's kernel ends (a block that gives up a wait still arrives at its counter), and a partial
+// tile is always written before it is read, so nothing has to be cleared between calls.
+//
+// Errors on the device.  Every wait inside the kernel is bounded.  If one runs out (it never
+// should), the block records a code in an error word that lives beside the scratch, and the
+// output of that call is not valid although the call returned 0: the launch is asynchronous.
+// llb_gemm_tc_noalloc_status() waits for the stream, returns that word (0: every call since the
+// last query was complete) and clears it.  Callers that cannot afford to trust blindly ask it
+// before they use a result; it allocates nothing either.
 //
 // The function calls no cudaMalloc, cudaFree, or any other allocating routine, on the device or
 // on the host heap; tensor maps are encoded on the stack on every call.
@@ -49,6 +56,11 @@ extern "C" {
 __attribute__((visibility("default")))
 int llb_gemm_tc_noalloc(const void* X, const void* W, const void* bias, int bias_dtype, void* Y, int y_dtype,
                         int T, int N, int K, int ldx, int ldy, int bn, int splits, cudaStream_t stream);
+
+// Waits for `stream`, then returns 0 if no call on the current device gave up a wait since the last
+// query, else the code of the wait (101-104) after clearing it, or LLB_NOALLOC_SETUP_FAILED.
+__attribute__((visibility("default")))
+int llb_gemm_tc_noalloc_status(cudaStream_t stream);
 
 #ifdef __cplusplus
 }

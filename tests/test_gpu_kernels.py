@@ -511,3 +511,49 @@ def test_attention_prefill_from_cache_tcgen05(nh, nkvh, dh, window):
         _close(kernels.attention_prefill(*args, all_from_cache=True), want, dtype, atol=6e-3)
     finally:
         kernels.ops.TC_ATTENTION = True
+
+
+@pytest.mark.parametrize("splits", [1, 3])
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_next_launch_is_right(splits, tmp_path):
+    """A test build of the tensor-core product (a small wait limit, and a switch that arms one stage barrier for
+    sixteen bytes that nothing ever brings: no fault, no copy left in flight) makes the issuing thread's wait run
+    out.  The block must record code 101, free its tensor memory and return; the tile counters must be back at
+    zero; Engine.check() must raise; and the launches that follow must be right."""
+    from ctypes import c_int, c_longlong, c_void_p
+    from helpers import TINY_A, build_engine, make_folder
+    from llaisys_b200 import kernels
+    from llaisys_b200.csrc.build import load_module
+    from llaisys_b200.engine import StepError
+    from llaisys_b200.kernels import ops
+    lib = load_module("gemm_tc.cu", {"LLB_WAIT_LIMIT": 4096, "LLB_TEST_STALL": 1})
+    f = lib.llb_gemm_tc
+    f.restype = c_int
+    f.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                  c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p]
+    T, N, K = 8, 300, 1096
+    x, w, b = _tc_case(T, N, K, 77, bias=torch.float32)
+    want = plain.linear(x.double().cpu().numpy(), w.double().cpu().numpy(), b.double().cpu().numpy())
+    scratch, counters, err = ops._tc_resources(torch.device(DEV))
+    engine = build_engine(make_folder(tmp_path, TINY_A, 0), torch.bfloat16, max_tokens=64)
+
+    def launch():
+        out = torch.zeros((T, N), dtype=torch.float32, device=DEV)
+        rc = f(x.data_ptr(), w.data_ptr(), b.data_ptr(), 0, out.data_ptr(), 0, T, N, K, x.stride(0), out.stride(0), 16, splits, 0, 0,
+               scratch.data_ptr(), scratch.numel(), counters.data_ptr(), counters.numel(), err.data_ptr(),
+               torch.cuda.current_stream().cuda_stream)
+        assert rc == 0
+        torch.cuda.synchronize()
+        return out
+
+    assert kernels.tc_error(DEV) == 0
+    _tc_check(launch(), want, K)                       # the test build is the same kernel when the switch is off
+    err.fill_(-7)                                      # the switch: this launch's first stage never fills
+    launch()
+    assert kernels.tc_error(DEV, clear=False) == 101   # the wait for a full stage ran out, and said so
+    assert int(counters.abs().sum()) == 0              # blocks that gave up still arrived at their tile's counter
+    with pytest.raises(StepError, match="101"):
+        engine.check()
+    engine.check()                                     # reported once
+    _tc_check(launch(), want, K)                       # the context is whole: the same launch is right again
+    _tc_check(kernels.linear(x, w, b, out_dtype=torch.float32, plan=(16, splits, 0)), want, K)
+    assert kernels.tc_error(DEV) == 0

@@ -22,6 +22,13 @@ def _entry():
     return f
 
 
+def _status():
+    from llaisys_b200.csrc.build import load_module
+    f = load_module("gemm_tc.cu").llb_gemm_tc_noalloc_status
+    f.restype, f.argtypes = c_int, [c_void_p]
+    return f(torch.cuda.current_stream().cuda_stream)
+
+
 def _call(f, x, w, bias, out, bn, splits):
     return f(x.data_ptr(), w.data_ptr(), bias.data_ptr() if bias is not None else None, 1, out.data_ptr(),
              0 if out.dtype == torch.float32 else 1, x.shape[0], w.shape[0], x.shape[1], x.stride(0), out.stride(0),
@@ -37,6 +44,8 @@ def test_same_result_as_the_regular_entry_point_twice_in_a_row(T, N, K, bn, spli
     w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(DEV)
     b = torch.randn(N, generator=g).to(torch.bfloat16).to(DEV)
     want = kernels.linear(x, w, b, out_dtype=torch.float32, plan=(bn, splits)).clone()
+    import plain_qwen2 as plain
+    exact = torch.from_numpy(plain.linear(x.double().cpu().numpy(), w.double().cpu().numpy(), b.double().cpu().numpy())).to(DEV)
     for call in range(2):                     # the second call meets the scratch and the counters the first one left
         out = torch.full((T, N), float("nan"), dtype=torch.float32, device=DEV)
         torch.cuda.synchronize()
@@ -50,6 +59,10 @@ def test_same_result_as_the_regular_entry_point_twice_in_a_row(T, N, K, bn, spli
         err = (out - want).abs()
         bound = 5e-4 * (K / 64) ** 0.5 + 2e-3 * want.abs()
         assert torch.isfinite(out).all() and bool((err <= bound).all()), f"call {call}: max error {float(err.max())}"
+        # and against the plain product, which shares nothing with either entry point
+        err = (out.double() - exact).abs()
+        assert bool((err <= 5e-4 * (K / 64) ** 0.5 + 2e-3 * exact.abs()).all()), f"call {call}: {float(err.max())} from the plain product"
+        assert _status() == 0                 # no block gave up a wait
     out_bf = torch.empty((T, N), dtype=torch.bfloat16, device=DEV)
     assert _call(f, x, w, None, out_bf, bn, 1) == 0                  # no bias, bfloat16 out, no split
     ref = kernels.linear(x, w)
@@ -66,3 +79,4 @@ def test_sizes_beyond_the_built_in_scratch_are_refused():
     torch.cuda.synchronize()
     assert float(out.min()) == 7.0                                   # nothing was launched
     assert _call(f, x, w, None, out, 100, 1) != 0                    # a tile size the kernel does not have
+    assert _status() == 0
