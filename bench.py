@@ -344,7 +344,7 @@ def own_workload(args, model, cfg, cfg_dict, layers, full_layers, shape_name, pk
     return 0
 
 
-REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+REF_DIR = os.environ.get("LLAISYS_REF_DIR") or os.path.join(ROOT, "baseline", "_ref")
 REF_SOURCES = ["src/utils/*.cpp", "src/device/*.cpp", "src/device/cpu/*.cpp", "src/core/*/*.cpp", "src/tensor/*.cpp",
                "src/ops/*/*.cpp", "src/ops/*/cpu/*.cpp", "src/llaisys/*.cc", "src/models/qwen2/*.cpp"]
 
@@ -411,6 +411,10 @@ def reference_arm(args) -> int:
                        q + "self_attn.v_proj.weight": (nkvh * dh, H), q + "self_attn.v_proj.bias": (nkvh * dh,),
                        q + "self_attn.o_proj.weight": (H, nh * dh), q + "mlp.gate_proj.weight": (I, H),
                        q + "mlp.up_proj.weight": (I, H), q + "mlp.down_proj.weight": (H, I)})
+    # that project prints its progress on standard output: send it to standard error, so that this arm prints one line
+    sys.stdout.flush()
+    saved_stdout = os.dup(1)
+    os.dup2(2, 1)
     try:
         with tempfile.TemporaryDirectory() as tmp:
             # float32 N(0, 0.02) weights (norm weights 1 + N), written tensor by tensor
@@ -444,8 +448,12 @@ def reference_arm(args) -> int:
             dt = time.perf_counter() - t0
             done = len(more) - 1
     except Exception as e:              # no room for the 7 GB folder, a missing package: say which
+        sys.stdout.flush()
+        os.dup2(saved_stdout, 1)
         print(json.dumps({"impl": "reference", "unavailable": f"running xsmccc/llaisys on the CPU failed: {type(e).__name__}: {e}"}))
         return 0
+    sys.stdout.flush()
+    os.dup2(saved_stdout, 1)
     print(json.dumps({
         "impl": "reference",
         "metric": "decode tok/s @ batch 1 (Qwen2-1.5B shape, float32, CPU: the only device and batch xsmccc/llaisys serves)",

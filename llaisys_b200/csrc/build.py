@@ -151,7 +151,7 @@ def load_module(source: str, defines: dict | None = None) -> ctypes.CDLL:
 # The modules that serving the usual head sizes (64 and 128) needs, in both precisions.  Any other
 # head size is compiled when a model first asks for it; tests name the sizes they need themselves.
 DEFAULT_MODULES = [
-    ("basic.cu", {}), ("gemm_simt.cu", {}), ("gemm_tc.cu", {}), ("gemm_tc2.cu", {}), ("sampling.cu", {}), ("random_init.cu", {}),
+    ("basic.cu", {}), ("gemm_simt.cu", {}), ("gemm_tc.cu", {}), ("gemm_tc2.cu", {}), ("mlp_tc.cu", {}), ("sampling.cu", {}), ("random_init.cu", {}),
     *[("attention_simt.cu", {"LLB_HEAD_DIM": d}) for d in (64, 128)],
     *[("attention_mma.cu", {"LLB_HEAD_DIM": d}) for d in (64, 128)],
     *[("attention_tc.cu", {"LLB_HEAD_DIM": d}) for d in (64, 128)],

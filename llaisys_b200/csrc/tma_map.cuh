@@ -73,4 +73,29 @@ static inline int bf16_map_64(const void* ptr, long long rows, int cols, int ld,
     return 0;
 }
 
+// A 2-D map over a row-major float32 matrix [rows, cols] with row stride ld (elements): boxes of {box_cols columns,
+// box_rows rows}, no swizzle (a box lies in shared memory as [box_rows][box_cols]); for stores and reductions, which
+// clip what lies outside the matrix.  The base must be 16-byte aligned and ld a multiple of 4.  Cached like the others.
+static inline int f32_map_plain(const void* ptr, long long rows, int cols, int ld, int box_cols, int box_rows, CUtensorMap* out) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    MapKey key{ptr, rows, cols, ld, box_rows * 65536 + box_cols};
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = cache.find(key);
+    if (it != cache.end()) { *out = it->second; return 0; }
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 4};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return -1000 - (int)r;
+    if (cache.size() > 4096) cache.clear();
+    cache.emplace(key, *out);
+    return 0;
+}
+
 }  // namespace llb_tma

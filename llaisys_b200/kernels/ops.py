@@ -363,6 +363,44 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, plan=None) -> torch.Te
     return swiglu(linear(x, gate_up))
 
 
+FUSED_MLP = __import__("os").environ.get("LLAISYS_FUSED_MLP", "1") != "0"     # tests switch the one-launch feed-forward off to compare
+_MLP_STAGES = int(__import__("os").environ.get("LLAISYS_MLP_STAGES", "0"))     # depth of its TMA ring (0: the kernel's choice)
+# LLAISYS_MLP_WAIT_LIMIT: a build of that kernel whose bounded waits give up after this many tries (for trying out changes)
+_MLP_DEFINES = ({"LLB_WAIT_LIMIT": int(__import__("os").environ["LLAISYS_MLP_WAIT_LIMIT"])}
+                if __import__("os").environ.get("LLAISYS_MLP_WAIT_LIMIT") else None)
+
+
+def mlp_fused_ok(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, residual: torch.Tensor) -> bool:
+    """True when the whole SwiGLU feed-forward of these tokens can run as one launch (csrc/mlp_tc.cu):
+    bfloat16 operands, at most 32 tokens, widths that are multiples of 8 and an output width whose
+    accumulators fit tensor memory."""
+    if not (FUSED_MLP and TC_ENABLED and x.is_cuda and x.dtype == gate_up.dtype == down.dtype == torch.bfloat16
+            and residual.dtype == torch.float32 and residual.is_contiguous() and x.stride(1) == 1 and x.stride(0) % 8 == 0
+            and not ((x.data_ptr() | gate_up.data_ptr() | down.data_ptr()) & 15)):
+        return False
+    T, H = x.shape
+    I = down.shape[1]
+    if gate_up.shape != (2 * I, H) or down.shape != (H, I) or residual.shape != (T, H):
+        return False
+    f = load_module("mlp_tc.cu", _MLP_DEFINES).llb_mlp_fused_ok
+    f.argtypes, f.restype = [c_int, c_int, c_int], c_int
+    return bool(f(T, H, I))
+
+
+def mlp_fused(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, residual: torch.Tensor, stages: int = 0) -> None:
+    """residual [T, H] (float32) += down(up(x) * silu(gate(x))) in one launch; gate_up is [2I, H] with the gate rows
+    first, down [H, I].  See mlp_fused_ok() for what it takes."""
+    _need_cuda(x, gate_up, down, residual)
+    T, H = x.shape
+    I = down.shape[1]
+    err = _tc_resources(x.device)[2]
+    stages = stages or _MLP_STAGES
+    f = _fn(load_module("mlp_tc.cu", _MLP_DEFINES), "llb_mlp_fused",
+            [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(x), x.stride(0), _ptr(gate_up), _ptr(down), _ptr(residual), T, H, I, _sm_count(x.device), stages,
+             _ptr(err), _stream()), "feed-forward (one launch, tensor cores)")
+
+
 # ------------------------------------------------------------------ attention
 class _AttnParams(ctypes.Structure):
     _fields_ = [("q", c_void_p), ("k_new", c_void_p), ("v_new", c_void_p), ("row_stride", c_int),

@@ -151,7 +151,14 @@ class Mixer(Part):
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        """x: normalised activations [T, H].  Returns what is to be added to the residual stream."""
         raise NotImplementedError
+
+    def forward_into(self, x: torch.Tensor, ctx, residual: torch.Tensor) -> bool:
+        """A feed-forward that can add its result to the float32 residual stream [T, H] itself (in its
+        last kernel, which saves a pass over the activations) does so and returns True; the block
+        then has no delta to hand on.  False (the default): nothing was done, call forward()."""
+        return False
 
 
 @dataclass

@@ -24,6 +24,8 @@ class PreNormResidual(Block):
                 h = residual.to(self.env.dtype)
             if sub.category == "mixer":
                 pending = sub.part.forward(h, ctx, next(mixers))
+            elif sub.part.forward_into(h, ctx, residual):
+                pending = None
             else:
                 pending = sub.part.forward(h, ctx)
         return residual, pending

@@ -32,3 +32,10 @@ class SwiGLUMLP(FeedForward):
 
     def forward(self, x, ctx):
         return kernels.linear(kernels.linear_swiglu(x, self.gate_up), self.down)
+
+    def forward_into(self, x, ctx, residual):
+        # a few tokens (decode): the three matrices stream through one launch that ends in the residual add
+        if not kernels.mlp_fused_ok(x, self.gate_up, self.down, residual):
+            return False
+        kernels.mlp_fused(x, self.gate_up, self.down, residual)
+        return True

@@ -12,8 +12,8 @@ import pytest
 ROOT = Path(__file__).resolve().parent.parent
 
 
-def _bench(*args):
-    return subprocess.run([sys.executable, str(ROOT / "bench.py"), *args], capture_output=True, text=True, timeout=120)
+def _bench(*args, env=None):
+    return subprocess.run([sys.executable, str(ROOT / "bench.py"), *args], capture_output=True, text=True, timeout=120, env=env)
 
 
 def test_more_than_one_gpu_is_refused_with_one_line():
@@ -22,11 +22,14 @@ def test_more_than_one_gpu_is_refused_with_one_line():
     assert len(p.stdout.strip().splitlines()) == 1 and "single-GPU" in p.stdout
 
 
-def test_reference_arm_says_why_it_is_unavailable():
-    p = _bench("--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "1")
-    assert p.returncode == 0
-    line = json.loads(p.stdout.strip().splitlines()[-1])
+def test_reference_arm_says_why_it_is_unavailable(tmp_path):
+    """Without a built copy of the reference (here: an empty folder in its place) the arm prints one line that says so."""
+    import os
+    p = _bench("--impl", "reference", "--gpus", "1", "--steps", "2", "--warmup", "1", env=dict(os.environ, LLAISYS_REF_DIR=str(tmp_path)))
+    assert p.returncode == 0 and len(p.stdout.strip().splitlines()) == 1
+    line = json.loads(p.stdout.strip())
     assert line["impl"] == "reference" and isinstance(line["unavailable"], str) and "\n" not in line["unavailable"]
+    assert "--reference-src" in line["unavailable"]
 
 
 def test_own_workload_needs_a_shape_that_has_one():

@@ -557,3 +557,38 @@ def test_a_bounded_wait_that_runs_out_is_reported_and_the_next_launch_is_right(s
     _tc_check(launch(), want, K)                       # the context is whole: the same launch is right again
     _tc_check(kernels.linear(x, w, b, out_dtype=torch.float32, plan=(16, splits, 0)), want, K)
     assert kernels.tc_error(DEV) == 0
+
+
+@pytest.mark.parametrize("T,H,I,stages", [(8, 1536, 8960, 0), (1, 1536, 8960, 4), (16, 1536, 8960, 10), (17, 1536, 8960, 0),
+                                          (32, 256, 520, 6), (5, 144, 232, 0), (9, 64, 72, 8), (3, 3584, 18944, 0),
+                                          (20, 3584, 1096, 0), (2, 5120, 640, 0)])
+def test_feed_forward_in_one_launch(T, H, I, stages):
+    """gate/up + SwiGLU + down + residual add as one kernel: slices of the intermediate dimension per block, the
+    down projection's partial sums added to the float32 residual.  Sizes: the benchmark shapes' (one and two
+    slices per block, 12 and 28 output tiles), widths that are no multiple of the tiles, both token tiles."""
+    from llaisys_b200 import kernels
+    rng = np.random.default_rng(T + H + I)
+    x = torch.from_numpy(rng.normal(size=(T, H))).to(torch.bfloat16).to(DEV)
+    gu = torch.from_numpy(rng.normal(size=(2 * I, H)) * (2.0 / math.sqrt(H))).to(torch.bfloat16).to(DEV)
+    wd = torch.from_numpy(rng.normal(size=(H, I)) * (1.0 / math.sqrt(I))).to(torch.bfloat16).to(DEV)
+    res0 = torch.from_numpy(rng.normal(size=(T, H))).float().to(DEV)
+    if not kernels.mlp_fused_ok(x, gu, wd, res0):
+        bn = 16 if T <= 16 else 32
+        assert 2 * bn + -(-H // 128) * bn > 512          # refused only where tensor memory cannot hold the accumulators
+        return
+    pre = plain.linear(x.double().cpu().numpy(), gu.double().cpu().numpy())
+    act = torch.from_numpy(plain.swiglu(pre[:, :I], pre[:, I:])).to(torch.bfloat16).double().numpy()      # the kernel rounds it once too
+    want = res0.double().cpu().numpy() + plain.linear(act, wd.double().cpu().numpy())
+    for turn in range(2):
+        res = res0.clone()
+        kernels.mlp_fused(x, gu, wd, res, stages=stages)
+        torch.cuda.synchronize()
+        got = res.double().cpu().numpy()
+        # float32 sums of bfloat16 products; an activation next to a rounding boundary may round the other way
+        bound = 2e-3 * math.sqrt(I / 64) * float(np.abs(want - res0.double().cpu().numpy()).std()) + 1e-4 + 1e-5 * np.abs(want)
+        err = np.abs(got - want)
+        assert np.isfinite(got).all() and (err <= bound).all(), f"turn {turn}: worst {err.max():.3e} against {bound.min():.3e}"
+    assert kernels.tc_error(DEV) == 0
+    # and the unfused pair of launches agrees (its output is rounded to bfloat16 before the add)
+    two = kernels.linear(kernels.linear_swiglu(x, gu), wd).float() + res0
+    assert float((two - res).abs().max()) <= 2.0 ** -7 * float((res - res0).abs().max()) + 1e-3
