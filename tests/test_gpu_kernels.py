@@ -592,3 +592,27 @@ def test_feed_forward_in_one_launch(T, H, I, stages):
     # and the unfused pair of launches agrees (its output is rounded to bfloat16 before the add)
     two = kernels.linear(kernels.linear_swiglu(x, gu), wd).float() + res0
     assert float((two - res).abs().max()) <= 2.0 ** -7 * float((res - res0).abs().max()) + 1e-3
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_random_weights_are_the_same_numbers_on_the_device_and_on_the_host(dtype):
+    """The device kernel and its numpy twin perform the same IEEE operations in the same order: a tensor made on
+    the GPU (what the benchmark's 3 GB of weights are) equals the tensor that write_random_model puts in a file."""
+    from llaisys_b200 import kernels
+    from llaisys_b200.parts import TensorDecl
+    from llaisys_b200.weights import RandomSource
+    from llaisys_b200.weights.rng import normal, tensor_key
+    decls = {"model.layers.3.mlp.up_proj.weight": TensorDecl((301, 517)), "n.weight": TensorDecl((1000,), init="one_plus_normal", use="vector")}
+    host, dev = RandomSource(decls, 7, dtype), RandomSource(decls, 7, dtype, device=DEV)
+    for name in decls:
+        a, b = host.get(name), dev.get(name)
+        assert b.is_cuda and b.dtype == dtype and torch.equal(a, b.cpu()), name
+    # a piece in the middle of a long tensor, and the far tails of the distribution
+    key = tensor_key(7, "big")
+    out = torch.empty(4096, dtype=torch.float32, device=DEV)
+    kernels.fill_normal(out, key, 0.0, 1.0, first=3_000_000_000)
+    assert np.array_equal(out.cpu().numpy(), normal(key, 4096, first=3_000_000_000))
+    big = torch.empty(1 << 22, dtype=torch.float32, device=DEV)
+    kernels.fill_normal(big, key, 0.0, 1.0)
+    assert abs(float(big.mean())) < 2e-3 and abs(float(big.std()) - 1) < 2e-3 and float(big.abs().max()) > 4.5
+    assert np.array_equal(big[-100000:].cpu().numpy(), normal(key, 100000, first=(1 << 22) - 100000))
