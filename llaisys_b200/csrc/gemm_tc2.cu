@@ -24,6 +24,14 @@
 //               slot in both CTAs and, per tile, hands the accumulator to both epilogues
 //   warps 2-9   epilogue of this CTA's 128 rows: two warps per 32 rows, each with half of the columns
 //
+// INTO (an instantiation of its own): the product is not stored but added to a float32 stream [T, N]
+// (the residual stream: an output projection or a down projection that ends in the residual add of
+// src/models/qwen2/layer.hpp:60-66, 75-81).  The pair's work units are then (tile, K range): where one
+// round of tiles would leave many pairs idle (48 tiles on 74 pairs), the K range is cut so that the
+// units fill the rounds, and every unit adds its partial tile to the stream with one TMA reduction
+// (cp.reduce.async.bulk.tensor ... add) per 32 tokens from a float32 staging buffer.  Nothing is
+// gathered or re-read: the sums meet in the L2.
+//
 // Every wait on an mbarrier is bounded; when a bound is hit the role records an error code in
 // *err and stops, the other roles run into their own bounds, and both CTAs meet at the final
 // cluster barrier, free their tensor memory and return.
@@ -132,6 +140,7 @@ struct Gemm2Args {
     int dual_offset;
     int tok_tiles, n_tiles, n_pairs;
     int* err;
+    int ksplit, chunk_kb;  // INTO: K ranges per tile and k-blocks per range (1 and all of them otherwise)
 };
 
 // The loads issued so far have arrived.  The registers pass through the statement so that no use of them is
@@ -149,14 +158,14 @@ __device__ __forceinline__ void pin16(uint32_t* r) {
                  :: "memory");
 }
 
-template <int BN, int STAGES, bool DUAL>
+template <int BN, int STAGES, bool DUAL, bool INTO = false>
 struct Smem2 {
     static constexpr int ACCS = DUAL ? 2 : 1;
     static constexpr int A_BYTES = BM * BK * 2;
     static constexpr int B_BYTES = (BN / 2) * BK * 2;             // this CTA's half of the token tile
     static constexpr int STAGE_BYTES = ACCS * A_BYTES + B_BYTES;
     static constexpr int STG_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int STG_BYTES = 2 * CHUNK * BM * 2;          // two transposition buffers [32 tokens][128 rows]
+    static constexpr int STG_BYTES = 2 * CHUNK * BM * (INTO ? 4 : 2);   // two transposition buffers [32 tokens][128 rows], bf16 or (INTO) f32
     static constexpr int BAR_OFFSET = STG_OFFSET + STG_BYTES;
     static constexpr int N_BARS = 2 * STAGES + 4;
     static constexpr int TOTAL = BAR_OFFSET + N_BARS * 8 + 16 + 1024;   // + slack to align the base
@@ -165,10 +174,11 @@ struct Smem2 {
     static_assert(ACC_COLS == 256 || ACC_COLS == 512, "an accumulator buffer is a half or the whole of tensor memory");
 };
 
-template <int BN, int STAGES, bool DUAL>
+template <int BN, int STAGES, bool DUAL, bool INTO = false>
 __global__ void __launch_bounds__(THREADS)
-gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, Gemm2Args g) {
-    using S = Smem2<BN, STAGES, DUAL>;
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                const __grid_constant__ CUtensorMap map_out, Gemm2Args g) {
+    using S = Smem2<BN, STAGES, DUAL, INTO>;
     constexpr int ACCS = S::ACCS, ACC_COLS = S::ACC_COLS, NBUF = S::NBUF;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -184,6 +194,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     const bool leader = rank == 0;
     const int pair = blockIdx.x >> 1;
     const int kblocks = (g.K + BK - 1) / BK;
+    // work units: unit u is tile u % n_tiles over the k-blocks [(u / n_tiles) * chunk_kb, ...) (one unit per tile unless INTO)
+    const int n_units = g.n_tiles * g.ksplit;
+    auto unit_kb0 = [&](int u) { return (u / g.n_tiles) * g.chunk_kb; };
+    auto unit_kb1 = [&](int u) { return min(kblocks, (u / g.n_tiles + 1) * g.chunk_kb); };
 
     if (tid == 0) {
         s_abort = 0;
@@ -212,15 +226,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 
     // The weight does not depend on any earlier kernel of the step: the first tile's first STAGES k-blocks of it are
     // requested before the grid dependency resolves, while the predecessor is still running.
-    const int prefetched = min(STAGES, kblocks);
+    const int first_kb0 = unit_kb0(pair);
+    const int prefetched = min(STAGES, unit_kb1(pair) - first_kb0);
     if (warp == 0 && lane == 0) {
         const uint32_t full0 = mapa(bar_full, 0);
-        const int m0 = ((pair / g.tok_tiles) * 2 + (int)rank) * BM;
+        const int m0 = (((pair % g.n_tiles) / g.tok_tiles) * 2 + (int)rank) * BM;
         for (int i = 0; i < prefetched; ++i) {
             const uint32_t dst = base + i * S::STAGE_BYTES, bar = full0 + 8 * i;
             if (leader) mbar_expect_tx(bar_full + 8 * i, 2u * S::STAGE_BYTES);
-            tma_load_2d_pair(dst, &map_w, bar, i * BK, m0, HINT_EVICT_FIRST);
-            if (DUAL) tma_load_2d_pair(dst + S::A_BYTES, &map_w, bar, i * BK, m0 + g.dual_offset, HINT_EVICT_FIRST);
+            tma_load_2d_pair(dst, &map_w, bar, (first_kb0 + i) * BK, m0, HINT_EVICT_FIRST);
+            if (DUAL) tma_load_2d_pair(dst + S::A_BYTES, &map_w, bar, (first_kb0 + i) * BK, m0 + g.dual_offset, HINT_EVICT_FIRST);
         }
     }
     llb_grid_dependency_sync();      // from here on memory written by earlier kernels is touched
@@ -230,15 +245,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             // ---- producer: this CTA's weight rows and its half of the tokens, k-block after k-block, tile after tile
             const uint32_t full0 = mapa(bar_full, 0);
             {   // the activations of the k-blocks whose weight is on its way already
-                const int n0 = (pair % g.tok_tiles) * BN + (int)rank * (BN / 2);
+                const int n0 = ((pair % g.n_tiles) % g.tok_tiles) * BN + (int)rank * (BN / 2);
                 for (int i = 0; i < prefetched; ++i)
-                    tma_load_2d_pair(base + i * S::STAGE_BYTES + ACCS * S::A_BYTES, &map_x, full0 + 8 * i, i * BK, n0, HINT_EVICT_LAST);
+                    tma_load_2d_pair(base + i * S::STAGE_BYTES + ACCS * S::A_BYTES, &map_x, full0 + 8 * i, (first_kb0 + i) * BK, n0, HINT_EVICT_LAST);
             }
             int it = prefetched;
-            for (int t = pair; t < g.n_tiles && !s_abort; t += g.n_pairs) {
+            for (int u = pair; u < n_units && !s_abort; u += g.n_pairs) {
+                const int t = u % g.n_tiles, kb1 = unit_kb1(u);
                 const int m0 = ((t / g.tok_tiles) * 2 + (int)rank) * BM;
                 const int n0 = (t % g.tok_tiles) * BN + (int)rank * (BN / 2);
-                for (int kb = (t == pair ? prefetched : 0); kb < kblocks; ++kb, ++it) {
+                for (int kb = unit_kb0(u) + (u == pair ? prefetched : 0); kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES && !mbar_wait(bar_empty + 8 * s, (uint32_t)(it / STAGES - 1) & 1u, &s_abort)) {
                         if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC2_WAIT_EMPTY); }
@@ -264,15 +280,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             // ---- tensor-core issue for both SMs
             const uint32_t idesc = umma_idesc_pair(BN);
             int it = 0, ti = 0;
-            for (int t = pair; t < g.n_tiles && !s_abort; t += g.n_pairs, ++ti) {
-                const int buf = ti % NBUF;
+            for (int u = pair; u < n_units && !s_abort; u += g.n_pairs, ++ti) {
+                const int buf = ti % NBUF, kb0 = unit_kb0(u), kb1 = unit_kb1(u);
                 if (ti >= NBUF && !mbar_wait(bar_acc_empty + 8 * buf, (uint32_t)(ti / NBUF - 1) & 1u, &s_abort)) {
                     if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC2_WAIT_ACC_EMPTY); }
                     break;
                 }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t acc = tmem + buf * ACC_COLS;
-                for (int kb = 0; kb < kblocks; ++kb, ++it) {
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait(bar_full + 8 * s, (uint32_t)(it / STAGES) & 1u, &s_abort)) {
                         if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC2_WAIT_FULL); }
@@ -283,7 +299,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     const uint64_t ad = umma_desc(a), bd = umma_desc(b), ad2 = umma_desc(a + S::A_BYTES);
 #pragma unroll
                     for (int k = 0; k < BK / UMMA_K; ++k) {
-                        const uint32_t accumulate = (kb > 0 || k > 0) ? 1u : 0u;
+                        const uint32_t accumulate = (kb > kb0 || k > 0) ? 1u : 0u;
                         const uint64_t step = (uint64_t)(k * UMMA_K * 2 >> 4);      // the start address field counts 16 bytes
                         umma_pair(acc, ad + step, bd + step, idesc, accumulate);
                         if (DUAL) umma_pair(acc + BN, ad2 + step, bd + step, idesc, accumulate);
@@ -304,15 +320,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t acc_empty0 = mapa(bar_acc_empty, 0);
         bf16* stg = reinterpret_cast<bf16*>(gen_base + S::STG_OFFSET);
+        float* stgf = reinterpret_cast<float*>(gen_base + S::STG_OFFSET);          // INTO: [2][32 tokens][128 rows] float32
         const int sub = et & 15;
         int ti = 0, chunk_i = 0;
-        for (int t = pair; t < g.n_tiles; t += g.n_pairs, ++ti) {
-            const int buf = ti % NBUF;
+        for (int u = pair; u < n_units; u += g.n_pairs, ++ti) {
+            const int buf = ti % NBUF, t = u % g.n_tiles;
             const int m0 = ((t / g.tok_tiles) * 2 + (int)rank) * BM;
             const int n0 = (t % g.tok_tiles) * BN;
             const int m = m0 + row;
             float bias_v = 0.f;
-            if (g.bias && m < g.rows_out)
+            if (g.bias && m < g.rows_out && u < g.n_tiles)             // the bias goes in with the first K range only
                 bias_v = g.bias_dtype == LLB_F32 ? ((const float*)g.bias)[m] : to_f32(((const bf16*)g.bias)[m]);
             if (!mbar_wait(bar_acc_full + 8 * buf, (uint32_t)(ti / NBUF) & 1u, &s_abort)) {
                 s_epi_abort = 1;
@@ -341,6 +358,24 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     tmem_ld16_nowait(acc + c + CHUNK + h, nxt0);
                     if (DUAL) tmem_ld16_nowait(acc + BN + c + CHUNK + h, nxt1);
                 }
+                if (INTO) {
+                    // this K range's partial sums of 32 tokens x 128 rows, laid out as they lie in the stream, then one
+                    // reduction into the stream.  The other buffer is written right after the barrier below (the next
+                    // chunk), so the reduction that read it last (the one issued after the barrier before) must have
+                    // read it by then: the thread that issues them waits for that before it arrives.
+                    float* sf = stgf + (chunk_i & 1) * (CHUNK * BM);
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) sf[(h + j) * BM + row] = v0[j] + bias_v;
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    if (et == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    asm volatile("bar.sync 1, 256;" ::: "memory");
+                    if (et == 0) {
+                        asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                                     ::"l"(&map_out), "r"(m0), "r"(n0 + c), "r"(smem_u32(sf)) : "memory");
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                    continue;
+                }
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     float v = v0[j];
@@ -367,6 +402,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         }
     }
 
+    if (INTO && tid == 64) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");       // the sums have reached memory
     // Neither CTA leaves while the other may still signal its barriers, read its shared memory or write its
     // tensor memory.
     __syncthreads();
@@ -377,15 +413,17 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     if (warp == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
 }
 
-template <int BN, int STAGES, bool DUAL>
-int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Gemm2Args& g, cudaStream_t stream) {
-    auto k = gemm_tc2_kernel<BN, STAGES, DUAL>;
-    constexpr int smem = Smem2<BN, STAGES, DUAL>::TOTAL;
-    static bool configured = false;
-    if (!configured) {
+template <int BN, int STAGES, bool DUAL, bool INTO = false>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, const Gemm2Args& g, cudaStream_t stream) {
+    auto k = gemm_tc2_kernel<BN, STAGES, DUAL, INTO>;
+    constexpr int smem = Smem2<BN, STAGES, DUAL, INTO>::TOTAL;
+    static bool configured[64] = {};         // function attributes belong to a device's copy of the kernel
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return (int)cudaErrorInvalidDevice;
+    if (!configured[dev]) {
         cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return -2000 - (int)e;
-        configured = true;
+        configured[dev] = true;
     }
     llb_prefer_max_shared((const void*)k);
     cudaLaunchConfig_t cfg = {};
@@ -407,7 +445,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const Gemm2Args& g, cud
     ++n_attr;
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    cudaLaunchKernelEx(&cfg, k, mw, mx, g);
+    cudaLaunchKernelEx(&cfg, k, mw, mx, mo, g);
     return llb_status();
 }
 
@@ -434,10 +472,62 @@ LLB_API int llb_gemm_tc2(const void* X, const void* W, const void* bias, int bia
     g.n_tiles = (int)tiles;
     g.n_pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
     g.err = err;
+    g.ksplit = 1;
+    g.chunk_kb = (K + BK - 1) / BK;
     CUtensorMap mw, mx;
     int rc = llb_tma::bf16_map_64(W, N, K, K, BM, &mw);
     if (rc) return rc;
     rc = llb_tma::bf16_map_64(X, T, K, ldx, bn / 2, &mx);
     if (rc) return rc;
-    return dual ? launch<256, 4, true>(mw, mx, g, stream) : launch<256, 6, false>(mw, mx, g, stream);
+    return dual ? launch<256, 4, true>(mw, mx, mw, g, stream) : launch<256, 6, false>(mw, mx, mw, g, stream);
+}
+
+// K ranges per tile for llb_gemm_tc2_into: the count (1 to 4) that minimises rounds of units times the length of a
+// unit, a unit costing its k-blocks plus about eight k-blocks' time of epilogue.
+LLB_API int llb_gemm_tc2_into_ksplit(int T, int N, int K, int max_pairs) {
+    const int kblocks = (K + BK - 1) / BK;
+    const long long tiles = (long long)((N + 2 * BM - 1) / (2 * BM)) * ((T + 255) / 256);
+    int best = 1;
+    long long best_cost = -1;
+    for (int ks = 1; ks <= 4 && ks <= kblocks; ++ks) {
+        const int chunk = (kblocks + ks - 1) / ks;
+        if ((ks - 1) * chunk >= kblocks) continue;                       // an empty range
+        const long long rounds = (tiles * ks + max_pairs - 1) / max_pairs, cost = rounds * (chunk + 8);
+        if (best_cost < 0 || cost < best_cost) { best = ks; best_cost = cost; }
+    }
+    return best;
+}
+
+// stream[T, N] (float32, row stride lds, 16-byte aligned, lds a multiple of 4) += X W^T + bias, for many tokens: the
+// same paired kernel, its partial tiles added to the stream by TMA reductions.  ksplit: K ranges per tile (0 chooses).
+// The sums of a tile's K ranges meet in the L2 in no fixed order: reproducible up to float32 rounding of that sum.
+LLB_API int llb_gemm_tc2_into(const void* X, const void* W, const void* bias, int bias_dtype, float* stream_, int T, int N, int K,
+                              int ldx, int lds, int ksplit, int max_pairs, int* err, cudaStream_t stream) {
+    if (T == 0 || N == 0) return 0;
+    if (K <= 0 || K % 8 || ldx % 8 || lds % 4 || max_pairs < 1 || !stream_ ||
+        (((uintptr_t)X | (uintptr_t)W | (uintptr_t)stream_) & 15))
+        return (int)cudaErrorInvalidValue;
+    const int bn = 256, kblocks = (K + BK - 1) / BK;
+    if (ksplit <= 0) ksplit = llb_gemm_tc2_into_ksplit(T, N, K, max_pairs);
+    if (ksplit > kblocks) ksplit = kblocks;
+    Gemm2Args g;
+    g.bias = bias; g.bias_dtype = bias_dtype; g.Y = nullptr;
+    g.T = T; g.K = K; g.ldy = lds; g.rows_out = N; g.dual_offset = 0;
+    g.tok_tiles = (T + bn - 1) / bn;
+    const long long tiles = (long long)((N + 2 * BM - 1) / (2 * BM)) * g.tok_tiles;
+    if (tiles * ksplit > (1 << 30)) return (int)cudaErrorInvalidValue;
+    g.n_tiles = (int)tiles;
+    g.chunk_kb = (kblocks + ksplit - 1) / ksplit;
+    g.ksplit = (kblocks + g.chunk_kb - 1) / g.chunk_kb;                  // no range is empty
+    const long long units = tiles * g.ksplit;
+    g.n_pairs = (int)(units < max_pairs ? units : max_pairs);
+    g.err = err;
+    CUtensorMap mw, mx, mo;
+    int rc = llb_tma::bf16_map_64(W, N, K, K, BM, &mw);
+    if (rc) return rc;
+    rc = llb_tma::bf16_map_64(X, T, K, ldx, bn / 2, &mx);
+    if (rc) return rc;
+    rc = llb_tma::f32_map_plain(stream_, T, N, lds, BM, CHUNK, &mo);
+    if (rc) return rc;
+    return launch<256, 6, false, true>(mw, mx, mo, g, stream);
 }

@@ -351,6 +351,26 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return out
 
 
+def linear_into_ok(x: torch.Tensor, weight: torch.Tensor, bias, stream: torch.Tensor) -> bool:
+    """True when linear_into() takes these operands: bfloat16 on the tensor cores, more than 256 tokens (the paired-SM
+    kernel), a float32 stream with 16-byte aligned rows."""
+    return (_tc_ok(x, weight, bias) and x.shape[0] > 256 and stream.dtype == torch.float32 and stream.stride(1) == 1
+            and stream.stride(0) % 4 == 0 and stream.data_ptr() % 16 == 0 and stream.shape == (x.shape[0], weight.shape[0]))
+
+
+def linear_into(x: torch.Tensor, weight: torch.Tensor, bias, stream: torch.Tensor, ksplit: int = 0) -> None:
+    """stream [T, N] (float32) += x weight^T + bias in place (csrc/gemm_tc2.cu, INTO): a projection that ends in the
+    residual add.  ksplit: K ranges per tile (0: chosen so that the units fill the rounds of SM pairs)."""
+    _need_cuda(x, weight, bias, stream)
+    T, K = x.shape
+    N = weight.shape[0]
+    err = _tc_resources(x.device)[2]
+    f = _fn(load_module("gemm_tc2.cu"), "llb_gemm_tc2_into",
+            [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(f(_ptr(x), _ptr(weight), _ptr(bias), _dt(bias) if bias is not None else 0, _ptr(stream), T, N, K, x.stride(0),
+             stream.stride(0), ksplit, _sm_count(x.device) // 2, _ptr(err), _stream()), "linear into the residual stream (tensor cores, paired SMs)")
+
+
 def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, plan=None) -> torch.Tensor:
     """up(x) * silu(gate(x)) for the fused [2I, K] matrix (gate rows first): [M, I].  On the
     tensor cores the two products share one kernel and the [M, 2I] intermediate is never written."""

@@ -102,6 +102,18 @@ class GQAttention(Mixer):
         self.b_o = tensors["o_proj.bias"].contiguous() if self.out_bias else None
 
     def forward(self, x, ctx, call):
+        return kernels.linear(self._attend(x, ctx, call), self.w_o, self.b_o)
+
+    def forward_into(self, x, ctx, call, residual):
+        # many tokens (prefill): the output projection's tiles are added to the residual stream as they are finished
+        if not (x.shape[0] > 256 and x.dtype == torch.bfloat16 and self.w_o.dtype == torch.bfloat16
+                and kernels.linear_into_ok(x.new_empty((x.shape[0], self.nh * self.dh)), self.w_o, self.b_o, residual)):
+            return False
+        kernels.linear_into(self._attend(x, ctx, call), self.w_o, self.b_o, residual)
+        return True
+
+    def _attend(self, x, ctx, call):
+        """Projections, position encoding, cache append and attention: [T, nh * dh], before the output projection."""
         kv = ctx.kv(call)
         qkv = kernels.linear(x, self.w_qkv, self.b_qkv)
         append = None
@@ -142,4 +154,4 @@ class GQAttention(Mixer):
                                             all_from_cache=not kv.writable)
             if append:
                 kernels.rope_append(qkv, self.nh, self.nkvh, self.dh, tok_pos=ctx.tok_pos, append=append, err=ctx.err)
-        return kernels.linear(out, self.w_o, self.b_o)
+        return out

@@ -148,6 +148,12 @@ class Mixer(Part):
         its state rows [n_slots, state_size]."""
         raise NotImplementedError
 
+    def forward_into(self, x: torch.Tensor, ctx, call: int, residual: torch.Tensor) -> bool:
+        """A mixer whose last kernel can add its result to the float32 residual stream [T, H] itself does
+        so and returns True; the block then has no delta to hand on.  False (the default): nothing was
+        done, call forward()."""
+        return False
+
 
 class FeedForward(Part):
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:

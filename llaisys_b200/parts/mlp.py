@@ -35,7 +35,15 @@ class SwiGLUMLP(FeedForward):
 
     def forward_into(self, x, ctx, residual):
         # a few tokens (decode): the three matrices stream through one launch that ends in the residual add
-        if not kernels.mlp_fused_ok(x, self.gate_up, self.down, residual):
-            return False
-        kernels.mlp_fused(x, self.gate_up, self.down, residual)
-        return True
+        if kernels.mlp_fused_ok(x, self.gate_up, self.down, residual):
+            kernels.mlp_fused(x, self.gate_up, self.down, residual)
+            return True
+        # many tokens (prefill): the down projection's tiles are added to the stream as they are finished
+        if x.dtype == torch.bfloat16 and self.gate_up.dtype == torch.bfloat16 and x.shape[0] > 256:
+            act = kernels.linear_swiglu(x, self.gate_up)
+            if kernels.linear_into_ok(act, self.down, None, residual):
+                kernels.linear_into(act, self.down, None, residual)
+                return True
+            kernels.residual_add(residual, kernels.linear(act, self.down))
+            return True
+        return False

@@ -616,3 +616,24 @@ def test_random_weights_are_the_same_numbers_on_the_device_and_on_the_host(dtype
     kernels.fill_normal(big, key, 0.0, 1.0)
     assert abs(float(big.mean())) < 2e-3 and abs(float(big.std()) - 1) < 2e-3 and float(big.abs().max()) > 4.5
     assert np.array_equal(big[-100000:].cpu().numpy(), normal(key, 100000, first=(1 << 22) - 100000))
+
+
+@pytest.mark.parametrize("T,N,K,ksplit", [(2048, 1536, 1536, 0), (2048, 1536, 8960, 0), (300, 520, 1096, 3), (700, 200, 72, 1),
+                                          (257, 1536, 8960, 4), (1000, 3584, 512, 2)])
+def test_linear_into_the_residual_stream_on_paired_sms(T, N, K, ksplit):
+    """A projection of many tokens that ends in the residual add: K ranges of a tile as separate units, their partial
+    tiles added to the float32 stream by TMA reductions."""
+    from llaisys_b200 import kernels
+    x, w, b = _tc_case(T, N, K, T + N + K, bias=torch.bfloat16)
+    rng = np.random.default_rng(3)
+    s0 = torch.from_numpy(rng.normal(size=(T, N))).float().to(DEV)
+    prod = plain.linear(x.double().cpu().numpy(), w.double().cpu().numpy())
+    for bias in (b, None):
+        stream = s0.clone()
+        assert kernels.linear_into_ok(x, w, bias, stream)
+        for turn in range(2):                                    # adding twice adds twice
+            kernels.linear_into(x, w, bias, stream, ksplit=ksplit)
+        torch.cuda.synchronize()
+        want = s0.double().cpu().numpy() + 2 * (prod + (b.double().cpu().numpy() if bias is not None else 0.0))
+        _tc_check(stream, want, 4 * K)
+    assert kernels.tc_error(DEV) == 0
