@@ -483,17 +483,20 @@ LLB_API int llb_gemm_tc2(const void* X, const void* W, const void* bias, int bia
 }
 
 // K ranges per tile for llb_gemm_tc2_into: the count (1 to 4) that minimises rounds of units times the length of a
-// unit, a unit costing its k-blocks plus about eight k-blocks' time of epilogue.
+// unit.  Fitted to measurements at the 1.5B and 7B shapes (2,048 to 8,192 tokens): a k-block of a 256 x 256 tile takes a
+// pair 0.37 us, a unit's epilogue (tensor memory -> float32 staging -> reduction) as long as eighteen k-blocks; a cut
+// has to win five per cent to be taken.
 LLB_API int llb_gemm_tc2_into_ksplit(int T, int N, int K, int max_pairs) {
     const int kblocks = (K + BK - 1) / BK;
     const long long tiles = (long long)((N + 2 * BM - 1) / (2 * BM)) * ((T + 255) / 256);
+    const long long whole = ((tiles + max_pairs - 1) / max_pairs) * (kblocks + 18);
     int best = 1;
-    long long best_cost = -1;
-    for (int ks = 1; ks <= 4 && ks <= kblocks; ++ks) {
+    long long best_cost = whole;
+    for (int ks = 2; ks <= 4 && ks <= kblocks; ++ks) {
         const int chunk = (kblocks + ks - 1) / ks;
         if ((ks - 1) * chunk >= kblocks) continue;                       // an empty range
-        const long long rounds = (tiles * ks + max_pairs - 1) / max_pairs, cost = rounds * (chunk + 8);
-        if (best_cost < 0 || cost < best_cost) { best = ks; best_cost = cost; }
+        const long long rounds = (tiles * ks + max_pairs - 1) / max_pairs, cost = rounds * (chunk + 18);
+        if (cost * 100 < whole * 95 && cost < best_cost) { best = ks; best_cost = cost; }
     }
     return best;
 }

@@ -67,3 +67,18 @@ def test_launch_plans_are_launchable(T, rows, K, dual):
         assert tiles * splits <= 2 * 148                             # all resident at once, at most two per SM
     if splits == 16:
         assert bn == 64 or T <= 4
+
+
+@pytest.mark.parametrize("T,N,K,want", [(2048, 1536, 8960, 3), (2048, 1536, 1536, 1), (4096, 1536, 8960, 3), (8192, 1536, 8960, 1),
+                                        (2048, 3584, 18944, 3), (4096, 3584, 18944, 2), (300, 200, 72, 1), (100000, 5120, 27648, 1)])
+def test_k_ranges_of_the_prefill_projection_that_ends_in_the_residual_add(T, N, K, want):
+    """Where one round of 256 x 256 tiles would leave SM pairs idle (48 tiles on 74 pairs), the K range is cut so
+    that the units fill the rounds; where the tiles fill many rounds anyway, it is not (the plan is host code)."""
+    import ctypes
+    from llaisys_b200.csrc.build import load_module
+    f = load_module("gemm_tc2.cu").llb_gemm_tc2_into_ksplit
+    f.restype, f.argtypes = ctypes.c_int, [ctypes.c_int] * 4
+    ks = f(T, N, K, 74)
+    assert ks == want
+    kblocks = math.ceil(K / 64)
+    assert 1 <= ks <= 4 and (ks - 1) * math.ceil(kblocks / ks) < kblocks          # no K range is empty
