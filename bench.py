@@ -490,6 +490,9 @@ def main() -> int:
     ap.add_argument("--products", action="store_true",
                     help="time a layer's four matrix products alone at --tokens tokens, with each kernel that takes them")
     ap.add_argument("--tokens", type=int, default=PREFILL_TOKENS, help="tokens for --products")
+    ap.add_argument("--prompt-len", type=int, default=None,
+                    help="for measurements beside the reported one: tokens every sequence holds before decoding, and tokens of "
+                         "the timed prefill step (default 2,048; the cache is sized for twice as many per sequence)")
     ap.add_argument("--timeline", choices=["decode", "prefill"], default=None,
                     help="print the per-kernel timeline of a step (torch.profiler, no ncu) instead of measuring")
     args = ap.parse_args()
@@ -503,6 +506,9 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.prompt_len:
+        g = globals()
+        g["PROMPT_LEN"], g["CONTEXT"], g["PREFILL_TOKENS"] = args.prompt_len, 2 * args.prompt_len, args.prompt_len
 
     import numpy as np
     import torch
@@ -618,7 +624,7 @@ def main() -> int:
                "h2d_bytes_per_step": 4 * meta_ints, "d2h_bytes_per_step": 4 * args.batch}
 
     out = {
-        "metric": f"decode tok/s @ batch {args.batch} ({shape_name.split(' shape')[0]} shape, bf16, 2048-token prompts, context 4096)",
+        "metric": f"decode tok/s @ batch {args.batch} ({shape_name.split(' shape')[0]} shape, bf16, {PROMPT_LEN}-token prompts, context {CONTEXT})",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random weights N(0,0.02), seeded uniform-random token ids",
