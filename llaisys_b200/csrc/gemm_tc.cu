@@ -163,9 +163,15 @@ struct Smem {
     static constexpr int TOTAL = RECV_OFFSET + RECV_BYTES + 1024;                  // + slack to align the base
 };
 
-template <int BN, int STAGES, bool DUAL>
+// INTO (instantiations of their own, so that the others' epilogues do not grow): the product is not stored but added
+// to a float32 stream [T, N] (the residual stream: a projection that ends in the residual add).  The K range is
+// divided over gridDim.z blocks that need not be a cluster; each stages its partial tile in the idle ring as the rows
+// lie in the stream ([token][128 rows]) and hands it to the copy engine as one reduction
+// (cp.reduce.async.bulk.tensor ... add), so the sums meet in the L2 and no block waits for another.
+template <int BN, int STAGES, bool DUAL, bool INTO = false>
 __global__ void __launch_bounds__(THREADS)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, GemmArgs g) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+               const __grid_constant__ CUtensorMap map_out, GemmArgs g) {
     using S = Smem<BN, STAGES, DUAL>;
     constexpr int ACCS = DUAL ? 2 : 1;
     constexpr int TMEM_COLS = (ACCS * BN) <= 32 ? 32 : (ACCS * BN) <= 64 ? 64 : (ACCS * BN) <= 128 ? 128 : (ACCS * BN) <= 256 ? 256 : 512;
@@ -319,7 +325,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // branch's cluster barrier would be waited for there)
     auto finish = [&](float acc0, float acc1, int j, float bias_v) { finish_at(acc0, acc1, j, m, bias_v); };
 
-    if (!aborted) {
+    if (INTO) {
+        if (!aborted) {
+            float* stg = reinterpret_cast<float*>(gen_base);              // [BN tokens][128 rows] float32 in the idle ring
+            const float bias_v = (split == 0 && row_ok) ? bias_of(m) : 0.f;      // the bias goes in with the first K range
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                float v0[16];
+                tmem_ld16(lane_addr + c, v0);
+#pragma unroll
+                for (int j = 0; j < 16; ++j) stg[(c + j) * BM + tid] = v0[j] + bias_v;
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncthreads();
+            if (tid == 0) {
+                // what lies beyond the step's tokens or the matrix's rows is clipped by the copy engine
+                asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
+                             ::"l"(&map_out), "r"(m0), "r"(n0), "r"(smem_u32(stg)) : "memory");
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");         // before the shared memory is given up
+            }
+        }
+    } else if (!aborted) {
         if (g.splits == 1 && g.y_dtype == LLB_BF16 && m0 + BM <= (DUAL ? g.dual_offset : g.N) &&
             g.ldy % 8 == 0 && ((uintptr_t)g.Y & 15) == 0) {
             // Whole tile of bfloat16 outputs: a thread holds one weight row, i.e. one output COLUMN, so storing
@@ -445,7 +472,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
         }
     }
-    if (aborted && g.splits > 1 && !push && tid == 0) {
+    if (!INTO && aborted && g.splits > 1 && !push && tid == 0) {
         // A block that gave up still arrives at its tile's counter, so that the counter is back at zero when the
         // launch is over whatever happened (the tile's output is not valid; the error word says so).
         const int tile = blockIdx.y * gridDim.x + blockIdx.x;
@@ -502,9 +529,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 }
 
 // ------------------------------------------------------------------ host side
-template <int BN, int STAGES, bool DUAL>
-int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& g, dim3 grid, cudaStream_t stream) {
-    auto k = gemm_tc_kernel<BN, STAGES, DUAL>;
+template <int BN, int STAGES, bool DUAL, bool INTO = false>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& g, dim3 grid, cudaStream_t stream,
+           const CUtensorMap* mo = nullptr) {
+    auto k = gemm_tc_kernel<BN, STAGES, DUAL, INTO>;
     constexpr int smem = Smem<BN, STAGES, DUAL>::TOTAL;
     // function attributes belong to a device's copy of the kernel: set them once on every device that launches it
     static bool configured[64] = {};
@@ -538,7 +566,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& g, dim3
     }
     cfg.attrs = attr;
     cfg.numAttrs = n_attr;
-    cudaLaunchKernelEx(&cfg, k, mw, mx, g);
+    cudaLaunchKernelEx(&cfg, k, mw, mx, mo ? *mo : mw, g);
     return llb_status();
 }
 
@@ -599,6 +627,41 @@ LLB_API int llb_gemm_tc(const void* X, const void* W, const void* bias, int bias
         default: return (int)cudaErrorInvalidValue;
     }
 #undef LLB_TC
+}
+
+// stream[T, N] (float32, row stride lds a multiple of 4, 16-byte aligned) += X W^T + bias for up to 256 tokens: the K
+// range divided over `splits` blocks (any number up to the k-blocks), every block adding its partial tile to the
+// stream by a TMA reduction.  bn: tokens per tile (16, 32, 64, 128, 256).  The sums meet in the L2 in no fixed order.
+LLB_API int llb_gemm_tc_into(const void* X, const void* W, const void* bias, int bias_dtype, float* stream_, int T, int N, int K,
+                             int ldx, int lds, int bn, int splits, int* err, cudaStream_t stream) {
+    if (T <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 || ldx % 8 || lds % 4 || !stream_ || (((uintptr_t)X | (uintptr_t)W | (uintptr_t)stream_) & 15))
+        return (int)cudaErrorInvalidValue;
+    const int kblocks = (K + BK - 1) / BK;
+    if (splits < 1) splits = 1;
+    if (splits > kblocks) splits = kblocks;
+    {   // no split may be empty
+        int chunk = (kblocks + splits - 1) / splits;
+        splits = (kblocks + chunk - 1) / chunk;
+    }
+    dim3 grid((N + BM - 1) / BM, (T + bn - 1) / bn, splits);
+    if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
+    CUtensorMap mw, mx, mo;
+    int rc = llb_tma::bf16_map_64(W, N, K, K, BM, &mw);
+    if (rc) return rc;
+    rc = llb_tma::bf16_map_64(X, T, K, ldx, bn, &mx);
+    if (rc) return rc;
+    rc = llb_tma::f32_map_plain(stream_, T, N, lds, BM, bn, &mo);
+    if (rc) return rc;
+    GemmArgs g{bias, bias_dtype, nullptr, LLB_F32, T, N, K, lds, 0, splits, 0, nullptr, nullptr, err};
+    switch (bn) {
+        case 16: return launch<16, 5, false, true>(mw, mx, g, grid, stream, &mo);
+        case 32: return launch<32, 4, false, true>(mw, mx, g, grid, stream, &mo);
+        case 64: return launch<64, 4, false, true>(mw, mx, g, grid, stream, &mo);
+        case 128: return launch<128, 6, false, true>(mw, mx, g, grid, stream, &mo);
+        case 256: return launch<256, 4, false, true>(mw, mx, g, grid, stream, &mo);
+        default: return (int)cudaErrorInvalidValue;
+    }
 }
 
 // ------------------------------------------------------------------ allocation-free entry point

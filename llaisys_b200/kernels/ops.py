@@ -352,19 +352,38 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
 
 
 def linear_into_ok(x: torch.Tensor, weight: torch.Tensor, bias, stream: torch.Tensor) -> bool:
-    """True when linear_into() takes these operands: bfloat16 on the tensor cores, more than 256 tokens (the paired-SM
-    kernel), a float32 stream with 16-byte aligned rows."""
-    return (_tc_ok(x, weight, bias) and x.shape[0] > 256 and stream.dtype == torch.float32 and stream.stride(1) == 1
+    """True when linear_into() takes these operands: bfloat16 on the tensor cores, a float32 stream with 16-byte
+    aligned rows."""
+    return (_tc_ok(x, weight, bias) and x.shape[0] > 0 and stream.dtype == torch.float32 and stream.stride(1) == 1
             and stream.stride(0) % 4 == 0 and stream.data_ptr() % 16 == 0 and stream.shape == (x.shape[0], weight.shape[0]))
 
 
+def into_plan(T: int, N: int, K: int, sms: int):
+    """(tokens per tile, K ranges) of linear_into() for up to 256 tokens: the smallest tile that holds the tokens, and as
+    many K ranges as keep every block at two k-blocks or more and all blocks resident at once (two per SM while a
+    block's ring stays under half of an SM's shared memory)."""
+    bn = 16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else 128 if T <= 128 else 256
+    tiles = -(-N // 128) * -(-T // bn)
+    kblocks = -(-K // 64)
+    room = 2 * sms if bn <= 64 else sms
+    return bn, max(1, min(kblocks // 2, room // tiles))
+
+
 def linear_into(x: torch.Tensor, weight: torch.Tensor, bias, stream: torch.Tensor, ksplit: int = 0) -> None:
-    """stream [T, N] (float32) += x weight^T + bias in place (csrc/gemm_tc2.cu, INTO): a projection that ends in the
-    residual add.  ksplit: K ranges per tile (0: chosen so that the units fill the rounds of SM pairs)."""
+    """stream [T, N] (float32) += x weight^T + bias in place: a projection that ends in the residual add.  Up to 256
+    tokens: csrc/gemm_tc.cu (INTO), the K range divided over blocks that each add their partial tile by a TMA
+    reduction; more: the paired-SM kernel (csrc/gemm_tc2.cu, INTO).  ksplit: K ranges per tile (0: chosen)."""
     _need_cuda(x, weight, bias, stream)
     T, K = x.shape
     N = weight.shape[0]
     err = _tc_resources(x.device)[2]
+    if T <= 256:
+        bn, splits = into_plan(T, N, K, _sm_count(x.device))
+        f = _fn(load_module("gemm_tc.cu"), "llb_gemm_tc_into",
+                [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+        _check(f(_ptr(x), _ptr(weight), _ptr(bias), _dt(bias) if bias is not None else 0, _ptr(stream), T, N, K, x.stride(0),
+                 stream.stride(0), bn, ksplit or splits, _ptr(err), _stream()), "linear into the residual stream (tensor cores)")
+        return
     f = _fn(load_module("gemm_tc2.cu"), "llb_gemm_tc2_into",
             [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(f(_ptr(x), _ptr(weight), _ptr(bias), _dt(bias) if bias is not None else 0, _ptr(stream), T, N, K, x.stride(0),
@@ -376,6 +395,16 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, plan=None) -> torch.Te
     tensor cores the two products share one kernel and the [M, 2I] intermediate is never written."""
     _need_cuda(x, gate_up)
     I = gate_up.shape[0] // 2
+    if (plan is None and FUSED_MLP and _tc_ok(x, gate_up, None) and 32 < x.shape[0] <= 64 and I % 8 == 0):
+        # 33 to 64 tokens: a slice's gate rows and up rows in one tile, I / 64 blocks with one accumulator each
+        # (csrc/mlp_tc.cu, its gate/up half alone)
+        out = torch.empty((x.shape[0], I), dtype=x.dtype, device=x.device)
+        err = _tc_resources(x.device)[2]
+        f = _fn(load_module("mlp_tc.cu", _MLP_DEFINES), "llb_mlp_gate_up",
+                [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+        _check(f(_ptr(x), x.stride(0), _ptr(gate_up), _ptr(out), out.stride(0), x.shape[0], x.shape[1], I, _sm_count(x.device),
+                 _MLP_STAGES, _ptr(err), _stream()), "gate/up + SwiGLU (slices, tensor cores)")
+        return out
     if _tc_ok(x, gate_up, None) and x.shape[0] > 0:
         out = torch.empty((x.shape[0], I), dtype=x.dtype, device=x.device)
         _gemm_tc(x, gate_up, None, out, dual_offset=I, plan=plan)

@@ -105,8 +105,8 @@ class GQAttention(Mixer):
         return kernels.linear(self._attend(x, ctx, call), self.w_o, self.b_o)
 
     def forward_into(self, x, ctx, call, residual):
-        # many tokens (prefill): the output projection's tiles are added to the residual stream as they are finished
-        if not (x.shape[0] > 256 and x.dtype == torch.bfloat16 and self.w_o.dtype == torch.bfloat16
+        # the output projection's tiles are added to the residual stream as they are finished
+        if not (x.dtype == torch.bfloat16 and self.w_o.dtype == torch.bfloat16
                 and kernels.linear_into_ok(x.new_empty((x.shape[0], self.nh * self.dh)), self.w_o, self.b_o, residual)):
             return False
         kernels.linear_into(self._attend(x, ctx, call), self.w_o, self.b_o, residual)

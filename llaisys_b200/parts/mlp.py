@@ -38,8 +38,8 @@ class SwiGLUMLP(FeedForward):
         if kernels.mlp_fused_ok(x, self.gate_up, self.down, residual):
             kernels.mlp_fused(x, self.gate_up, self.down, residual)
             return True
-        # many tokens (prefill): the down projection's tiles are added to the stream as they are finished
-        if x.dtype == torch.bfloat16 and self.gate_up.dtype == torch.bfloat16 and x.shape[0] > 256:
+        # more tokens: the down projection's tiles are added to the stream as they are finished
+        if x.dtype == torch.bfloat16 and self.gate_up.dtype == torch.bfloat16 and x.shape[0] > 0:
             act = kernels.linear_swiglu(x, self.gate_up)
             if kernels.linear_into_ok(act, self.down, None, residual):
                 kernels.linear_into(act, self.down, None, residual)

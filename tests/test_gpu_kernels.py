@@ -619,10 +619,13 @@ def test_random_weights_are_the_same_numbers_on_the_device_and_on_the_host(dtype
 
 
 @pytest.mark.parametrize("T,N,K,ksplit", [(2048, 1536, 1536, 0), (2048, 1536, 8960, 0), (300, 520, 1096, 3), (700, 200, 72, 1),
-                                          (257, 1536, 8960, 4), (1000, 3584, 512, 2)])
+                                          (257, 1536, 8960, 4), (1000, 3584, 512, 2),
+                                          (8, 1536, 1536, 0), (1, 1536, 8960, 0), (64, 1536, 8960, 0), (64, 1536, 1536, 5), (20, 144, 200, 0),
+                                          (100, 300, 1096, 7), (200, 520, 72, 0), (33, 3584, 3584, 1)])
 def test_linear_into_the_residual_stream_on_paired_sms(T, N, K, ksplit):
-    """A projection of many tokens that ends in the residual add: K ranges of a tile as separate units, their partial
-    tiles added to the float32 stream by TMA reductions."""
+    """A projection that ends in the residual add: K ranges of a tile as separate units (of the paired-SM kernel above
+    256 tokens, blocks of the one-CTA kernel up to there), their partial tiles added to the float32 stream by TMA
+    reductions."""
     from llaisys_b200 import kernels
     x, w, b = _tc_case(T, N, K, T + N + K, bias=torch.bfloat16)
     rng = np.random.default_rng(3)
@@ -636,4 +639,22 @@ def test_linear_into_the_residual_stream_on_paired_sms(T, N, K, ksplit):
         torch.cuda.synchronize()
         want = s0.double().cpu().numpy() + 2 * (prod + (b.double().cpu().numpy() if bias is not None else 0.0))
         _tc_check(stream, want, 4 * K)
+    assert kernels.tc_error(DEV) == 0
+
+
+@pytest.mark.parametrize("T,I,K", [(64, 8960, 1536), (33, 8960, 1536), (50, 232, 144), (40, 18944, 3584), (64, 136, 72)])
+def test_gate_up_in_slices_for_33_to_64_tokens(T, I, K):
+    """linear_swiglu() between 33 and 64 tokens runs the slice kernel's gate/up half: against the plain formula, and
+    against the two-accumulator product that serves the other token counts."""
+    from llaisys_b200 import kernels
+    x, w, _ = _tc_case(T, 2 * I, K, T + I)
+    w = (w.float() * 4).to(torch.bfloat16)
+    gu = plain.linear(x.double().cpu().numpy(), w.double().cpu().numpy())
+    want = plain.swiglu(gu[:, :I], gu[:, I:])
+    for turn in range(2):
+        got = kernels.linear_swiglu(x, w)
+        assert got.shape == (T, I)
+        _close(got, want, torch.bfloat16, atol=5e-3)
+    other = kernels.linear_swiglu(x, w, plan=(64, 1))
+    assert float((other.float() - got.float()).abs().max()) <= 2.0 ** -7 * float(got.float().abs().max()) + 1e-3
     assert kernels.tc_error(DEV) == 0
