@@ -133,8 +133,6 @@ struct MlpArgs {
     int n_mt;              // ceil(H / 128): output row tiles of the down projection
     int tmem_cols;         // power of two >= 2 BN + n_mt BN
     int* err;
-    bf16* act_out;         // ACT_ONLY instantiations: [T, ldact] receives up * silu(gate); nothing else is computed
-    int ldact;
 };
 
 template <int BN, int STAGES>
@@ -151,12 +149,7 @@ struct Smem {
     static constexpr int TOTAL = BAR_OFFSET + N_BARS * 8 + 16 + 1024;
 };
 
-// ACT_ONLY: the first half alone, for steps of more tokens than the whole kernel serves (its blocks' partial sums of
-// the down projection grow with the tokens): act[T, I] = up(x) * silu(gate(x)) is written to memory.  What it shares
-// with the whole kernel is the point of it: one tile holds a slice's gate rows and up rows, so I / 64 blocks stream
-// the matrix with one accumulator each and no reduction, where a tile of 128 gate rows plus a tile of 128 up rows
-// makes half as many blocks.
-template <int BN, int STAGES, bool ACT_ONLY = false>
+template <int BN, int STAGES>
 __global__ void __launch_bounds__(THREADS)
 mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_constant__ CUtensorMap map_up,
                  const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_down,
@@ -176,7 +169,7 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
     const int KB1 = (g.H + BK - 1) / BK;
     // this block's slices: blockIdx.x, blockIdx.x + gridDim.x, ...
     const int my_slices = ((int)blockIdx.x < g.n_slices) ? (g.n_slices - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-    const int per_slice = KB1 + (ACT_ONLY ? 0 : g.n_mt);  // ring stages a slice takes
+    const int per_slice = KB1 + g.n_mt;                   // ring stages a slice takes
 
     if (tid == 0) {
         s_abort = 0;
@@ -265,10 +258,6 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
             for (int sl = 0; sl < my_slices && ok; ++sl) {
                 const int b = sl & 1;
                 const uint32_t d1 = tmem + (uint32_t)(b * BN);
-                if (ACT_ONLY && sl >= 2 && !mbar_wait(bar_act + 8 * b, (uint32_t)((sl - 2) >> 1) & 1u, &s_abort)) {
-                    if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_MLP_ACT); }      // (the epilogue has taken D1[b] out)
-                    break;
-                }
                 // gate/up: D1[b] = [gate rows; up rows] x X^T over all of K = H
                 for (int j = 0; j < KB1; ++j, ++n) {
                     const int s = n % STAGES;
@@ -286,7 +275,6 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
                 }
                 if (!ok) break;
                 umma_commit(bar_d1 + 8 * b);
-                if (ACT_ONLY) continue;
                 // down: D2[m] += Wd[m tile, slice] x act^T, once the epilogue has put act[b] into shared memory
                 if (!mbar_wait(bar_act + 8 * b, (uint32_t)(sl >> 1) & 1u, &s_abort)) {
                     if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_MLP_ACT); }
@@ -347,15 +335,10 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
                 // act[n][col] = up * gate / (1 + exp(-gate)), bfloat16, into the swizzled K-major tile: row n (token) is
                 // 128 bytes; its 16-byte piece col / 8 sits at piece (col / 8) ^ (n % 8); groups of 8 rows are 1024 bytes
                 uint8_t* act = gen_base + S::ACT_OFFSET + b * S::ACT_BYTES;
-                const int icol = ((int)blockIdx.x + sl * (int)gridDim.x) * SLICE + col;       // this thread's column of I
 #pragma unroll
                 for (int n = 0; n < BN; ++n) {
                     const float gate = v[n], up = exch[col * BN + n];
                     const float a = up * __fdividef(gate, 1.0f + __expf(-gate));
-                    if (ACT_ONLY) {
-                        if (n < g.T && icol < g.I) g.act_out[(size_t)n * g.ldact + icol] = __float2bfloat16_rn(a);
-                        continue;
-                    }
                     const int off = (n >> 3) * 1024 + (n & 7) * 128 + ((((col >> 3) ^ (n & 7)) & 7) << 4) + (col & 7) * 2;
                     *reinterpret_cast<bf16*>(act + off) = __float2bfloat16_rn(a);
                 }
@@ -374,7 +357,7 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
         // 3 us; one bulk reduction per token and tile (96 a block at 8 tokens) were slower still, a reduction costs per
         // operation more than per byte.  Spread over the tiles, one operation each, they hide behind the weight stream.
         bool go = ok && !s_abort;
-        for (int m = 0; m < (ACT_ONLY ? 0 : g.n_mt); ++m) {
+        for (int m = 0; m < g.n_mt; ++m) {
             const int buf = m & 1;
             const uint32_t par = (uint32_t)(m >> 1) & 1u;
             go = go && mbar_wait(bar_tile + 8 * m, 0, &s_abort);
@@ -410,7 +393,7 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
                 }
             }
         }
-        if (!ACT_ONLY && warp == 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // the sums have reached memory
+        if (warp == 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // the sums have reached memory
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
@@ -419,10 +402,10 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
     }
 }
 
-template <int BN, int STAGES, bool ACT_ONLY = false>
+template <int BN, int STAGES>
 int launch(const CUtensorMap& mg, const CUtensorMap& mu, const CUtensorMap& mx, const CUtensorMap& md, const CUtensorMap& mr,
            const MlpArgs& g, int blocks, cudaStream_t stream) {
-    auto k = mlp_fused_kernel<BN, STAGES, ACT_ONLY>;
+    auto k = mlp_fused_kernel<BN, STAGES>;
     constexpr int smem = Smem<BN, STAGES>::TOTAL;
     static bool configured[64] = {};
     int dev = 0;
@@ -463,8 +446,6 @@ LLB_API int llb_mlp_fused(const void* X, int ldx, const void* Wgu, const void* W
     while (pow2 < cols) pow2 *= 2;
     g.tmem_cols = pow2;
     g.err = err;
-    g.act_out = nullptr;
-    g.ldact = 0;
     CUtensorMap mg, mu, mx, md, mr;
     int rc = llb_tma::bf16_map_64(Wgu, I, H, H, SLICE, &mg);
     if (rc) return rc;
@@ -482,37 +463,5 @@ LLB_API int llb_mlp_fused(const void* X, int ldx, const void* Wgu, const void* W
     LLB_MLP(16, 4); LLB_MLP(16, 5); LLB_MLP(16, 6); LLB_MLP(16, 8); LLB_MLP(16, 10);
     LLB_MLP(32, 4); LLB_MLP(32, 5); LLB_MLP(32, 6); LLB_MLP(32, 8);
 #undef LLB_MLP
-    return (int)cudaErrorInvalidValue;
-}
-
-// act [T, I] bf16 (row stride ldact) = up(X) * silu(gate(X)) for up to 64 tokens: the gate/up half of the kernel above
-// alone (ACT_ONLY), I / 64 blocks with one accumulator each.  X [T, H] bf16 (row stride ldx), Wgu [2 I, H] bf16 dense
-// (gate rows first).  H and I multiples of 8.  stages: 3 to 6 (0 chooses).
-LLB_API int llb_mlp_gate_up(const void* X, int ldx, const void* Wgu, void* act, int ldact, int T, int H, int I, int blocks,
-                            int stages, int* err, cudaStream_t stream) {
-    if (T <= 0 || T > 64 || H <= 0 || I <= 0 || H % 8 || I % 8 || ldx % 8 || blocks <= 0 || !act) return (int)cudaErrorInvalidValue;
-    if (((uintptr_t)X | (uintptr_t)Wgu) & 15) return (int)cudaErrorInvalidValue;
-    const int bn = T <= 16 ? 16 : T <= 32 ? 32 : 64;
-    MlpArgs g;
-    g.residual = nullptr;
-    g.T = T; g.H = H; g.I = I;
-    g.n_slices = (I + SLICE - 1) / SLICE;
-    g.n_mt = 0;
-    g.tmem_cols = 2 * bn < 32 ? 32 : 2 * bn;
-    g.err = err;
-    g.act_out = (bf16*)act;
-    g.ldact = ldact;
-    CUtensorMap mg, mu, mx;
-    int rc = llb_tma::bf16_map_64(Wgu, I, H, H, SLICE, &mg);
-    if (rc) return rc;
-    rc = llb_tma::bf16_map_64((const bf16*)Wgu + (size_t)I * H, I, H, H, SLICE, &mu);
-    if (rc) return rc;
-    rc = llb_tma::bf16_map_64(X, T, H, ldx, bn, &mx);
-    if (rc) return rc;
-    const int grid = g.n_slices < blocks ? g.n_slices : blocks;
-    if (stages == 0) stages = bn == 64 ? 5 : 6;
-#define LLB_GU(BN_, ST_) if (bn == BN_ && stages == ST_) return launch<BN_, ST_, true>(mg, mu, mx, mg, mg, g, grid, stream)
-    LLB_GU(16, 6); LLB_GU(32, 6); LLB_GU(64, 3); LLB_GU(64, 4); LLB_GU(64, 5); LLB_GU(64, 6);
-#undef LLB_GU
     return (int)cudaErrorInvalidValue;
 }

@@ -395,16 +395,6 @@ def linear_swiglu(x: torch.Tensor, gate_up: torch.Tensor, plan=None) -> torch.Te
     tensor cores the two products share one kernel and the [M, 2I] intermediate is never written."""
     _need_cuda(x, gate_up)
     I = gate_up.shape[0] // 2
-    if (plan is None and FUSED_MLP and _tc_ok(x, gate_up, None) and 32 < x.shape[0] <= 64 and I % 8 == 0):
-        # 33 to 64 tokens: a slice's gate rows and up rows in one tile, I / 64 blocks with one accumulator each
-        # (csrc/mlp_tc.cu, its gate/up half alone)
-        out = torch.empty((x.shape[0], I), dtype=x.dtype, device=x.device)
-        err = _tc_resources(x.device)[2]
-        f = _fn(load_module("mlp_tc.cu", _MLP_DEFINES), "llb_mlp_gate_up",
-                [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
-        _check(f(_ptr(x), x.stride(0), _ptr(gate_up), _ptr(out), out.stride(0), x.shape[0], x.shape[1], I, _sm_count(x.device),
-                 _MLP_STAGES, _ptr(err), _stream()), "gate/up + SwiGLU (slices, tensor cores)")
-        return out
     if _tc_ok(x, gate_up, None) and x.shape[0] > 0:
         out = torch.empty((x.shape[0], I), dtype=x.dtype, device=x.device)
         _gemm_tc(x, gate_up, None, out, dual_offset=I, plan=plan)

@@ -640,21 +640,3 @@ def test_linear_into_the_residual_stream_on_paired_sms(T, N, K, ksplit):
         want = s0.double().cpu().numpy() + 2 * (prod + (b.double().cpu().numpy() if bias is not None else 0.0))
         _tc_check(stream, want, 4 * K)
     assert kernels.tc_error(DEV) == 0
-
-
-@pytest.mark.parametrize("T,I,K", [(64, 8960, 1536), (33, 8960, 1536), (50, 232, 144), (40, 18944, 3584), (64, 136, 72)])
-def test_gate_up_in_slices_for_33_to_64_tokens(T, I, K):
-    """linear_swiglu() between 33 and 64 tokens runs the slice kernel's gate/up half: against the plain formula, and
-    against the two-accumulator product that serves the other token counts."""
-    from llaisys_b200 import kernels
-    x, w, _ = _tc_case(T, 2 * I, K, T + I)
-    w = (w.float() * 4).to(torch.bfloat16)
-    gu = plain.linear(x.double().cpu().numpy(), w.double().cpu().numpy())
-    want = plain.swiglu(gu[:, :I], gu[:, I:])
-    for turn in range(2):
-        got = kernels.linear_swiglu(x, w)
-        assert got.shape == (T, I)
-        _close(got, want, torch.bfloat16, atol=5e-3)
-    other = kernels.linear_swiglu(x, w, plan=(64, 1))
-    assert float((other.float() - got.float()).abs().max()) <= 2.0 ** -7 * float(got.float().abs().max()) + 1e-3
-    assert kernels.tc_error(DEV) == 0
