@@ -18,6 +18,7 @@ from typing import Dict, List, Optional
 import numpy as np
 import torch
 
+from .. import diagnostics
 from ..csrc.build import page_tokens
 from ..parts.base import KVNeed
 from .slots import CacheError, CacheFull, SlotBook
@@ -103,14 +104,31 @@ class PagedCache:
         self.v_pools: List[torch.Tensor] = []
         self.state: Dict[int, torch.Tensor] = {}
         self.state_sizes = list(state_sizes)
+        self._guards: List[tuple] = []            # (what, raw allocation) of every guarded tensor
         if allocate:
-            for (nkvh, dk, dv, _), n_entries, pages in zip(self.group_keys, entries_per_group, self.group_pages):
-                self.k_pools.append(torch.zeros((n_entries, pages, nkvh, PAGE, dk), dtype=dtype, device=self.device))
-                self.v_pools.append(torch.zeros((n_entries, pages, nkvh, PAGE, dv), dtype=dtype, device=self.device)
+            for g, ((nkvh, dk, dv, _), n_entries, pages) in enumerate(zip(self.group_keys, entries_per_group, self.group_pages)):
+                self.k_pools.append(self._zeros(f"keys of group {g}", (n_entries, pages, nkvh, PAGE, dk), dtype))
+                self.v_pools.append(self._zeros(f"values of group {g}", (n_entries, pages, nkvh, PAGE, dv), dtype)
                                     if dv > 0 else None)
             for c, n in enumerate(state_sizes):
                 if n > 0:
-                    self.state[c] = torch.zeros((self.n_slots, n), dtype=torch.float32, device=self.device)
+                    self.state[c] = self._zeros(f"state of user {c}", (self.n_slots, n), torch.float32)
+        diagnostics.log.info("cache: %d pages of %d tokens, %d slots, groups %s, %.1f MB", n_pages, PAGE, self.n_slots,
+                             [(k, p) for k, p in zip(self.group_keys, self.group_pages)],
+                             sum(p.numel() * p.element_size() for p in self.k_pools + self.v_pools if p is not None) / 1e6)
+
+    def _zeros(self, what: str, shape, dtype) -> torch.Tensor:
+        if not diagnostics.CANARY:
+            return torch.zeros(shape, dtype=dtype, device=self.device)
+        t, raw = diagnostics.guarded(shape, dtype, self.device)
+        self._guards.append((what, raw))
+        return t
+
+    def check_guards(self) -> None:
+        """Raises CacheError naming every guarded tensor whose guard words were overwritten (LLAISYS_CANARY=1)."""
+        broken = [what for what, raw in self._guards if not diagnostics.guards_intact(raw)]
+        if broken:
+            raise CacheError("guard words overwritten around: " + ", ".join(broken))
 
     # ---- sequences
     def acquire(self) -> int:

@@ -123,3 +123,37 @@ class SlotBook:
 
     def pages(self, slot: int, group: int) -> List[int]:
         return self._seq(slot).pages[group]
+
+    def audit(self) -> List[str]:
+        """Everything that is wrong with the books, in words (empty when they are in order): a slot that is
+        live but not held or held but not live, a page that two sequences list or that lies outside its pool,
+        a listed page that the pool thinks free, a held page that nobody lists, a sequence with fewer pages
+        than its length needs or more than its ring has."""
+        bad: List[str] = []
+        for slot in self.seqs:
+            if not self.slots.is_held(slot):
+                bad.append(f"slot {slot} is live but not held")
+        for slot in range(self.slots.n):
+            if self.slots.is_held(slot) and slot not in self.seqs:
+                bad.append(f"slot {slot} is held but holds no sequence")
+        for g, pool in enumerate(self.pools):
+            owner: Dict[int, int] = {}
+            for slot, seq in self.seqs.items():
+                pages = seq.pages[g]
+                if len(pages) < self.pages_needed(g, seq.length):
+                    bad.append(f"slot {slot} holds {len(pages)} pages of group {g}, too few for {seq.length} tokens")
+                if self.rings[g] is not None and len(pages) > self.rings[g]:
+                    bad.append(f"slot {slot} holds {len(pages)} pages of group {g}, more than its ring of {self.rings[g]}")
+                for pg in pages:
+                    if not (0 <= pg < pool.n):
+                        bad.append(f"slot {slot} lists page {pg} of group {g}, outside the pool (0..{pool.n - 1})")
+                        continue
+                    if pg in owner:
+                        bad.append(f"page {pg} of group {g} is listed by slots {owner[pg]} and {slot}")
+                    owner[pg] = slot
+                    if not pool.is_held(pg):
+                        bad.append(f"slot {slot} lists page {pg} of group {g}, which the pool thinks free")
+            for pg in range(pool.n):
+                if pool.is_held(pg) and pg not in owner:
+                    bad.append(f"page {pg} of group {g} is held but no sequence lists it")
+        return bad

@@ -114,6 +114,9 @@ def main(argv=None) -> int:
         model = CausalLM(model_dir, DeviceType.NVIDIA, dtype=args.dtype, max_tokens=args.max_tokens, seed=args.seed)
         outs = model.generate_batch(prompts, max_new_tokens=args.max_steps, top_k=top_k, top_p=top_p, temperature=temperature)
     elapsed = time.time() - start
+    from .diagnostics import timers
+    if timers.enabled and args.device != "cpu":
+        print(timers.table(), file=sys.stderr)      # LLAISYS_TIMERS=1: device time per kernel class
 
     print("\n=== Your Result ===\n")
     for p, new in zip(prompts, outs):

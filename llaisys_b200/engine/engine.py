@@ -6,6 +6,7 @@ from typing import List, Optional, Sequence
 
 import torch
 
+from .. import diagnostics
 from ..cache.kv import CacheConfig, PagedCache
 from ..cache.slots import CacheError
 from ..config.spec import ModelSpec
@@ -60,7 +61,8 @@ class Engine:
                                 self.env.dtype, self.env.device)
         self.sm_count = torch.cuda.get_device_properties(self.env.device).multi_processor_count
         self.err = torch.zeros(1, dtype=torch.int32, device=self.env.device)
-        self.use_graphs = use_graphs and model.capturable()
+        # with kernel timers on, steps run uncaptured: a replayed graph has no launches to put events around
+        self.use_graphs = use_graphs and model.capturable() and not diagnostics.timers.enabled
         # The longest sequence a slot can reach: the model's limit, and the cache's room unless every
         # group keeps a window only (rings never run out of pages).  Parts size their tables for it once;
         # a captured step has their addresses, so they must not move afterwards.
@@ -68,6 +70,10 @@ class Engine:
         if any(r is None for r in self.cache.rings):
             self.position_limit = min(self.position_limit, self.cache.n_pages * self.page)
         model.prepare(self.position_limit)
+        diagnostics.log.info("engine: %s, %s on %s, %d layers in the run order, positions up to %d, graphs %s",
+                             self.spec.architecture, str(self.env.dtype).replace("torch.", ""), self.env.device,
+                             len(self.spec.order),
+                             self.position_limit, "on" if self.use_graphs else "off")
         # the last sampled token of every slot, for steps that take their tokens from the device (see feed())
         self.fed_tokens = torch.zeros(self.cache.n_slots, dtype=torch.int32, device=self.env.device)
         self._last_ctx = None
@@ -163,6 +169,10 @@ class Engine:
             out_rows += [base + int(w) for w in e.want]
             base += n
         book = self.cache.book
+        if diagnostics.BOUNDS:
+            wrong = book.audit()
+            if wrong:
+                raise StepError("the cache's books are out of order before the step: " + "; ".join(wrong[:8]))
         for s, n in zip(slots, n_new):
             if book.length(s) + n > self.spec.max_positions:
                 raise StepError(f"slot {s} would reach {book.length(s) + n} positions; the model allows "
@@ -184,6 +194,7 @@ class Engine:
             give_back()
             raise
         with torch.cuda.device(self.env.device):
+            diagnostics.timers.start()
             graphed = self.use_graphs and max(n_new) == 1
             shape = StepContext.shape_of(self.cache, slots, n_new, out_rows, bucket=graphed)
             try:
@@ -194,6 +205,8 @@ class Engine:
                     buf, ev = self._staging(ctx.meta.numel())
                     ctx.load(slots, n_new, tokens, out_rows, buf)
                     ev.record()
+                    if diagnostics.BOUNDS:
+                        self._audit_step(ctx, buf)
                     logits = self._forward(ctx, fed)
                     self._last_ctx = ctx
             except Exception:
@@ -219,6 +232,8 @@ class Engine:
         buf, ev = self._staging(ctx.meta.numel())
         ctx.load(slots, n_new, tokens, out_rows, buf)
         ev.record()
+        if diagnostics.BOUNDS:
+            self._audit_step(ctx, buf)
         if entry[1] is None:
             logits = self._forward(ctx, fed)          # the real step, uncaptured; this also loads every kernel
             from ..kernels import ops
@@ -243,10 +258,44 @@ class Engine:
         self.graph_replays += 1
         return entry[2]
 
+    def _audit_step(self, ctx: StepContext, staged: torch.Tensor) -> None:
+        """The step's description as the kernels will read it (the staged host copy), checked against the
+        cache: every position inside the limit, every packed token inside its sequence, every page-table entry
+        that a sequence's length reaches inside its group's pool and in no other sequence's row."""
+        meta = staged[:ctx.meta.numel()].numpy()
+        o = ctx._offs
+        tok_seq, tok_pos, starts, lens = (meta[o[i]:o[i + 1]] for i in (1, 2, 3, 4))
+        wrong = []
+        B, T = ctx.n_seqs, ctx.n_tokens
+        if starts[0] != 0 or starts[B] != T or (starts[1:] <= starts[:-1]).any():
+            wrong.append(f"sequence starts {starts.tolist()} do not partition {T} tokens")
+        if T and (tok_pos.min() < 0 or tok_pos.max() >= self.position_limit):
+            wrong.append(f"positions {int(tok_pos.min())}..{int(tok_pos.max())} outside 0..{self.position_limit - 1}")
+        if T and (tok_seq.min() < 0 or tok_seq.max() >= B):
+            wrong.append("a token names a sequence outside the batch")
+        for g, w in enumerate(ctx.widths):
+            table = meta[o[7 + g]:o[8 + g]].reshape(B, w)
+            ring, seen = self.cache.rings[g], set()
+            for b in range(B):
+                used = self.cache.book.pages_needed(g, int(lens[b]) + ctx.n_new[b])
+                if used > w or (ring is not None and used > ring):
+                    wrong.append(f"sequence {b} needs {used} pages of group {g}; its table row has {w}, its ring {ring}")
+                    continue
+                for pg in table[b, :used].tolist():
+                    if not (0 <= pg < self.cache.group_pages[g]):
+                        wrong.append(f"sequence {b} names page {pg} of group {g}, outside 0..{self.cache.group_pages[g] - 1}")
+                    elif pg in seen:
+                        wrong.append(f"page {pg} of group {g} is in two sequences' tables")
+                    seen.add(pg)
+        if wrong:
+            raise StepError("the step's description is out of order: " + "; ".join(wrong[:8]))
+
     def check(self) -> None:
         """Waits for the device and raises if a kernel flagged an error since the last check."""
-        from ..kernels import tc_error
+        from ..kernels import ops, tc_error
         code = int(self.err.item())
+        self.cache.check_guards()
+        ops.check_guards(self.env.device)
         if code:
             self.err.zero_()
         tc = tc_error(self.env.device)            # read and cleared

@@ -8,6 +8,8 @@ from typing import Optional
 import torch
 
 from ..csrc.build import load_module, page_tokens
+from .. import diagnostics
+from ..diagnostics import timers
 
 PAGE = page_tokens()           # tokens of a cache page (LLB_PAGE in csrc/common.cuh)
 DT = {torch.float32: 0, torch.bfloat16: 1}
@@ -63,6 +65,8 @@ def launch_count() -> int:
 def _check(rc: int, what: str, n: int = 1):
     global _launches
     _launches += n
+    if timers.enabled:
+        timers.mark(what)
     if rc <= -2000:
         raise KernelError(f"{what}: the kernel's shared-memory size was refused (CUDA error {-rc - 2000})")
     if rc <= -1000:
@@ -210,11 +214,27 @@ def _tc_resources(device):
     device = _dev_key(device)
     r = _tc_res.get(device)
     if r is None:
-        r = (torch.empty(_TC_SCRATCH_ELEMS, dtype=torch.float32, device=device),
-             torch.zeros(_TC_COUNTERS, dtype=torch.int32, device=device),
-             torch.zeros(1, dtype=torch.int32, device=device))
+        if diagnostics.CANARY:
+            scratch, raw_s = diagnostics.guarded((_TC_SCRATCH_ELEMS,), torch.float32, device, fill_zero=False)
+            counters, raw_c = diagnostics.guarded((_TC_COUNTERS,), torch.int32, device)
+            _tc_guards[device] = [("tensor-core scratch", raw_s), ("tensor-core tile counters", raw_c)]
+        else:
+            scratch = torch.empty(_TC_SCRATCH_ELEMS, dtype=torch.float32, device=device)
+            counters = torch.zeros(_TC_COUNTERS, dtype=torch.int32, device=device)
+        r = (scratch, counters, torch.zeros(1, dtype=torch.int32, device=device))
         _tc_res[device] = r
     return r
+
+
+_tc_guards = {}
+
+
+def check_guards(device) -> None:
+    """Raises KernelError if the guard words around the tensor-core scratch or counters of `device` were
+    overwritten (they exist only under LLAISYS_CANARY=1)."""
+    broken = [what for what, raw in _tc_guards.get(_dev_key(device), []) if not diagnostics.guards_intact(raw)]
+    if broken:
+        raise KernelError("guard words overwritten around: " + ", ".join(broken))
 
 
 def _dev_key(device) -> torch.device:
