@@ -30,6 +30,7 @@ MEASURED_PEAKS.json beside this file when it exists, else from the fallback figu
 from __future__ import annotations
 
 import argparse
+import contextlib
 import json
 import os
 import statistics
@@ -82,38 +83,57 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while a timed region runs.
+
+    The program is started before the warm-up steps and waited for until its first line has come, so that its
+    start-up (a process to create, the management library to load) does not run beside the timed steps, where it
+    was measured to take tenths of a millisecond per step from a host that enqueues 64-sequence steps.  region()
+    marks the timed steps; the summary is over the samples that arrived between its start and shortly after its
+    end (all samples since the start of the program if the region was shorter than a sampling period)."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    PERIOD_MS = 50
 
     def __init__(self):
-        self.rows, self.proc = [], None
+        self.rows, self.proc, self.t0, self.t1 = [], None, None, None
+        self.first = threading.Event()
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                                          "-lms", str(self.PERIOD_MS)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
+            self.first.wait(timeout=5.0)
         except OSError:
             self.proc = None
         return self
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
+            self.first.set()
+
+    def region_start(self):
+        self.t0 = time.perf_counter()
+
+    def region_end(self):
+        self.t1 = time.perf_counter()
 
     def __exit__(self, *a):
         if self.proc:
-            time.sleep(0.15)
+            time.sleep(0.12)
             self.proc.terminate()
             self.thread.join(timeout=2)
 
     def summary(self):
-        sm = [int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit()]
-        mx = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
+        rows = [r for t, r in self.rows if self.t0 is not None and self.t0 <= t <= (self.t1 or t) + 1.5 * self.PERIOD_MS / 1e3]
+        if not rows:
+            rows = [r for _, r in self.rows]
+        sm = [int(r[0]) for r in rows if len(r) >= 6 and r[0].isdigit()]
+        mx = [int(r[1]) for r in rows if len(r) >= 6 and r[1].isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in self.rows)]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower().startswith("active") for r in rows)]
         return {"sm_mhz": int(statistics.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": reasons, "samples": len(sm)}
 
@@ -311,9 +331,11 @@ def own_workload(args, model, cfg, cfg_dict, layers, full_layers, shape_name, pk
         loop = GenerationLoop(engine, Sampler(SamplingParams(top_k=1)), stop_ids=[])
         torch.cuda.synchronize()
         with ClockSampler() as clk:
+            clk.region_start()
             t0 = time.perf_counter()
             out = loop.run(prompts, max_new_tokens=steps + 1)
             marks = loop.step_marks
+            clk.region_end()
         engine.check()
     assert all(len(g.tokens) == steps + 1 for g in out) and loop.batches_run == 1
     T = sum(lengths)
@@ -576,28 +598,32 @@ def main() -> int:
                "frac": round(prefill_flops / (prefill_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
 
     # ---- decode at a given batch: sequences that already hold PROMPT_LEN tokens each
-    def decode(batch, steps, warmup):
+    def decode(batch, steps, warmup, clocks=True):
         slots = filled_slots(engine, batch, rng, V)
         toks = rng.integers(0, V, size=(warmup + steps, batch)).tolist()
         sampler = Sampler(SamplingParams(top_k=1))
-        for i in range(warmup):
-            sampler.on_device(engine.step([StepEntry(s, [t], [0]) for s, t in zip(slots, toks[i])]), slots, [i] * batch)
-        torch.cuda.synchronize()
-        n0 = kernels.launch_count()
-        a, b = events()
-        with ClockSampler() as clk:
+        with (ClockSampler() if clocks else contextlib.nullcontext()) as clk:      # up and sampling before the warm-up
+            for i in range(warmup):
+                sampler.on_device(engine.step([StepEntry(s, [t], [0]) for s, t in zip(slots, toks[i])]), slots, [i] * batch)
+            torch.cuda.synchronize()
+            n0 = kernels.launch_count()
+            a, b = events()
+            if clk:
+                clk.region_start()
             a.record()
             for i in range(warmup, warmup + steps):
                 sampler.on_device(engine.step([StepEntry(s, [t], [0]) for s, t in zip(slots, toks[i])]), slots, [i] * batch)
             b.record()
             torch.cuda.synchronize()
+            if clk:
+                clk.region_end()
         ms = a.elapsed_time(b) / steps
         launches = kernels.launch_count() - n0
         ctx = PROMPT_LEN + warmup + steps // 2            # mean cached length over the timed steps
         for s in slots:
             engine.release(s)
         engine.check()
-        return ms, launches, clk.summary(), ctx
+        return ms, launches, clk.summary() if clk else None, ctx
 
     ms, launches, clocks, ctx_len = decode(args.batch, args.steps, args.warmup)
     value = args.batch * 1e3 / ms
@@ -610,7 +636,7 @@ def main() -> int:
     points, e2e = {}, None
     if not args.no_points:
         for b in (1, 64):
-            m, _, _, _ = decode(b, max(8, args.steps // 2), 3)
+            m, _, _, _ = decode(b, max(8, args.steps // 2), 3, clocks=False)
             points[f"decode_b{b}"] = round(b * 1e3 / m, 1)
         # ---- end to end through the generation loop: host ids in, host ids out
         prompts = [rng.integers(0, V, size=PROMPT_LEN).tolist() for _ in range(args.batch)]

@@ -82,3 +82,17 @@ def test_k_ranges_of_the_prefill_projection_that_ends_in_the_residual_add(T, N, 
     assert ks == want
     kblocks = math.ceil(K / 64)
     assert 1 <= ks <= 4 and (ks - 1) * math.ceil(kblocks / ks) < kblocks          # no K range is empty
+
+
+def test_clock_summary_is_over_the_samples_of_the_timed_region():
+    sys.path.insert(0, str(Path(__file__).resolve().parent.parent))
+    import bench
+    clk = bench.ClockSampler()
+    row = lambda mhz, cap: [str(mhz), "1965", "Not Active", "Not Active", "Not Active", "Active" if cap else "Not Active"]
+    clk.rows = [(10.00, row(300, False)), (10.05, row(1900, False)), (10.10, row(1950, True)), (10.15, row(1920, True)),
+                (10.40, row(500, False))]
+    clk.t0, clk.t1 = 10.04, 10.12
+    s = clk.summary()                      # the samples at 10.05, 10.10 and (within a period and a half of the end) 10.15
+    assert s == {"sm_mhz": 1920, "sm_max_mhz": 1965, "reasons": ["sw_power_cap"], "samples": 3}
+    clk.t0, clk.t1 = 11.0, 11.001          # a region no sample fell into: all of them
+    assert clk.summary()["samples"] == 5
