@@ -31,6 +31,7 @@ from __future__ import annotations
 
 import argparse
 import contextlib
+import gc
 import json
 import os
 import statistics
@@ -63,6 +64,10 @@ SHAPES = {
                                       max_window_layers=64)),
 }
 PROMPT_LEN, CONTEXT, PREFILL_TOKENS = 2048, 4096, 2048
+# Untimed decode steps between the prefill that fills the cache and the warm-up.  After a prefill burst at the power
+# limit the device runs its next 40 to 70 ms at reduced clocks (measured: steps of 1.35, then 1.20, then 1.12 ms at
+# batch 8); the decode measurements are of the steady state behind that.
+SETTLE_STEPS = 64
 # The two larger shapes' own workloads: (requests, shortest prompt, longest prompt, decode steps).  The prompts
 # of unequal lengths go through one prefill step together, then every request decodes that many tokens.
 OWN_WORKLOADS = {"7b": (16, 256, 4096, 256), "32b": (64, 512, 2048, 128)}
@@ -600,6 +605,7 @@ def main() -> int:
     # ---- decode at a given batch: sequences that already hold PROMPT_LEN tokens each
     def decode(batch, steps, warmup, clocks=True):
         slots = filled_slots(engine, batch, rng, V)
+        warmup += SETTLE_STEPS
         toks = rng.integers(0, V, size=(warmup + steps, batch)).tolist()
         sampler = Sampler(SamplingParams(top_k=1))
         with (ClockSampler() if clocks else contextlib.nullcontext()) as clk:      # up and sampling before the warm-up
@@ -608,6 +614,10 @@ def main() -> int:
             torch.cuda.synchronize()
             n0 = kernels.launch_count()
             a, b = events()
+            # a collection of the host's garbage (the prompts of the fill are a few hundred thousand objects) inside a
+            # region of some tens of milliseconds shows as milliseconds of idle device: collect before, not during
+            gc.collect()
+            gc.disable()
             if clk:
                 clk.region_start()
             a.record()
@@ -615,6 +625,7 @@ def main() -> int:
                 sampler.on_device(engine.step([StepEntry(s, [t], [0]) for s, t in zip(slots, toks[i])]), slots, [i] * batch)
             b.record()
             torch.cuda.synchronize()
+            gc.enable()
             if clk:
                 clk.region_end()
         ms = a.elapsed_time(b) / steps
@@ -636,12 +647,12 @@ def main() -> int:
     points, e2e = {}, None
     if not args.no_points:
         for b in (1, 64):
-            m, _, _, _ = decode(b, max(8, args.steps // 2), 3, clocks=False)
+            m, _, _, _ = decode(b, max(8, args.steps), 3, clocks=False)
             points[f"decode_b{b}"] = round(b * 1e3 / m, 1)
         # ---- end to end through the generation loop: host ids in, host ids out
         prompts = [rng.integers(0, V, size=PROMPT_LEN).tolist() for _ in range(args.batch)]
         loop = GenerationLoop(engine, Sampler(SamplingParams(top_k=1)), stop_ids=[])
-        n = args.warmup + args.steps
+        n = SETTLE_STEPS + args.warmup + args.steps
         loop.run(prompts, max_new_tokens=n + 1)
         marks = loop.step_marks
         dt = marks[-1] - marks[-1 - args.steps]
@@ -657,7 +668,7 @@ def main() -> int:
         "config": {"model": shape_name, "layers": layers,
                    "layers_of_config": full_layers, "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
                    "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size,
-                   "vocab": cfg.vocab_size, "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN,
+                   "vocab": cfg.vocab_size, "global_batch": args.batch, "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "settle_steps": SETTLE_STEPS,
                    "parallelism": "single GPU", "l2": f"no flush: each step streams {weight_bytes / 1e9:.1f} GB of weights, larger than L2",
                    "peaks": pk_src},
         "clocks": clocks, "gpu_launches": launches, "prefill": prefill, "roofline": roofline, "points": points,
