@@ -86,6 +86,21 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "l"(hint) : "memory");
 }
 // K-major tile, 128-byte rows, 128-byte swizzle, 8-row groups 1024 bytes apart.
+// Bounded wait of a whole (converged) warp: every lane polls and the vote keeps the control flow uniform.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (__all_sync(0xffffffffu, mbar_try(bar, parity))) return true;
+        if ((i & 255u) == 255u && __any_sync(0xffffffffu, *abort_flag != 0)) return false;
+    }
+    return false;
+}
+// True in exactly one lane of a converged warp; the compiler knows that what follows runs in one thread.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     uint64_t d = 0;
     d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
@@ -202,21 +217,27 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
     pdl_launch_dependents();
 
     if (warp == 0) {
-        // ---------------------------------------------------------------- producer (one thread)
-        if (lane == 0 && my_slices > 0) {
+        // ---------------------------------------------------------------- producer (the warp waits, one elected lane issues)
+        if (my_slices > 0) {
             // The weights do not depend on any earlier kernel of the step: the first stages' gate and up rows are
             // requested before the grid dependency resolves, their activations after it.
             const int pre = min(STAGES, KB1);
             const int row0 = (int)blockIdx.x * SLICE;
-            for (int i = 0; i < pre; ++i) {
-                const uint32_t dst = base + i * S::STAGE_BYTES;
-                mbar_expect_tx(bar_full + 8 * i, S::STAGE_BYTES);
-                tma_load_2d(dst, &map_gate, bar_full + 8 * i, i * BK, row0, HINT_EVICT_FIRST);
-                tma_load_2d(dst + S::A_BYTES / 2, &map_up, bar_full + 8 * i, i * BK, row0, HINT_EVICT_FIRST);
+            if (elect_one()) {
+                for (int i = 0; i < pre; ++i) {
+                    const uint32_t dst = base + i * S::STAGE_BYTES;
+                    mbar_expect_tx(bar_full + 8 * i, S::STAGE_BYTES);
+                    tma_load_2d(dst, &map_gate, bar_full + 8 * i, i * BK, row0, HINT_EVICT_FIRST);
+                    tma_load_2d(dst + S::A_BYTES / 2, &map_up, bar_full + 8 * i, i * BK, row0, HINT_EVICT_FIRST);
+                }
             }
+            __syncwarp();
             pdl_wait();                                    // the activations are the previous kernel's output
-            for (int i = 0; i < pre; ++i)
-                tma_load_2d(base + i * S::STAGE_BYTES + S::A_BYTES, &map_x, bar_full + 8 * i, i * BK, 0, HINT_EVICT_LAST);
+            if (elect_one()) {
+                for (int i = 0; i < pre; ++i)
+                    tma_load_2d(base + i * S::STAGE_BYTES + S::A_BYTES, &map_x, bar_full + 8 * i, i * BK, 0, HINT_EVICT_LAST);
+            }
+            __syncwarp();
             int n = pre;                                   // stages issued so far
             bool ok = true;
             for (int sl = 0; sl < my_slices && ok; ++sl) {
@@ -224,24 +245,27 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
                 for (int j = (sl == 0 ? pre : 0); j < per_slice && ok; ++j, ++n) {
                     const int s = n % STAGES;
                     const uint32_t round = (uint32_t)(n / STAGES);
-                    if (round > 0 && !mbar_wait(bar_empty + 8 * s, (round - 1) & 1, &s_abort)) {
-                        if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_MLP_EMPTY); }
+                    if (round > 0 && !warp_wait(bar_empty + 8 * s, (round - 1) & 1, &s_abort)) {
+                        if (lane == 0 && !s_abort) { s_abort = 1; atomicExch(g.err, ERR_MLP_EMPTY); }
                         ok = false;
                         break;
                     }
-                    const uint32_t dst = base + s * S::STAGE_BYTES;
-                    if (j < KB1) {
-                        mbar_expect_tx(bar_full + 8 * s, S::STAGE_BYTES);
-                        tma_load_2d(dst, &map_gate, bar_full + 8 * s, j * BK, slice * SLICE, HINT_EVICT_FIRST);
-                        tma_load_2d(dst + S::A_BYTES / 2, &map_up, bar_full + 8 * s, j * BK, slice * SLICE, HINT_EVICT_FIRST);
-                        tma_load_2d(dst + S::A_BYTES, &map_x, bar_full + 8 * s, j * BK, 0, HINT_EVICT_LAST);
-                    } else {
-                        mbar_expect_tx(bar_full + 8 * s, S::A_BYTES);
-                        tma_load_2d(dst, &map_down, bar_full + 8 * s, slice * SLICE, (j - KB1) * BM, HINT_EVICT_FIRST);
+                    if (elect_one()) {
+                        const uint32_t dst = base + s * S::STAGE_BYTES;
+                        if (j < KB1) {
+                            mbar_expect_tx(bar_full + 8 * s, S::STAGE_BYTES);
+                            tma_load_2d(dst, &map_gate, bar_full + 8 * s, j * BK, slice * SLICE, HINT_EVICT_FIRST);
+                            tma_load_2d(dst + S::A_BYTES / 2, &map_up, bar_full + 8 * s, j * BK, slice * SLICE, HINT_EVICT_FIRST);
+                            tma_load_2d(dst + S::A_BYTES, &map_x, bar_full + 8 * s, j * BK, 0, HINT_EVICT_LAST);
+                        } else {
+                            mbar_expect_tx(bar_full + 8 * s, S::A_BYTES);
+                            tma_load_2d(dst, &map_down, bar_full + 8 * s, slice * SLICE, (j - KB1) * BM, HINT_EVICT_FIRST);
+                        }
                     }
+                    __syncwarp();
                 }
             }
-            if (s_abort) {
+            if (s_abort && lane == 0) {
                 // copies in flight must land before this block's shared memory is given up
                 const int first = n > STAGES ? n - STAGES : 0;
                 for (int i = first; i < n; ++i)
@@ -250,53 +274,66 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
         }
         __syncwarp();
     } else if (warp == 1) {
-        // ---------------------------------------------------------------- tensor-core issue (one thread)
-        if (lane == 0 && my_slices > 0) {
+        // ---------------------------------------------------------------- tensor-core issue
+        // The whole warp waits (every lane polls, a vote keeps the warp converged: a satisfied wait costs about 60
+        // cycles so, several times that with one lane polling in a divergent branch) and one elected lane issues.
+        // The operand descriptors are made once; an instruction's own differs from them by a constant.  Built per
+        // instruction by the single issuing thread they cost about as long as a stage takes to arrive.
+        if (my_slices > 0) {
             const uint32_t idesc = umma_idesc(BN);
-            int n = 0;
+            const uint64_t a_desc0 = umma_desc(base), x_desc0 = umma_desc(base + S::A_BYTES);
+            int s = 0;
+            uint32_t ph = 0;
             bool ok = true;
             for (int sl = 0; sl < my_slices && ok; ++sl) {
                 const int b = sl & 1;
                 const uint32_t d1 = tmem + (uint32_t)(b * BN);
                 // gate/up: D1[b] = [gate rows; up rows] x X^T over all of K = H
-                for (int j = 0; j < KB1; ++j, ++n) {
-                    const int s = n % STAGES;
-                    if (!mbar_wait(bar_full + 8 * s, (uint32_t)(n / STAGES) & 1u, &s_abort)) {
-                        if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_MLP_FULL); }
+                for (int j = 0; j < KB1; ++j) {
+                    if (!warp_wait(bar_full + 8 * s, ph, &s_abort)) {
+                        if (lane == 0 && !s_abort) { s_abort = 1; atomicExch(g.err, ERR_MLP_FULL); }
                         ok = false;
                         break;
                     }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a = base + s * S::STAGE_BYTES, x = a + S::A_BYTES;
+                    if (elect_one()) {
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint64_t so = (uint64_t)(s * (S::STAGE_BYTES >> 4));
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma(d1, umma_desc(a + k * UMMA_K * 2), umma_desc(x + k * UMMA_K * 2), idesc, (j > 0 || k > 0) ? 1u : 0u);
-                    umma_commit(bar_empty + 8 * s);
+                        for (int k = 0; k < BK / UMMA_K; ++k)
+                            umma(d1, a_desc0 + so + (uint64_t)((k * UMMA_K * 2) >> 4), x_desc0 + so + (uint64_t)((k * UMMA_K * 2) >> 4), idesc,
+                                 (j > 0 || k > 0) ? 1u : 0u);
+                        umma_commit(bar_empty + 8 * s);
+                    }
+                    __syncwarp();
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
                 if (!ok) break;
-                umma_commit(bar_d1 + 8 * b);
+                if (elect_one()) umma_commit(bar_d1 + 8 * b);
+                __syncwarp();
                 // down: D2[m] += Wd[m tile, slice] x act^T, once the epilogue has put act[b] into shared memory
-                if (!mbar_wait(bar_act + 8 * b, (uint32_t)(sl >> 1) & 1u, &s_abort)) {
-                    if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_MLP_ACT); }
+                if (!warp_wait(bar_act + 8 * b, (uint32_t)(sl >> 1) & 1u, &s_abort)) {
+                    if (lane == 0 && !s_abort) { s_abort = 1; atomicExch(g.err, ERR_MLP_ACT); }
                     break;
                 }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t act = base + S::ACT_OFFSET + b * S::ACT_BYTES;
-                for (int m = 0; m < g.n_mt; ++m, ++n) {
-                    const int s = n % STAGES;
-                    if (!mbar_wait(bar_full + 8 * s, (uint32_t)(n / STAGES) & 1u, &s_abort)) {
-                        if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_MLP_FULL); }
+                const uint64_t act_desc0 = umma_desc(base + S::ACT_OFFSET + b * S::ACT_BYTES);
+                for (int m = 0; m < g.n_mt; ++m) {
+                    if (!warp_wait(bar_full + 8 * s, ph, &s_abort)) {
+                        if (lane == 0 && !s_abort) { s_abort = 1; atomicExch(g.err, ERR_MLP_FULL); }
                         ok = false;
                         break;
                     }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a = base + s * S::STAGE_BYTES;
+                    if (elect_one()) {
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint64_t so = (uint64_t)(s * (S::STAGE_BYTES >> 4));
 #pragma unroll
-                    for (int k = 0; k < SLICE / UMMA_K; ++k)
-                        umma(tmem_d2 + (uint32_t)(m * BN), umma_desc(a + k * UMMA_K * 2), umma_desc(act + k * UMMA_K * 2), idesc,
-                             (sl > 0 || k > 0) ? 1u : 0u);
-                    umma_commit(bar_empty + 8 * s);
-                    if (sl == my_slices - 1) umma_commit(bar_tile + 8 * m);            // this output tile is final
+                        for (int k = 0; k < SLICE / UMMA_K; ++k)
+                            umma(tmem_d2 + (uint32_t)(m * BN), a_desc0 + so + (uint64_t)((k * UMMA_K * 2) >> 4),
+                                 act_desc0 + (uint64_t)((k * UMMA_K * 2) >> 4), idesc, (sl > 0 || k > 0) ? 1u : 0u);
+                        umma_commit(bar_empty + 8 * s);
+                        if (sl == my_slices - 1) umma_commit(bar_tile + 8 * m);            // this output tile is final
+                    }
+                    __syncwarp();
+                    if (++s == STAGES) { s = 0; ph ^= 1u; }
                 }
             }
         }

@@ -517,8 +517,10 @@ def test_attention_prefill_from_cache_tcgen05(nh, nkvh, dh, window):
 def test_a_bounded_wait_that_runs_out_is_reported_and_the_next_launch_is_right(splits, tmp_path):
     """A test build of the tensor-core product (a small wait limit, and a switch that arms one stage barrier for
     sixteen bytes that nothing ever brings: no fault, no copy left in flight) makes the issuing thread's wait run
-    out.  The block must record code 101, free its tensor memory and return; the tile counters must be back at
-    zero; Engine.check() must raise; and the launches that follow must be right."""
+    out.  The block must record its code, free its tensor memory and return; the tile counters must be back at
+    zero; Engine.check() must raise; and the launches that follow must be right.  The code is 101 (the wait for a
+    full stage) or, where the K range is longer than the ring, 102 (the copying thread's wait for the same stage to
+    be freed, which starves with it): whichever of the two runs out first reports, the other sees the flag and leaves."""
     from ctypes import c_int, c_longlong, c_void_p
     from helpers import TINY_A, build_engine, make_folder
     from llaisys_b200 import kernels
@@ -549,9 +551,10 @@ def test_a_bounded_wait_that_runs_out_is_reported_and_the_next_launch_is_right(s
     _tc_check(launch(), want, K)                       # the test build is the same kernel when the switch is off
     err.fill_(-7)                                      # the switch: this launch's first stage never fills
     launch()
-    assert kernels.tc_error(DEV, clear=False) == 101   # the wait for a full stage ran out, and said so
+    code = kernels.tc_error(DEV, clear=False)          # a wait ran out, and said so
+    assert code == 101 or (code == 102 and -(-K // 64) // splits > 5)
     assert int(counters.abs().sum()) == 0              # blocks that gave up still arrived at their tile's counter
-    with pytest.raises(StepError, match="101"):
+    with pytest.raises(StepError, match=str(code)):
         engine.check()
     engine.check()                                     # reported once
     _tc_check(launch(), want, K)                       # the context is whole: the same launch is right again
