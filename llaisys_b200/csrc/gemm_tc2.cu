@@ -97,6 +97,22 @@ __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap
 }
 
 // K-major tile, 128-byte rows, 128-byte swizzle, 8-row groups 1024 bytes apart (what the TMA box writes).
+// Bounded wait of a whole (converged) warp: every lane polls and the vote keeps the control flow uniform (a satisfied
+// wait costs about 60 cycles so, several times that with one lane polling in a divergent branch).
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < WAIT_LIMIT; ++i) {
+        if (__all_sync(0xffffffffu, mbar_try(bar, parity))) return true;
+        if ((i & 255u) == 255u && __any_sync(0xffffffffu, *abort_flag != 0)) return false;
+    }
+    return false;
+}
+// True in exactly one lane of a converged warp; the compiler knows that what follows runs in one thread.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
     uint64_t d = 0;
     d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
@@ -241,73 +257,85 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     llb_grid_dependency_sync();      // from here on memory written by earlier kernels is touched
 
     if (warp == 0) {
-        if (lane == 0) {
-            // ---- producer: this CTA's weight rows and its half of the tokens, k-block after k-block, tile after tile
-            const uint32_t full0 = mapa(bar_full, 0);
-            {   // the activations of the k-blocks whose weight is on its way already
-                const int n0 = ((pair % g.n_tiles) % g.tok_tiles) * BN + (int)rank * (BN / 2);
-                for (int i = 0; i < prefetched; ++i)
-                    tma_load_2d_pair(base + i * S::STAGE_BYTES + ACCS * S::A_BYTES, &map_x, full0 + 8 * i, (first_kb0 + i) * BK, n0, HINT_EVICT_LAST);
-            }
-            int it = prefetched;
-            for (int u = pair; u < n_units && !s_abort; u += g.n_pairs) {
-                const int t = u % g.n_tiles, kb1 = unit_kb1(u);
-                const int m0 = ((t / g.tok_tiles) * 2 + (int)rank) * BM;
-                const int n0 = (t % g.tok_tiles) * BN + (int)rank * (BN / 2);
-                for (int kb = unit_kb0(u) + (u == pair ? prefetched : 0); kb < kb1; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    if (it >= STAGES && !mbar_wait(bar_empty + 8 * s, (uint32_t)(it / STAGES - 1) & 1u, &s_abort)) {
-                        if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC2_WAIT_EMPTY); }
-                        break;
-                    }
+        // ---- producer: this CTA's weight rows and its half of the tokens, k-block after k-block, tile after tile.  The
+        // warp waits for a free stage as a whole; one elected lane issues the copies.
+        const uint32_t full0 = mapa(bar_full, 0);
+        if (elect_one()) {   // the activations of the k-blocks whose weight is on its way already
+            const int n0 = ((pair % g.n_tiles) % g.tok_tiles) * BN + (int)rank * (BN / 2);
+            for (int i = 0; i < prefetched; ++i)
+                tma_load_2d_pair(base + i * S::STAGE_BYTES + ACCS * S::A_BYTES, &map_x, full0 + 8 * i, (first_kb0 + i) * BK, n0, HINT_EVICT_LAST);
+        }
+        __syncwarp();
+        int it = prefetched;
+        bool ok = true;
+        for (int u = pair; u < n_units && ok; u += g.n_pairs) {
+            const int t = u % g.n_tiles, kb1 = unit_kb1(u);
+            const int m0 = ((t / g.tok_tiles) * 2 + (int)rank) * BM;
+            const int n0 = (t % g.tok_tiles) * BN + (int)rank * (BN / 2);
+            for (int kb = unit_kb0(u) + (u == pair ? prefetched : 0); kb < kb1; ++kb, ++it) {
+                const int s = it % STAGES;
+                if (it >= STAGES && !warp_wait(bar_empty + 8 * s, (uint32_t)(it / STAGES - 1) & 1u, &s_abort)) {
+                    if (lane == 0 && !s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC2_WAIT_EMPTY); }
+                    ok = false;
+                    break;
+                }
+                if (elect_one()) {
                     const uint32_t dst = base + s * S::STAGE_BYTES, bar = full0 + 8 * s;
                     if (leader) mbar_expect_tx(bar_full + 8 * s, 2u * S::STAGE_BYTES);
                     tma_load_2d_pair(dst, &map_w, bar, kb * BK, m0, HINT_EVICT_FIRST);
                     if (DUAL) tma_load_2d_pair(dst + S::A_BYTES, &map_w, bar, kb * BK, m0 + g.dual_offset, HINT_EVICT_FIRST);
                     tma_load_2d_pair(dst + ACCS * S::A_BYTES, &map_x, bar, kb * BK, n0, HINT_EVICT_LAST);
                 }
+                __syncwarp();
             }
-            if (s_abort && leader) {
-                // copies in flight (of both CTAs) must land before the pair gives up its shared memory
-                int first = it > STAGES ? it - STAGES : 0;
-                for (int i = first; i < it; ++i)
-                    for (uint32_t w = 0; w < WAIT_LIMIT && !mbar_try(bar_full + 8 * (i % STAGES), (uint32_t)(i / STAGES) & 1u); ++w) {}
-            }
+        }
+        if (s_abort && leader && lane == 0) {
+            // copies in flight (of both CTAs) must land before the pair gives up its shared memory
+            int first = it > STAGES ? it - STAGES : 0;
+            for (int i = first; i < it; ++i)
+                for (uint32_t w = 0; w < WAIT_LIMIT && !mbar_try(bar_full + 8 * (i % STAGES), (uint32_t)(i / STAGES) & 1u); ++w) {}
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (lane == 0 && leader) {
-            // ---- tensor-core issue for both SMs
+        if (leader) {
+            // ---- tensor-core issue for both SMs: the warp waits as a whole, one elected lane issues; the operand
+            // descriptors are made once and a stage's or an instruction's own differ from them by a constant
             const uint32_t idesc = umma_idesc_pair(BN);
+            const uint64_t a_desc0 = umma_desc(base), b_desc0 = umma_desc(base + ACCS * S::A_BYTES);
             int it = 0, ti = 0;
-            for (int u = pair; u < n_units && !s_abort; u += g.n_pairs, ++ti) {
+            bool ok = true;
+            for (int u = pair; u < n_units && ok; u += g.n_pairs, ++ti) {
                 const int buf = ti % NBUF, kb0 = unit_kb0(u), kb1 = unit_kb1(u);
-                if (ti >= NBUF && !mbar_wait(bar_acc_empty + 8 * buf, (uint32_t)(ti / NBUF - 1) & 1u, &s_abort)) {
-                    if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC2_WAIT_ACC_EMPTY); }
+                if (ti >= NBUF && !warp_wait(bar_acc_empty + 8 * buf, (uint32_t)(ti / NBUF - 1) & 1u, &s_abort)) {
+                    if (lane == 0 && !s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC2_WAIT_ACC_EMPTY); }
                     break;
                 }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t acc = tmem + buf * ACC_COLS;
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
-                    if (!mbar_wait(bar_full + 8 * s, (uint32_t)(it / STAGES) & 1u, &s_abort)) {
-                        if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC2_WAIT_FULL); }
+                    if (!warp_wait(bar_full + 8 * s, (uint32_t)(it / STAGES) & 1u, &s_abort)) {
+                        if (lane == 0 && !s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC2_WAIT_FULL); }
+                        ok = false;
                         break;
                     }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t a = base + s * S::STAGE_BYTES, b = a + ACCS * S::A_BYTES;
-                    const uint64_t ad = umma_desc(a), bd = umma_desc(b), ad2 = umma_desc(a + S::A_BYTES);
+                    if (elect_one()) {
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint64_t so = (uint64_t)(s * (S::STAGE_BYTES >> 4));
+                        const uint64_t ad = a_desc0 + so, bd = b_desc0 + so, ad2 = ad + (uint64_t)(S::A_BYTES >> 4);
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k) {
-                        const uint32_t accumulate = (kb > kb0 || k > 0) ? 1u : 0u;
-                        const uint64_t step = (uint64_t)(k * UMMA_K * 2 >> 4);      // the start address field counts 16 bytes
-                        umma_pair(acc, ad + step, bd + step, idesc, accumulate);
-                        if (DUAL) umma_pair(acc + BN, ad2 + step, bd + step, idesc, accumulate);
+                        for (int k = 0; k < BK / UMMA_K; ++k) {
+                            const uint32_t accumulate = (kb > kb0 || k > 0) ? 1u : 0u;
+                            const uint64_t step = (uint64_t)(k * UMMA_K * 2 >> 4);      // the start address field counts 16 bytes
+                            umma_pair(acc, ad + step, bd + step, idesc, accumulate);
+                            if (DUAL) umma_pair(acc + BN, ad2 + step, bd + step, idesc, accumulate);
+                        }
+                        umma_commit_both(bar_empty + 8 * s);
                     }
-                    umma_commit_both(bar_empty + 8 * s);
+                    __syncwarp();
                 }
-                if (s_abort) break;
-                umma_commit_both(bar_acc_full + 8 * buf);
+                if (!ok) break;
+                if (elect_one()) umma_commit_both(bar_acc_full + 8 * buf);
+                __syncwarp();
             }
         }
         __syncwarp();
