@@ -476,7 +476,7 @@ class _MmaAttnParams(ctypes.Structure):
                 ("seq_len_before", c_void_p), ("nh", c_int), ("nkvh", c_int), ("window", c_int),
                 ("scale", c_float), ("all_from_cache", c_int), ("n_splits", c_int), ("part_o", c_void_p),
                 ("part_ml", c_void_p), ("rope_cos", c_void_p), ("rope_sin", c_void_p), ("rope_rows", c_int),
-                ("append_new", c_int), ("cluster", c_int)]
+                ("append_new", c_int), ("cluster", c_int), ("err", c_void_p)]
 
 
 MMA_ATTENTION = True                         # tests switch the tensor-core attention off to compare
@@ -620,6 +620,7 @@ def attention_decode(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_star
             p.rope_cos, p.rope_sin, p.rope_rows = rope[0].data_ptr(), rope[1].data_ptr(), rope[0].shape[0]
         p.append_new = int(append_new)
         p.cluster = int(1 < n_splits <= 8 or n_splits == 16)      # few slices merge inside a cluster, through shared memory
+        p.err = _tc_resources(qkv.device)[2].data_ptr()           # a bounded wait of that merge that runs out says so here
     p.n_splits = n_splits
     if n_splits > 1 and not (mma and p.cluster):
         part_o = torch.empty((n_seqs, nh, n_splits, dh), dtype=torch.float32, device=qkv.device)
