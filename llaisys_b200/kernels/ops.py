@@ -245,7 +245,7 @@ def _dev_key(device) -> torch.device:
 
 
 def tc_error(device, clear: bool = True) -> int:
-    """Error word of the tensor-core kernels on `device` (0: none; 101-104, 111-114, 121-122: a bounded
+    """Error word of the tensor-core kernels on `device` (0: none; 101-104, 111-114, 121-122, 131-136, 141: a bounded
     wait ran out).  Reading it waits for the device; a code that was found is cleared, so that it is
     reported once."""
     r = _tc_res.get(_dev_key(device))
