@@ -301,7 +301,13 @@ __device__ __forceinline__ Ring<NST> make_ring(uint8_t* smem_raw) {
 }
 constexpr int MAX_CLUSTER = 16;            // key slices that merge inside a thread-block cluster (16 needs the non-portable size)
 constexpr int QS_BYTES = 16 * (DH + 8) * 2;
+// What a block receives in the cluster merge by pushing: from each block its share of the heads' sums (n_heads * DH * 4
+// bytes over all sources) and 16 (maximum, sum) pairs.  A region of its own, so that a peer may push whenever it is done,
+// without asking whether this block still needs the memory; 6 KB, which two blocks of the largest head size still fit an
+// SM with (ten heads of 128 to a kv head and eight slices; beyond that the slices merge by loads from the peers).
+constexpr int MERGE_RECV_BYTES = 6144;
 constexpr int smem_bytes(int nst) { return nst * STAGE_BYTES + QS_BYTES + 16 + 128; }     // ring, staged queries, a barrier, alignment slack
+constexpr int smem_bytes_decode(int nst) { return smem_bytes(nst) + MERGE_RECV_BYTES; }
 constexpr uint32_t MERGE_WAIT_LIMIT = 1u << 22;
 enum { ERR_ATTN_MERGE_WAIT = 141 };
 
@@ -349,12 +355,12 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     Ring<NST> ring = make_ring<NST>(smem_raw);
     // The key slices of a cluster merge by pushing (below) when every block's share of the outputs is whole 16-byte
-    // pieces and what it receives fits the memory of the staged queries, which is free once they are in registers.
+    // pieces and what it receives fits the receive region.
     const int G_ = p.nh / p.nkvh, chunks_ = (G_ + 15) / 16;
     const int nh_blk = min(16, G_ - (int)(blockIdx.y % chunks_) * 16);
     const int share4 = p.n_splits > 0 ? nh_blk * (DH / 4) / p.n_splits : 0;               // 16-byte pieces a block owns
     const bool push_merge = p.cluster && p.n_splits > 1 && (nh_blk * (DH / 4)) % p.n_splits == 0 &&
-                            p.n_splits * (share4 * 16 + 16 * 8) <= QS_BYTES;
+                            p.n_splits * (share4 * 16 + 16 * 8) <= MERGE_RECV_BYTES;
     const uint32_t bar_merge = ring.base + NST * STAGE_BYTES + QS_BYTES;
     if (push_merge && tid == 0) {
         asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar_merge));
@@ -362,6 +368,13 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
         // from each block of the cluster: its partial sums of this block's share, and every head's maximum and sum
         asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;"
                      ::"r"(bar_merge), "r"((uint32_t)(p.n_splits * (share4 * 16 + nh_blk * 8))) : "memory");
+    }
+    if (push_merge) {
+        // The peers may push as soon as this barrier stands: arrive now, long before anyone has anything to push; the
+        // wait that precedes a block's first push then costs nothing.  (With the receive region in the memory of the
+        // staged queries the arrival had to follow their last use, behind the grid dependency: 2,600 cycles.)
+        __syncthreads();
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     }
     // With append_new nothing this kernel fetches from the cache was written by the kernels just before it
     // (the new token's row comes from the projections), and the step's description was copied before the
@@ -447,12 +460,6 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
     __syncthreads();
     uint32_t qf[KSTEPS][4];
     load_q(qf, [&](int r) -> const bf16* { return qs + r * (DH + 8); }, lane);
-    if (push_merge) {
-        // the staged queries are in registers: from here on the peers may write into their memory (they wait for
-        // this arrival before their first push, long after it has happened)
-        __syncthreads();
-        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    }
     float o[DTILES][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 #pragma unroll
     for (int d = 0; d < DTILES; ++d) o[d][0] = o[d][1] = o[d][2] = o[d][3] = 0.f;
@@ -518,9 +525,9 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
         const int S = p.n_splits;
         uint32_t rank;
         asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
-        const uint32_t recv = ring.base + NST * STAGE_BYTES;                 // [S][share4] float4, then [S][16] (maximum, sum)
+        const uint32_t recv = ring.base + NST * STAGE_BYTES + QS_BYTES + 16;     // [S][share4] float4, then [S][16] (maximum, sum)
         const uint32_t ml_off = (uint32_t)(S * share4 * 16);
-        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");      // every peer's queries are in its registers
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");      // every peer's barrier stands
         for (int i4 = tid; i4 < n_heads * (DH / 4); i4 += THREADS) {
             const int r = i4 / (DH / 4), d4 = i4 - r * (DH / 4);
             float mw[4], M = -INFINITY;
@@ -566,7 +573,7 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
             return;
         }
         // ---- this block's share: every source scaled to the common base, added, divided, stored
-        const uint8_t* rp = ring.ptr + NST * STAGE_BYTES;
+        const uint8_t* rp = ring.ptr + NST * STAGE_BYTES + QS_BYTES + 16;
         const float2* rml = reinterpret_cast<const float2*>(rp + ml_off);
         bf16* out_tok = p.out + (size_t)tok * p.nh * DH + (size_t)head0 * DH;
         for (int j = tid; j < share4 * 4; j += THREADS) {
@@ -764,7 +771,7 @@ LLB_API int llb_attn_mma_prefill(MmaAttnParams p, int B, int max_new, cudaStream
 // How many clusters of `size` blocks of the decode kernel the device can hold at once (0: that size cannot be launched).
 LLB_API int llb_attn_mma_decode_max_clusters(int size) {
     auto kernel = attn_mma_decode_kernel<STAGES>;
-    const int smem = smem_bytes(STAGES);
+    const int smem = smem_bytes_decode(STAGES);
     if (configure<1>(kernel, smem)) return 0;
     if (size > 8 && cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) != cudaSuccess) {
         cudaGetLastError();
@@ -798,7 +805,7 @@ LLB_API int llb_attn_mma_decode(MmaAttnParams p, int B, cudaStream_t stream) {
     dim3 grid(p.n_splits, p.nkvh * ((G + 15) / 16), B);
     if (grid.y > 65535 || grid.z > 65535) return (int)cudaErrorInvalidValue;
     auto kernel = attn_mma_decode_kernel<STAGES>;
-    const int smem = smem_bytes(STAGES);
+    const int smem = smem_bytes_decode(STAGES);
     int rc = configure<1>(kernel, smem);
     if (rc) return rc;
     if (p.cluster && p.n_splits > 8) {
