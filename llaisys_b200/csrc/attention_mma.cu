@@ -155,6 +155,37 @@ __device__ __forceinline__ void zero_unfetched(uint8_t* stage_ptr, int tile, int
     __syncthreads();
 }
 
+// The same two for the decode kernel, in which warp w owns the key rows [16 w, 16 w + 16) of every tile: it requests
+// them, multiplies with them and requests their successors itself, so its pace depends on no other warp's and the
+// walk over the tiles needs no barrier of the whole block.  (With one barrier in front of and one behind every tile
+// and the requests for a tile shared by all threads, the pass that re-requested a stage took 1,300 cycles longer.)
+__device__ __forceinline__ void issue_tile_rows(const Source& s, int tile, int key_lo, int key_hi, uint32_t stage, int warp, int lane) {
+    constexpr int CH = ROW_BYTES / 16;
+    const int p0 = tile * TILE;
+    const int j_lo = max(0, key_lo - p0), j_hi = min(TILE, key_hi - p0 + 1);
+    const size_t page_off = paged_row(s.table, s.ring, p0, s.kvh, s.nkvh, DH);
+    for (int it = lane; it < 16 * CH; it += 32) {
+        const int j = warp * 16 + it / CH, c = it % CH;
+        if (j < j_lo || j >= j_hi) continue;
+        const size_t off = page_off + (size_t)j * DH;
+        const uint32_t d = stage + j * ROW_STRIDE + c * 16;
+        cp_async16(d, s.kpool + off + c * 8);
+        cp_async16(d + TILE_BYTES, s.vpool + off + c * 8);
+    }
+}
+__device__ __forceinline__ void zero_unfetched_rows(uint8_t* stage_ptr, int tile, int key_lo, int key_hi, int warp, int lane) {
+    const int p0 = tile * TILE;
+    const int j_lo = max(0, key_lo - p0), j_hi = min(TILE, key_hi - p0 + 1);
+    if (j_lo == 0 && j_hi == TILE) return;
+    constexpr int CH = ROW_BYTES / 16;
+    for (int it = lane; it < 16 * CH; it += 32) {
+        const int j = warp * 16 + it / CH, c = it % CH;
+        if (j < j_lo || j >= j_hi)
+            *reinterpret_cast<uint4*>(stage_ptr + TILE_BYTES + j * ROW_STRIDE + c * 16) = make_uint4(0, 0, 0, 0);
+    }
+    __syncwarp();
+}
+
 // Elements d, d+1 of a head's vector after the half-split rotation by the angles of one position
 // (cs, sn: that position's DH/2 cosines and sines), rounded to bfloat16 like the separate kernel does.
 __device__ __forceinline__ uint32_t rotated_pair(const bf16* x, int d, const float* cs, const float* sn) {
@@ -405,7 +436,7 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
     Source src{p.kpool, p.vpool, nullptr, nullptr, p.page_table + (size_t)b * p.table_stride,
                p.ring, p.nkvh, kvh, 0, 0, 0, false};
     for (int i = 0; i < NST; ++i) {
-        if (i < n_tiles) issue_tile(src, tile_lo + i, key_lo, fetch_hi, ring.stage(i), tid);
+        if (i < n_tiles) issue_tile_rows(src, tile_lo + i, key_lo, fetch_hi, ring.stage(i), warp, lane);
         cp_async_commit();                                 // one group per stage, empty or not
     }
     // The ring holds NST tiles; the pages of the block's next two tiles are asked into L2 now, so that their
@@ -467,9 +498,11 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
 
     for (int i = 0; i < n_tiles; ++i) {
         cp_async_wait<NST - 1>();                       // this thread's copies of tile i have landed
-        __syncthreads();                                   // ... and everyone else's
+        __syncwarp();                                      // ... and those of the warp's other lanes: the warp's rows are there
         if (owns_new && tile_lo + i == pos / TILE) {
-            // the new token's row into this tile (and, once per kv head, into the cache)
+            // the new token's row into this tile (and, once per kv head, into the cache).  The one place where the warps
+            // meet: every warp is in this pass, so none still reads what the stage held three passes ago.
+            __syncthreads();
             uint8_t* krow = ring.stage_ptr(i) + (pos % TILE) * ROW_STRIDE;
             const int d = tid * 2;
             if (d < DH) {
@@ -483,10 +516,10 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
             }
             __syncthreads();
         }
-        zero_unfetched(ring.stage_ptr(i), tile_lo + i, key_lo, pos, tid);
+        zero_unfetched_rows(ring.stage_ptr(i), tile_lo + i, key_lo, pos, warp, lane);
         tile_step<2>(qf, o, m, l, ring.stage(i), warp * 16, (tile_lo + i) * TILE, key_lo, pos, key_lo, pos, scale_log2, lane);
-        __syncthreads();                                   // the stage is free
-        if (i + NST < n_tiles) issue_tile(src, tile_lo + i + NST, key_lo, fetch_hi, ring.stage(i + NST), tid);
+        __syncwarp();                                      // the warp's rows of the stage are free
+        if (i + NST < n_tiles) issue_tile_rows(src, tile_lo + i + NST, key_lo, fetch_hi, ring.stage(i + NST), warp, lane);
         cp_async_commit();
     }
     cp_async_wait<0>();
