@@ -159,11 +159,13 @@ __device__ __forceinline__ void zero_unfetched(uint8_t* stage_ptr, int tile, int
 // them, multiplies with them and requests their successors itself, so its pace depends on no other warp's and the
 // walk over the tiles needs no barrier of the whole block.  (With one barrier in front of and one behind every tile
 // and the requests for a tile shared by all threads, the pass that re-requested a stage took 1,300 cycles longer.)
-__device__ __forceinline__ void issue_tile_rows(const Source& s, int tile, int key_lo, int key_hi, uint32_t stage, int warp, int lane) {
+// page_off: where the tile's page begins in the pools (paged_row of its first position), which the caller looks up a
+// pass ahead: the entry comes from global memory, and read here its latency would stand in front of the requests.
+__device__ __forceinline__ void issue_tile_rows(const Source& s, int tile, int key_lo, int key_hi, uint32_t stage, int warp, int lane,
+                                                size_t page_off) {
     constexpr int CH = ROW_BYTES / 16;
     const int p0 = tile * TILE;
     const int j_lo = max(0, key_lo - p0), j_hi = min(TILE, key_hi - p0 + 1);
-    const size_t page_off = paged_row(s.table, s.ring, p0, s.kvh, s.nkvh, DH);
     for (int it = lane; it < 16 * CH; it += 32) {
         const int j = warp * 16 + it / CH, c = it % CH;
         if (j < j_lo || j >= j_hi) continue;
@@ -436,15 +438,18 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
     Source src{p.kpool, p.vpool, nullptr, nullptr, p.page_table + (size_t)b * p.table_stride,
                p.ring, p.nkvh, kvh, 0, 0, 0, false};
     for (int i = 0; i < NST; ++i) {
-        if (i < n_tiles) issue_tile_rows(src, tile_lo + i, key_lo, fetch_hi, ring.stage(i), warp, lane);
+        if (i < n_tiles)
+            issue_tile_rows(src, tile_lo + i, key_lo, fetch_hi, ring.stage(i), warp, lane,
+                            paged_row(src.table, p.ring, (tile_lo + i) * TILE, kvh, p.nkvh, DH));
         cp_async_commit();                                 // one group per stage, empty or not
     }
     // The ring holds NST tiles; the pages of the block's next two tiles are asked into L2 now, so that their
     // copies, which can start only when a stage is free, find them there (a page is contiguous per kv head).
     // Only two: a block with a long walk (large batches) streams at full rate anyway, and asking for all its
     // pages at once was measured to cost 5 % at batch 64.
+    size_t off_ahead = NST < n_tiles ? paged_row(src.table, p.ring, (tile_lo + NST) * TILE, kvh, p.nkvh, DH) : 0;      // page of the first re-request
     for (int i = NST; i < min(n_tiles, NST + 2); ++i) {
-        const size_t off = paged_row(src.table, p.ring, (tile_lo + i) * TILE, kvh, p.nkvh, DH);
+        const size_t off = i == NST ? off_ahead : paged_row(src.table, p.ring, (tile_lo + i) * TILE, kvh, p.nkvh, DH);
         for (int c = tid * 64; c < TILE * DH; c += THREADS * 64) {          // 64 elements = one 128-byte line
             asm volatile("prefetch.global.L2 [%0];" ::"l"(p.kpool + off + c));
             asm volatile("prefetch.global.L2 [%0];" ::"l"(p.vpool + off + c));
@@ -455,6 +460,9 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
     const int qj = tid % HALF, qr0 = tid / HALF;
     float q_co = 1.f, q_si = 0.f;
     if (cs) { q_co = cs[qj]; q_si = sn[qj]; }
+    // every peer's barrier stands (they arrived at their start, as this block did; a cluster's blocks start together):
+    // waited for here, where the block is waiting for the projections anyway, and not in front of the first push
+    if (push_merge) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     if (p.append_new) llb_grid_dependency_sync();          // the projections are read from here on
 
     // the new token's key and value (for the block that owns the last tile): loaded now, used at that tile
@@ -497,6 +505,8 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
     const float scale_log2 = p.scale * 1.4426950408889634f;
 
     for (int i = 0; i < n_tiles; ++i) {
+        const size_t off_now = off_ahead;                  // page of tile i + NST, looked up a pass ago
+        if (i + 1 + NST < n_tiles) off_ahead = paged_row(src.table, p.ring, (tile_lo + i + 1 + NST) * TILE, kvh, p.nkvh, DH);
         cp_async_wait<NST - 1>();                       // this thread's copies of tile i have landed
         __syncwarp();                                      // ... and those of the warp's other lanes: the warp's rows are there
         if (owns_new && tile_lo + i == pos / TILE) {
@@ -519,7 +529,7 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
         zero_unfetched_rows(ring.stage_ptr(i), tile_lo + i, key_lo, pos, warp, lane);
         tile_step<2>(qf, o, m, l, ring.stage(i), warp * 16, (tile_lo + i) * TILE, key_lo, pos, key_lo, pos, scale_log2, lane);
         __syncwarp();                                      // the warp's rows of the stage are free
-        if (i + NST < n_tiles) issue_tile_rows(src, tile_lo + i + NST, key_lo, fetch_hi, ring.stage(i + NST), warp, lane);
+        if (i + NST < n_tiles) issue_tile_rows(src, tile_lo + i + NST, key_lo, fetch_hi, ring.stage(i + NST), warp, lane, off_now);
         cp_async_commit();
     }
     cp_async_wait<0>();
@@ -560,7 +570,6 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
         asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
         const uint32_t recv = ring.base + NST * STAGE_BYTES + QS_BYTES + 16;     // [S][share4] float4, then [S][16] (maximum, sum)
         const uint32_t ml_off = (uint32_t)(S * share4 * 16);
-        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");      // every peer's barrier stands
         for (int i4 = tid; i4 < n_heads * (DH / 4); i4 += THREADS) {
             const int r = i4 / (DH / 4), d4 = i4 - r * (DH / 4);
             float mw[4], M = -INFINITY;
