@@ -252,10 +252,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             if (DUAL) tma_load_2d(dst + S::A_BYTES, &map_w, bar_full + 8 * i, (kb0 + i) * BK, m0 + g.dual_offset, HINT_EVICT_FIRST);
         }
     }
-    llb_grid_dependency_sync();      // from here on memory written by earlier kernels is touched
     // The peers of a cluster start together and arrived before this point in their own code: the wait that must
-    // precede the first push into a buffer of its own costs nothing here, and is off the epilogue.
+    // precede the first push into a buffer of its own is done here, where the block waits for its input anyway (even
+    // satisfied it costs some hundred cycles, which behind the grid dependency would be on the step's critical path).
     if (push && S::OWN_RECV) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    llb_grid_dependency_sync();      // from here on memory written by earlier kernels is touched
 
     if (warp == 0) {
         if (lane == 0) {
