@@ -220,6 +220,62 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const bf16* __restrict__ de
     }
 }
 
+// The same once more for many rows (prefill): a warp owns a row, a lane G groups of eight columns 256 columns apart, so
+// a row needs no barrier of the block and no shared memory, every load of a lane is in flight at once, and eight rows
+// share a block (a block per row is 2,048 blocks of which a quarter run as a second, partial wave).
+template <int G>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_warp_kernel(float* __restrict__ residual, const bf16* __restrict__ delta, int n_part, size_t part_stride,
+                        const bf16* __restrict__ weight, bf16* __restrict__ out, int R, int H, float eps) {
+    const int lane = threadIdx.x & 31, r = blockIdx.x * 8 + (threadIdx.x >> 5);
+    uint4 w[G];
+#pragma unroll
+    for (int i = 0; i < G; ++i) w[i] = *reinterpret_cast<const uint4*>(weight + (lane + i * 32) * 8);      // depends on no earlier kernel
+    llb_grid_dependency_sync();
+    if (r >= R) return;
+    float* res = residual + (size_t)r * H;
+    float x[G][8];
+#pragma unroll
+    for (int i = 0; i < G; ++i) {
+        const int c = (lane + i * 32) * 8;
+        const float4 a = *reinterpret_cast<const float4*>(res + c), b = *reinterpret_cast<const float4*>(res + c + 4);
+        x[i][0] = a.x; x[i][1] = a.y; x[i][2] = a.z; x[i][3] = a.w; x[i][4] = b.x; x[i][5] = b.y; x[i][6] = b.z; x[i][7] = b.w;
+    }
+    if (delta) {
+#pragma unroll
+        for (int i = 0; i < G; ++i) {
+            const int c = (lane + i * 32) * 8;
+            float d[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int q = 0; q < n_part; ++q) {
+                const uint4 v = *reinterpret_cast<const uint4*>(delta + q * part_stride + (size_t)r * H + c);
+                const bf16* e8 = reinterpret_cast<const bf16*>(&v);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) d[e] += to_f32(e8[e]);
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) x[i][e] += d[e];
+            *reinterpret_cast<float4*>(res + c) = make_float4(x[i][0], x[i][1], x[i][2], x[i][3]);
+            *reinterpret_cast<float4*>(res + c + 4) = make_float4(x[i][4], x[i][5], x[i][6], x[i][7]);
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < G; ++i)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += x[i][e] * x[i][e];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+    for (int i = 0; i < G; ++i) {
+        const bf16* w8 = reinterpret_cast<const bf16*>(&w[i]);
+        uint4 o;
+        bf16* o8 = reinterpret_cast<bf16*>(&o);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) o8[e] = from_f32<bf16>(x[i][e] * to_f32(w8[e]) * inv);
+        *reinterpret_cast<uint4*>(out + (size_t)r * H + (lane + i * 32) * 8) = o;
+    }
+}
+
 template <typename TD, typename TW>
 static int add_rmsnorm_out(float* residual, const void* delta, int n_part, size_t part_stride,
                            const void* weight, void* out, int out_dtype, const int* rows, int R,
@@ -250,6 +306,16 @@ LLB_API int llb_add_rmsnorm(float* residual, const void* delta, int delta_dtype,
     if ((!delta || delta_dtype == LLB_BF16) && weight_dtype == LLB_BF16 && (!out || out_dtype == LLB_BF16) && H % 8 == 0 &&
         H <= 8192 && part_stride % 8 == 0 &&
         !(((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15)) {
+        // many whole rows, a width of G * 256 columns: a warp per row
+        if (R >= 256 && !rows && out && write_back && H % 256 == 0 && H <= 4096) {
+#define LLB_NW(G) case G: llb_launch(add_rmsnorm_warp_kernel<G>, dim3((R + 7) / 8), dim3(256), 0, stream, residual, (const bf16*)delta, \
+                                     n_part, (size_t)part_stride, (const bf16*)weight, (bf16*)out, R, H, eps); return llb_status()
+            switch (H / 256) {
+                LLB_NW(1); LLB_NW(2); LLB_NW(3); LLB_NW(4); LLB_NW(5); LLB_NW(6); LLB_NW(7); LLB_NW(8);
+                LLB_NW(9); LLB_NW(10); LLB_NW(11); LLB_NW(12); LLB_NW(13); LLB_NW(14); LLB_NW(15); LLB_NW(16);
+            }
+#undef LLB_NW
+        }
 #define LLB_NV(G) llb_launch(add_rmsnorm_vec_kernel<G>, dim3(R), dim3(256), 0, stream, residual, (const bf16*)delta, n_part, \
                              (size_t)part_stride, (const bf16*)weight, (bf16*)out, rows, H, eps, write_back)
         if (H <= 2048) LLB_NV(1);

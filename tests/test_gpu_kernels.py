@@ -51,7 +51,8 @@ def test_embedding(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("T,H", [(1, 8), (5, 200), (37, 1536), (3, 5000), (4, 3584), (2, 8192), (3, 1001)])
+@pytest.mark.parametrize("T,H", [(1, 8), (5, 200), (37, 1536), (3, 5000), (4, 3584), (2, 8192), (3, 1001),
+                                 (300, 1536), (257, 256), (261, 3584), (256, 4096), (300, 5120)])       # many rows: a warp per row where the width allows
 def test_add_rmsnorm(dtype, T, H):
     from llaisys_b200 import kernels
     rng = np.random.default_rng(T * H)
