@@ -41,7 +41,7 @@ constexpr int BK = 64;          // k elements of a stage: one 128-byte swizzled 
 constexpr int SLICE = 64;       // columns of the intermediate dimension per slice
 constexpr int BM = 128;         // rows of a UMMA tile
 constexpr int UMMA_K = 16;
-constexpr int THREADS = 192;
+constexpr int THREADS = 224;       // warp 0 copies, 1 issues, 2-5 epilogue, 6 hands finished tiles to the copy engine
 constexpr int MAX_MT = 32;      // output row tiles of the down projection (tensor memory holds 30 of 16 columns beside the two D1 buffers)
 #ifndef LLB_WAIT_LIMIT
 #define LLB_WAIT_LIMIT (1u << 22)
@@ -338,7 +338,7 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
             }
         }
         __syncwarp();
-    } else if (my_slices > 0) {
+    } else if (warp < 6 && my_slices > 0) {
         // ---------------------------------------------------------------- epilogue (warps 2-5)
         const int q = warp & 3;                            // the quarter of the tensor-memory lanes this warp may read
         const int row = q * 32 + lane;                     // accumulator row: 0-63 gate of column `row`, 64-127 up of column row - 64
@@ -387,12 +387,15 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
         // ---- the block's partial [T, H] of the down projection, added to the residual stream, tile by tile while the
         // rest of Wd is still streaming.  In the last slice every output tile of 128 rows is final as soon as its
         // tensor-core operations complete.  The four warps copy it from tensor memory into a staging buffer laid out as
-        // the rows lie in global memory ([token][128]; two buffers take turns), and one thread hands the tile to the copy
+        // the rows lie in global memory ([token][128]; two buffers take turns), and warp 6 hands the tile to the copy
         // engine as one tensor reduction (cp.reduce.async.bulk.tensor ... add), which the L2 applies a sector at a time.
         // Measured on the way here: scalar atomics from every thread took 3.6 us at the end of the kernel (1.7 million
         // float adds that reach the L2 one by one); bulk reductions of whole token rows issued after the last tile 2 to
         // 3 us; one bulk reduction per token and tile (96 a block at 8 tokens) were slower still, a reduction costs per
         // operation more than per byte.  Spread over the tiles, one operation each, they hide behind the weight stream.
+        // With one of these threads also issuing the reductions, a buffer was handed back only after the next tile's
+        // reduction had been issued: staging, hand-over and issue of a tile ran one after the other, 370 ns a tile against
+        // 230 ns between the tiles' arrivals, and the last reduction left 1.8 us after the last tile's products.
         bool go = ok && !s_abort;
         for (int m = 0; m < g.n_mt; ++m) {
             const int buf = m & 1;
@@ -413,24 +416,28 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
                 if (n < g.T) stage[n * BM + row] = v[n];
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");       // these writes -> the copy engine's reads
             mbar_arrive(bar_staged + 8 * buf);
-            if (warp == 2 && lane == 0) {
-                if (!mbar_wait(bar_staged + 8 * buf, par, &s_abort)) {
-                    if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_MLP_D2); }
-                    break;
-                }
-                if (m == 0) pdl_wait();                    // the residual stream was last written by a kernel before this one
+        }
+    } else if (warp == 6 && my_slices > 0) {
+        // ---------------------------------------------------------------- staged output tiles -> the copy engine
+        for (int m = 0; m < g.n_mt; ++m) {
+            const int buf = m & 1;
+            if (!warp_wait(bar_staged + 8 * buf, (uint32_t)(m >> 1) & 1u, &s_abort)) {
+                if (lane == 0 && !s_abort) { s_abort = 1; atomicExch(g.err, ERR_MLP_D2); }
+                break;
+            }
+            if (m == 0) pdl_wait();                        // the residual stream was last written by a kernel before this one
+            if (lane == 0) {                               // one and the same thread: the copies' groups are its own
                 // one reduction for the whole tile: the box is [BN tokens][128 rows of the output]; what lies beyond the
                 // step's T tokens or the matrix's H columns is clipped by the copy engine
                 asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
-                             ::"l"(&map_res), "r"(m * BM), "r"(0), "r"(smem_u32(stage)) : "memory");
+                             ::"l"(&map_res), "r"(m * BM), "r"(0), "r"(base + (uint32_t)(S::EXCH_OFFSET + buf * S::EXCH_BYTES)) : "memory");
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-                if (m > 0) {                               // the tile before this one has been read: its buffer is free
-                    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-                    mbar_arrive(bar_unstaged + 8 * (buf ^ 1));
-                }
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");      // the tile has been read: its buffer is free
+                mbar_arrive(bar_unstaged + 8 * buf);
+                if (m == g.n_mt - 1) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");      // the sums have reached memory
             }
+            __syncwarp();
         }
-        if (warp == 2 && lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");     // the sums have reached memory
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
