@@ -434,10 +434,11 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");      // the tile has been read: its buffer is free
                 mbar_arrive(bar_unstaged + 8 * buf);
-                if (m == g.n_mt - 1) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");      // the sums have reached memory
             }
             __syncwarp();
         }
+        // the sums have reached memory (also after an early stop: no copy may still read this block's shared memory)
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
