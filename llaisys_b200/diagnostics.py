@@ -100,9 +100,10 @@ class KernelTimers:
     def table(self, reset: bool = True) -> str:
         rep = self.report(reset)
         total = sum(ms for _, ms in rep.values()) or 1.0
-        lines = [f"{'kernel class':<28}{'launches':>10}{'ms':>12}{'share':>9}"]
+        width = max([len(k) for k in rep] + [12]) + 2
+        lines = [f"{'kernel class':<{width}}{'launches':>10}{'ms':>12}{'share':>9}"]
         for k, (n, ms) in rep.items():
-            lines.append(f"{k:<28}{n:>10}{ms:>12.3f}{100 * ms / total:>8.1f}%")
+            lines.append(f"{k:<{width}}{n:>10}{ms:>12.3f}{100 * ms / total:>8.1f}%")
         return "\n".join(lines)
 
 
