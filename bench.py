@@ -257,6 +257,60 @@ def timeline_run(args, model, cfg, rng) -> int:
     return 0
 
 
+STAMP_NAMES = {
+    "gemm": ("gemm_tc.cu", ["set up", "input ready (grid dependency)", "first stage full", "all products issued", "accumulator ready",
+                            "own partial rows pushed", "peers' partial rows received", "end"]),
+    "attention": ("attention_mma.cu", ["set up", "projections ready (grid dependency)", "queries staged", "tiles walked",
+                                       "warps' sums in shared memory", "merged pieces pushed", "peers' pieces received", "stored"]),
+    "mlp": ("mlp_tc.cu", ["-", "activations ready (grid dependency)", "first tile of Wd issued", "last tile of Wd issued",
+                          "last reduction issued", "reductions complete", "end"]),
+}
+
+
+def stamps_run(args, model, cfg, rng) -> int:
+    """Cycle stamps from inside one kernel of the decode step, in its place in the step (replayed from its CUDA graph):
+    per stamp the minimum, median and maximum over the kernel's blocks, in SM cycles after the block saw its grid
+    dependency resolve.  A block's stamps come from one thread's clock64(), so differences within a block are exact;
+    the stamps themselves cost some cycles each."""
+    import numpy as np
+    import torch
+
+    from llaisys_b200.cache import CacheConfig
+    from llaisys_b200.engine import Engine, StepEntry
+    from llaisys_b200.kernels import ops
+
+    B = args.batch
+    engine = Engine(model, CacheConfig(max_tokens=B * CONTEXT, max_seqs=B))
+    slots = filled_slots(engine, B, rng, cfg.vocab_size)
+
+    def steps(n):
+        for _ in range(n):
+            engine.step([StepEntry(s, [int(rng.integers(0, cfg.vocab_size))], [0]) for s in slots])
+
+    steps(SETTLE_STEPS)
+    source, names = STAMP_NAMES[args.stamps]
+    blocks = 0
+    if args.stamps == "gemm":                      # the q/k/v product's grid, of all the launches of that module in a step
+        n_qkv = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
+        bn, splits = ops.tc_plan(B, n_qkv, cfg.hidden_size, engine.sm_count)
+        blocks = -(-n_qkv // 128) * -(-B // bn) * splits
+    buf = torch.zeros((1 << 16, 16), dtype=torch.int64, device="cuda:0")
+    ops.set_stamps(source, buf, blocks)
+    steps(8)
+    torch.cuda.synchronize()
+    ops.set_stamps(source, None)
+    engine.check()
+    st = buf.cpu().numpy().astype(np.float64)
+    st = st[st[:, 1] != 0]
+    print(f"{args.stamps}: {len(st)} blocks of the last launch that stamped; SM cycles after the grid dependency resolved (batch {B})")
+    for i, name in enumerate(names):
+        if name == "-" or not (st[:, i] != 0).any():
+            continue
+        col = (st[:, i] - st[:, 1])[st[:, i] != 0]
+        print(f"  {name:36s} min {col.min():8.0f}   median {np.median(col):8.0f}   max {col.max():8.0f}")
+    return 0
+
+
 def products_run(args, cfg) -> int:
     """The four matrix products of a layer timed alone at --tokens tokens, with every kernel that takes them:
     the one-CTA tcgen05 kernel and, for more than 256 tokens, the paired-SM kernel (which the library chooses)."""
@@ -520,11 +574,17 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=None,
                     help="for measurements beside the reported one: tokens every sequence holds before decoding, and tokens of "
                          "the timed prefill step (default 2,048; the cache is sized for twice as many per sequence)")
+    ap.add_argument("--stamps", choices=["gemm", "attention", "mlp"], default=None,
+                    help="cycle stamps from inside one kernel of the decode step (the q/k/v product, decode attention or the "
+                         "one-launch feed-forward), in its place in the step replayed from its CUDA graph; builds that kernel "
+                         "with -DLLB_STAMPS=1")
     ap.add_argument("--timeline", choices=["decode", "prefill"], default=None,
                     help="print the per-kernel timeline of a step (torch.profiler, no ncu) instead of measuring")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.stamps:
+        os.environ["LLAISYS_STAMPS"] = "1"           # read when the package is imported, below
     if args.gpus != 1:
         print(f"bench.py: llaisys_b200 is a single-GPU library; --gpus {args.gpus} is not supported (use --gpus 1)")
         return 2
@@ -572,6 +632,8 @@ def main() -> int:
         return profile_run(args, model, cfg, rng)
     if args.timeline:
         return timeline_run(args, model, cfg, rng)
+    if args.stamps:
+        return stamps_run(args, model, cfg, rng)
     if args.workload == "own":
         return own_workload(args, model, cfg, cfg_dict, layers, full_layers, shape_name, pk, pk_src, rng)
 

@@ -463,7 +463,9 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
     // every peer's barrier stands (they arrived at their start, as this block did; a cluster's blocks start together):
     // waited for here, where the block is waiting for the projections anyway, and not in front of the first push
     if (push_merge) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (tid == 0) LLB_STAMP(0);       // stamps: 0 set up, 1 projections ready (grid dependency), 2 queries staged, 3 tiles walked,
     if (p.append_new) llb_grid_dependency_sync();          // the projections are read from here on
+    if (tid == 0) LLB_STAMP(1);       //         4 warps' sums in shared memory, 5 merged pieces pushed, 6 peers' pieces received, 7 stored
 
     // the new token's key and value (for the block that owns the last tile): loaded now, used at that tile
     const bool owns_new = p.append_new && n_tiles > 0 && tile_hi - 1 == pos / TILE;
@@ -497,6 +499,7 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
         }
     }
     __syncthreads();
+    if (tid == 0) LLB_STAMP(2);
     uint32_t qf[KSTEPS][4];
     load_q(qf, [&](int r) -> const bf16* { return qs + r * (DH + 8); }, lane);
     float o[DTILES][4], m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
@@ -534,6 +537,7 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
     }
     cp_async_wait<0>();
     __syncthreads();
+    if (tid == 0) LLB_STAMP(3);
 
     // ---- merge the four warps (each saw a quarter of the keys) through shared memory
     float* sm_ml = reinterpret_cast<float*>(ring.ptr);               // [4][16][2]
@@ -556,6 +560,7 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
         }
     }
     __syncthreads();
+    if (tid == 0) LLB_STAMP(4);
     if (push_merge) {
         // ---- merge of the key slices by pushing.  The four warps' partial sums are merged 16 bytes at a time and each
         // piece goes straight from the registers to the block that owns it (block q owns the q-th share of the
@@ -602,6 +607,7 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
                 }
             }
         }
+        if (tid == 0) LLB_STAMP(5);
         // ---- all blocks' pieces (bounded wait)
         bool got = false;
         for (uint32_t t = 0; t < MERGE_WAIT_LIMIT && !got; ++t) {
@@ -614,6 +620,7 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
             if (p.err) atomicExch(p.err, ERR_ATTN_MERGE_WAIT);
             return;
         }
+        if (tid == 0) LLB_STAMP(6);
         // ---- this block's share: every source scaled to the common base, added, divided, stored
         const uint8_t* rp = ring.ptr + NST * STAGE_BYTES + QS_BYTES + 16;
         const float2* rml = reinterpret_cast<const float2*>(rp + ml_off);
@@ -631,6 +638,7 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
             }
             out_tok[idx] = __float2bfloat16_rn(acc / L);
         }
+        if (tid == 0) LLB_STAMP(7);
         return;
     }
     // merged over the four warps: fin_ml [16][2], fin_o [16][DH] (kept in shared memory for the cluster merge)
@@ -838,6 +846,8 @@ LLB_API int llb_attn_mma_decode_max_clusters(int size) {
     }
     return n;
 }
+
+LLB_DEFINE_SET_STAMPS
 
 LLB_API int llb_attn_mma_decode(MmaAttnParams p, int B, cudaStream_t stream) {
     if (B == 0) return 0;

@@ -158,6 +158,11 @@ DEFAULT_MODULES = [
 ]
 
 
+# Builds with cycle stamps (bench.py --stamps): the three kernels of a decode step that carry them.
+STAMP_MODULES = [("gemm_tc.cu", {"LLB_STAMPS": 1}), ("mlp_tc.cu", {"LLB_STAMPS": 1}),
+                 ("attention_mma.cu", {"LLB_HEAD_DIM": 128, "LLB_STAMPS": 1})]
+
+
 def build_all(modules=None, jobs: int | None = None) -> list[Path]:
     from concurrent.futures import ThreadPoolExecutor
     modules = modules or DEFAULT_MODULES

@@ -23,6 +23,32 @@ template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
 
+// ---- cycle stamps: a build with -DLLB_STAMPS=1 records clock64() at a few places of a kernel, per block, so that
+// the inside of a short kernel can be read while it runs in its real place in a step (python bench.py --stamps ...).
+// llb_set_stamps(buffer, blocks) switches them on for launches of exactly `blocks` blocks (a module's kernels are
+// launched with several grids in a step; 0: every launch; the buffer holds LLB_STAMP_SLOTS values for every block of the
+// largest launch that stamps); a null buffer switches them off.  Without the definition the macro is empty and the kernels are what they are without it.
+#ifdef LLB_STAMPS
+constexpr int LLB_STAMP_SLOTS = 16;
+static __device__ long long* llb_stamps_buf = nullptr;
+static __device__ unsigned int llb_stamps_blocks = 0;
+#define LLB_STAMP(i)                                                                                                  \
+    do {                                                                                                              \
+        const long long llb_t = clock64();          /* read first: the switch below is two loads from global memory */  \
+        if (llb_stamps_buf && (llb_stamps_blocks == 0 || gridDim.x * gridDim.y * gridDim.z == llb_stamps_blocks))    \
+            llb_stamps_buf[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * LLB_STAMP_SLOTS + (i)] = llb_t; \
+    } while (0)
+#define LLB_DEFINE_SET_STAMPS                                                                                         \
+    LLB_API int llb_set_stamps(long long* buf, unsigned int blocks) {                                                  \
+        cudaError_t e = cudaMemcpyToSymbol(llb_stamps_blocks, &blocks, sizeof(blocks));                               \
+        if (e == cudaSuccess) e = cudaMemcpyToSymbol(llb_stamps_buf, &buf, sizeof(buf));                              \
+        return (int)e;                                                                                                \
+    }
+#else
+#define LLB_STAMP(i) do { } while (0)
+#define LLB_DEFINE_SET_STAMPS
+#endif
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -256,7 +256,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // precede the first push into a buffer of its own is done here, where the block waits for its input anyway (even
     // satisfied it costs some hundred cycles, which behind the grid dependency would be on the step's critical path).
     if (push && S::OWN_RECV) asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (tid == 64) LLB_STAMP(0);      // stamps: 0 set up, 1 input ready (grid dependency), 2 first stage full, 3 all products issued,
     llb_grid_dependency_sync();      // from here on memory written by earlier kernels is touched
+    if (tid == 64) LLB_STAMP(1);      //         4 accumulator ready, 5 epilogue's own part done, 6 peers' partial rows received, 7 end
 
     if (warp == 0) {
         if (lane == 0) {
@@ -301,6 +303,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 break;
             }
             if (elect_one()) {
+                if (kb == kb0) LLB_STAMP(2);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint64_t so = (uint64_t)(s * (S::STAGE_BYTES >> 4));
 #pragma unroll
@@ -315,7 +318,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             __syncwarp();
             if (++s == STAGES) { s = 0; ph ^= 1u; }
         }
-        if (elect_one()) umma_commit(bar_acc);       // accumulator complete (arrives even after an early stop)
+        if (elect_one()) {
+            LLB_STAMP(3);
+            umma_commit(bar_acc);                    // accumulator complete (arrives even after an early stop)
+        }
         __syncwarp();
     }
 
@@ -323,6 +329,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     bool ok = mbar_wait(bar_acc, 0, &s_abort);
     if (!ok && !s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC_WAIT_ACC); }
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    if (tid == 64) LLB_STAMP(4);
     __syncthreads();
     const bool aborted = s_abort != 0;
     const int m = m0 + tid;                                   // this thread's weight row (output column)
@@ -515,7 +522,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // the bias of this thread's first output piece is asked for before the wait for the peers
         float bias_first = 0.f;
         if (!aborted && tid < R * groups && m0 + (int)rank * R + tid % R < limit) bias_first = bias_of(m0 + (int)rank * R + tid % R);
+        if (tid == 64) LLB_STAMP(5);
         bool got = mbar_wait(bar_recv, 0, &s_abort);
+        if (tid == 64) LLB_STAMP(6);
         if (!got && !s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC_WAIT_RECV); }
         if (got && !aborted) {
             const float4* rb = reinterpret_cast<const float4*>(gen_base + (S::OWN_RECV ? S::RECV_OFFSET : 0));
@@ -544,6 +553,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             }
         }
     }
+    if (tid == 64) LLB_STAMP(7);
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) {
@@ -594,6 +604,8 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const GemmArgs& g, dim3
 }
 
 }  // namespace
+
+LLB_DEFINE_SET_STAMPS
 
 // float32 elements of scratch a launch needs (0 when splits == 1).
 static long long llb_gemm_tc_scratch_elems(int T, int N, int bn, int splits, int dual) {

@@ -233,6 +233,8 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
             }
             __syncwarp();
             pdl_wait();                                    // the activations are the previous kernel's output
+            if (lane == 0) LLB_STAMP(1);                   // stamps: 1 activations ready (grid dependency), 2 first tile of Wd issued,
+                                                           //         3 last tile issued, 4 last reduction issued, 5 reductions complete, 6 end
             if (elect_one()) {
                 for (int i = 0; i < pre; ++i)
                     tma_load_2d(base + i * S::STAGE_BYTES + S::A_BYTES, &map_x, bar_full + 8 * i, i * BK, 0, HINT_EVICT_LAST);
@@ -331,6 +333,8 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
                                  act_desc0 + (uint64_t)((k * UMMA_K * 2) >> 4), idesc, (sl > 0 || k > 0) ? 1u : 0u);
                         umma_commit(bar_empty + 8 * s);
                         if (sl == my_slices - 1) umma_commit(bar_tile + 8 * m);            // this output tile is final
+                        if (sl == my_slices - 1 && m == 0) LLB_STAMP(2);
+                        if (sl == my_slices - 1 && m == g.n_mt - 1) LLB_STAMP(3);
                     }
                     __syncwarp();
                     if (++s == STAGES) { s = 0; ph ^= 1u; }
@@ -438,10 +442,15 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
             __syncwarp();
         }
         // the sums have reached memory (also after an early stop: no copy may still read this block's shared memory)
-        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        if (lane == 0) {
+            LLB_STAMP(4);
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+            LLB_STAMP(5);
+        }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (tid == 0) LLB_STAMP(6);
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)g.tmem_cols) : "memory");
     }
@@ -477,6 +486,8 @@ LLB_API int llb_mlp_fused_ok(int T, int H, int I) {
 // X [T, H] bf16 (row stride ldx), Wgu [2 I, H] bf16 dense (gate rows first), Wd [H, I] bf16 dense;
 // residual [T, H] float32 dense += the feed-forward of X.  blocks: the most blocks to launch (the SM count).
 // stages: depth of the TMA ring (4, 5, 6, 8, and 10 for up to 16 tokens; 0 chooses).
+LLB_DEFINE_SET_STAMPS
+
 LLB_API int llb_mlp_fused(const void* X, int ldx, const void* Wgu, const void* Wd, float* residual, int T, int H, int I,
                           int blocks, int stages, int* err, cudaStream_t stream) {
     if (!llb_mlp_fused_ok(T, H, I) || ldx % 8 || blocks <= 0) return (int)cudaErrorInvalidValue;

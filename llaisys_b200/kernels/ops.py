@@ -55,6 +55,33 @@ def _lib_basic():
 
 _launches = 0
 
+# LLAISYS_STAMPS=1: the three kernels of a decode step that can record cycle stamps (see csrc/common.cuh) are built
+# with them; set_stamps() then switches them on for launches of a given grid size.  Off by default: the product's
+# builds contain no stamp.
+_STAMPS = {"LLB_STAMPS": 1} if __import__("os").environ.get("LLAISYS_STAMPS", "0") not in ("", "0") else {}
+_stamp_libs = {}
+
+
+def _stamped(source: str, defines: Optional[dict] = None):
+    lib = load_module(source, {**(defines or {}), **_STAMPS} or None)
+    if _STAMPS:
+        _stamp_libs[source] = lib
+    return lib
+
+
+def set_stamps(source: str, buf: Optional[torch.Tensor], blocks: int = 0) -> None:
+    """Cycle stamps of the kernels of `source` ("gemm_tc.cu", "attention_mma.cu", "mlp_tc.cu") into `buf` (int64
+    [blocks, 16] on the device) for launches of exactly `blocks` blocks; None switches them off.  Needs
+    LLAISYS_STAMPS=1 in the environment before the package is imported, and the module in use already."""
+    lib = _stamp_libs.get(source)
+    if lib is None:
+        raise KernelError(f"no stamped build of {source} is loaded (LLAISYS_STAMPS=1, and run a step first)")
+    lib.llb_set_stamps.argtypes = [c_void_p, ctypes.c_uint]
+    lib.llb_set_stamps.restype = c_int
+    rc = lib.llb_set_stamps(_ptr(buf), blocks)
+    if rc:
+        raise KernelError(f"llb_set_stamps: CUDA error {rc}")
+
 
 def launch_count() -> int:
     """Kernels of this package launched so far by this process (a captured launch counts once,
@@ -337,7 +364,7 @@ def _gemm_tc(x, weight, bias, out, dual_offset=0, plan=None):
     plan = plan or tc_plan(M, dual_offset or N, K, _sm_count(x.device), bool(dual_offset))
     bn, splits = plan[0], plan[1]
     cluster = plan[2] if len(plan) > 2 else 1            # (bn, splits, 0) forces the reduction through scratch
-    f = _fn(load_module("gemm_tc.cu"), "llb_gemm_tc",
+    f = _fn(_stamped("gemm_tc.cu"), "llb_gemm_tc",
             [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
              c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p])
     _check(f(_ptr(x), _ptr(weight), _ptr(bias), _dt(bias) if bias is not None else 0, _ptr(out), _dt(out),
@@ -399,7 +426,7 @@ def linear_into(x: torch.Tensor, weight: torch.Tensor, bias, stream: torch.Tenso
     err = _tc_resources(x.device)[2]
     if T <= 256:
         bn, splits = into_plan(T, N, K, _sm_count(x.device))
-        f = _fn(load_module("gemm_tc.cu"), "llb_gemm_tc_into",
+        f = _fn(_stamped("gemm_tc.cu"), "llb_gemm_tc_into",
                 [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
         _check(f(_ptr(x), _ptr(weight), _ptr(bias), _dt(bias) if bias is not None else 0, _ptr(stream), T, N, K, x.stride(0),
                  stream.stride(0), bn, ksplit or splits, _ptr(err), _stream()), "linear into the residual stream (tensor cores)")
@@ -441,7 +468,7 @@ def mlp_fused_ok(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, res
     I = down.shape[1]
     if gate_up.shape != (2 * I, H) or down.shape != (H, I) or residual.shape != (T, H):
         return False
-    f = load_module("mlp_tc.cu", _MLP_DEFINES).llb_mlp_fused_ok
+    f = _stamped("mlp_tc.cu", _MLP_DEFINES).llb_mlp_fused_ok
     f.argtypes, f.restype = [c_int, c_int, c_int], c_int
     return bool(f(T, H, I))
 
@@ -454,7 +481,7 @@ def mlp_fused(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, residu
     I = down.shape[1]
     err = _tc_resources(x.device)[2]
     stages = stages or _MLP_STAGES
-    f = _fn(load_module("mlp_tc.cu", _MLP_DEFINES), "llb_mlp_fused",
+    f = _fn(_stamped("mlp_tc.cu", _MLP_DEFINES), "llb_mlp_fused",
             [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(f(_ptr(x), x.stride(0), _ptr(gate_up), _ptr(down), _ptr(residual), T, H, I, _sm_count(x.device), stages,
              _ptr(err), _stream()), "feed-forward (one launch, tensor cores)")
@@ -531,7 +558,8 @@ def require_head_dim(dh: int) -> None:
 
 
 def _mma_lib(dh: int):
-    return load_module("attention_mma.cu", {"LLB_HEAD_DIM": dh})
+    lib = _stamped("attention_mma.cu", {"LLB_HEAD_DIM": dh})
+    return lib
 
 
 def _attn_lib(dh: int):

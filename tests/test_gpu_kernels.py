@@ -644,3 +644,33 @@ def test_linear_into_the_residual_stream_on_paired_sms(T, N, K, ksplit):
         want = s0.double().cpu().numpy() + 2 * (prod + (b.double().cpu().numpy() if bias is not None else 0.0))
         _tc_check(stream, want, 4 * K)
     assert kernels.tc_error(DEV) == 0
+
+
+def test_stamped_build_gives_the_same_product_and_ordered_stamps(monkeypatch):
+    """A build with cycle stamps (the tool behind `bench.py --stamps`) is the same kernel: equal results, and the
+    stamps that one thread of a block takes rise in the order of their places."""
+    from llaisys_b200 import kernels
+    from llaisys_b200.kernels import ops
+    x, w, b = _tc_case(8, 2048, 1536, 5, bias=torch.bfloat16)
+    plain_out = kernels.linear(x, w, b)
+    monkeypatch.setattr(ops, "_STAMPS", {"LLB_STAMPS": 1})
+    bn, splits = ops.tc_plan(8, 2048, 1536, ops._sm_count(DEV))
+    blocks = 16 * splits
+    buf = torch.zeros((blocks, 16), dtype=torch.int64, device=DEV)
+    with pytest.raises(kernels.KernelError):
+        ops.set_stamps("mlp_tc.cu", buf)                      # no stamped build of that module is loaded
+    out0 = kernels.linear(x, w, b)                            # loads the stamped build; stamps still off
+    ops.set_stamps("gemm_tc.cu", buf, blocks)
+    out1 = kernels.linear(x, w, b)
+    kernels.linear(x[:, :512].contiguous(), w[:, :512].contiguous(), b)      # another grid: leaves the stamps alone
+    torch.cuda.synchronize()
+    ops.set_stamps("gemm_tc.cu", None)
+    st = buf.cpu().numpy()
+    kernels.linear(x, w, b)
+    torch.cuda.synchronize()
+    assert torch.equal(out0, plain_out) and torch.equal(out1, plain_out)
+    assert (st[:, :8] > 0).all()
+    # places stamped by one and the same thread come in order: the epilogue's thread (0, 1, 4, 5, 6, 7), the issuing lane (2, 3)
+    assert (np.diff(st[:, [0, 1, 4, 5, 6, 7]], axis=1) > 0).all() and (st[:, 3] > st[:, 2]).all()
+    assert np.array_equal(buf.cpu().numpy(), st)              # switched off: nothing is written any more
+    assert kernels.tc_error(DEV) == 0
