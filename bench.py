@@ -263,15 +263,16 @@ STAMP_NAMES = {
     "attention": ("attention_mma.cu", ["set up", "projections ready (grid dependency)", "queries staged", "tiles walked",
                                        "warps' sums in shared memory", "merged pieces pushed", "peers' pieces received", "stored"]),
     "mlp": ("mlp_tc.cu", ["-", "activations ready (grid dependency)", "first tile of Wd issued", "last tile of Wd issued",
-                          "last reduction issued", "reductions complete", "end"]),
+                          "last reduction issued", "reductions complete"]),
 }
 
 
 def stamps_run(args, model, cfg, rng) -> int:
     """Cycle stamps from inside one kernel of the decode step, in its place in the step (replayed from its CUDA graph):
     per stamp the minimum, median and maximum over the kernel's blocks, in SM cycles after the block saw its grid
-    dependency resolve.  A block's stamps come from one thread's clock64(), so differences within a block are exact;
-    the stamps themselves cost some cycles each."""
+    dependency resolve.  All stamps of a block read one SM's cycle counter.  Stamps that one thread takes are in
+    program order; a stamp is not ordered with another thread's unless data flows between them (the clock read is
+    no memory operation, so a barrier alone does not hold it in place).  A stamp costs a clock read and a store."""
     import numpy as np
     import torch
 

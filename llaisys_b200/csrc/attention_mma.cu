@@ -387,6 +387,7 @@ __global__ void __launch_bounds__(THREADS) attn_mma_decode_kernel(MmaAttnParams 
     extern __shared__ uint8_t smem_raw[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     Ring<NST> ring = make_ring<NST>(smem_raw);
+    LLB_STAMPS_BEGIN();
     // The key slices of a cluster merge by pushing (below) when every block's share of the outputs is whole 16-byte
     // pieces and what it receives fits the receive region.
     const int G_ = p.nh / p.nkvh, chunks_ = (G_ + 15) / 16;

@@ -32,11 +32,23 @@ template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __f
 constexpr int LLB_STAMP_SLOTS = 16;
 static __device__ long long* llb_stamps_buf = nullptr;
 static __device__ unsigned int llb_stamps_blocks = 0;
+// at the top of a kernel: where this block's stamps go (null: nowhere), read once so that a stamp is a clock read and a store
+#define LLB_STAMPS_BEGIN()                                                                                            \
+    long long* llb_sp = nullptr;                                                                                      \
+    {                                                                                                                 \
+        long long* const llb_b = llb_stamps_buf;                                                                      \
+        const unsigned int llb_n = llb_stamps_blocks;                                                                 \
+        if (llb_b && (llb_n == 0 || gridDim.x * gridDim.y * gridDim.z == llb_n))                                      \
+            llb_sp = llb_b + ((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * LLB_STAMP_SLOTS; \
+    }
+// (the clock is read by an instruction that the compiler may not move across the memory operations and barriers around it)
 #define LLB_STAMP(i)                                                                                                  \
     do {                                                                                                              \
-        const long long llb_t = clock64();          /* read first: the switch below is two loads from global memory */  \
-        if (llb_stamps_buf && (llb_stamps_blocks == 0 || gridDim.x * gridDim.y * gridDim.z == llb_stamps_blocks))    \
-            llb_stamps_buf[((size_t)(blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x) * LLB_STAMP_SLOTS + (i)] = llb_t; \
+        if (llb_sp) {                                                                                                 \
+            long long llb_t;                                                                                          \
+            asm volatile("mov.u64 %0, %%clock64;" : "=l"(llb_t) : : "memory");                                       \
+            llb_sp[i] = llb_t;                                                                                        \
+        }                                                                                                             \
     } while (0)
 #define LLB_DEFINE_SET_STAMPS                                                                                         \
     LLB_API int llb_set_stamps(long long* buf, unsigned int blocks) {                                                  \
@@ -45,6 +57,7 @@ static __device__ unsigned int llb_stamps_blocks = 0;
         return (int)e;                                                                                                \
     }
 #else
+#define LLB_STAMPS_BEGIN() do { } while (0)
 #define LLB_STAMP(i) do { } while (0)
 #define LLB_DEFINE_SET_STAMPS
 #endif

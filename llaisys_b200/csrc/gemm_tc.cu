@@ -190,6 +190,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                const __grid_constant__ CUtensorMap map_out, GemmArgs g) {
     using S = Smem<BN, STAGES, DUAL>;
     constexpr int ACCS = DUAL ? 2 : 1;
+    LLB_STAMPS_BEGIN();
     constexpr int TMEM_COLS = (ACCS * BN) <= 32 ? 32 : (ACCS * BN) <= 64 ? 64 : (ACCS * BN) <= 128 ? 128 : (ACCS * BN) <= 256 ? 256 : 512;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -375,6 +376,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");         // before the shared memory is given up
             }
+            __syncwarp();                      // (that thread's warp goes to the block's last barrier together)
         }
     } else if (!aborted) {
         if (g.splits == 1 && g.y_dtype == LLB_BF16 && m0 + BM <= (DUAL ? g.dual_offset : g.N) &&

@@ -431,6 +431,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     }
 
     if (INTO && tid == 64) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");       // the sums have reached memory
+    __syncwarp();                              // (that thread's warp goes to the barrier below together)
     // Neither CTA leaves while the other may still signal its barriers, read its shared memory or write its
     // tensor memory.
     __syncthreads();

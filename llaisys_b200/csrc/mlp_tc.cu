@@ -171,6 +171,7 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
                  const __grid_constant__ CUtensorMap map_res, MlpArgs g) {
     using S = Smem<BN, STAGES>;
     extern __shared__ uint8_t smem_raw[];
+    LLB_STAMPS_BEGIN();
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t bar_full = base + S::BAR_OFFSET, bar_empty = bar_full + 8 * STAGES;
@@ -234,7 +235,7 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
             __syncwarp();
             pdl_wait();                                    // the activations are the previous kernel's output
             if (lane == 0) LLB_STAMP(1);                   // stamps: 1 activations ready (grid dependency), 2 first tile of Wd issued,
-                                                           //         3 last tile issued, 4 last reduction issued, 5 reductions complete, 6 end
+                                                           //         3 last tile issued, 4 last reduction issued, 5 reductions complete
             if (elect_one()) {
                 for (int i = 0; i < pre; ++i)
                     tma_load_2d(base + i * S::STAGE_BYTES + S::A_BYTES, &map_x, bar_full + 8 * i, i * BK, 0, HINT_EVICT_LAST);
@@ -447,10 +448,10 @@ mlp_fused_kernel(const __grid_constant__ CUtensorMap map_gate, const __grid_cons
             asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
             LLB_STAMP(5);
         }
+        __syncwarp();                                      // the warp goes to the block's last barrier together
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
-    if (tid == 0) LLB_STAMP(6);
     if (warp == 1) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"((uint32_t)g.tmem_cols) : "memory");
     }
