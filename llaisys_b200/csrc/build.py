@@ -159,7 +159,7 @@ DEFAULT_MODULES = [
 
 
 # Builds with cycle stamps (bench.py --stamps): the three kernels of a decode step that carry them.
-STAMP_MODULES = [("gemm_tc.cu", {"LLB_STAMPS": 1}), ("mlp_tc.cu", {"LLB_STAMPS": 1}),
+STAMP_MODULES = [("gemm_tc.cu", {"LLB_STAMPS": 1}), ("gemm_tc2.cu", {"LLB_STAMPS": 1}), ("mlp_tc.cu", {"LLB_STAMPS": 1}),
                  ("attention_mma.cu", {"LLB_HEAD_DIM": 128, "LLB_STAMPS": 1})]
 
 

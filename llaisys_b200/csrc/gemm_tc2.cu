@@ -22,7 +22,8 @@
 //               leader CTA's barrier
 //   warp 1      tcgen05.mma issue (one thread of the leader CTA); tcgen05.commit multicast frees the ring
 //               slot in both CTAs and, per tile, hands the accumulator to both epilogues
-//   warps 2-9   epilogue of this CTA's 128 rows: two warps per 32 rows, each with half of the columns
+//   warps 2-17  epilogue of this CTA's 128 rows: four warps per 32 rows, each with 8 of every 32 columns, transposed
+//               through a buffer of the warp's own (no barrier among the epilogue warps)
 //
 // INTO (an instantiation of its own): the product is not stored but added to a float32 stream [T, N]
 // (the residual stream: an output projection or a down projection that ends in the residual add of
@@ -43,9 +44,11 @@ namespace {
 constexpr int BM = 128;        // weight rows of one CTA (half of the pair's UMMA M)
 constexpr int BK = 64;         // k elements of a stage: one 128-byte swizzled row of bf16
 constexpr int UMMA_K = 16;
-constexpr int THREADS = 320;
-constexpr int EPI_THREADS = 256;
-constexpr int CHUNK = 32;      // tokens that the epilogue transposes at a time
+constexpr int EPI_SHARE = 4;                       // epilogue warps that share 32 rows (a quarter of tensor memory's lanes)
+constexpr int EPI_THREADS = 128 * EPI_SHARE;
+constexpr int THREADS = 64 + EPI_THREADS;
+constexpr int CHUNK = 32;                          // tokens that the epilogue transposes at a time
+constexpr int COLS = CHUNK / EPI_SHARE;            // of which a warp takes this many
 constexpr uint32_t WAIT_LIMIT = 1u << 22;
 
 constexpr uint64_t HINT_EVICT_FIRST = 0x12F0000000000000ull;
@@ -67,7 +70,7 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
 }
 // arrival on a barrier of any CTA of the cluster (a shared::cluster address)
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_bar) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_bar) : "memory");
 }
 __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
     uint32_t done;
@@ -147,6 +150,24 @@ __device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t* r) {
         : "r"(taddr) : "memory");
 }
 
+// the same for COLS (8 or 16) columns
+__device__ __forceinline__ void tmem_ld_cols_nowait(uint32_t taddr, uint32_t* r) {
+    if constexpr (COLS == 16) {
+        tmem_ld16_nowait(taddr, r);
+    } else {
+        static_assert(COLS == 8 || COLS == 16, "a warp takes 8 or 16 of every 32 columns");
+        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                     : "r"(taddr) : "memory");
+    }
+}
+
+// The two special-function results of a SwiGLU output as single instructions: without .ftz each of them comes with
+// a few more that rescale subnormal arguments and results, which decide nothing here (exp(-gate) below 1e-38 adds
+// nothing to 1, and a quotient below 1e-38 is rounded to a bfloat16 zero either way).
+__device__ __forceinline__ float ex2_ftz(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float rcp_ftz(float x) { float y; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+
 struct Gemm2Args {
     const void* bias;      // [rows_out] or null
     int bias_dtype;
@@ -166,6 +187,13 @@ __device__ __forceinline__ void tmem_wait_ld(uint32_t* r) {
                  : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
                    "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
                  :: "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld8(uint32_t* r) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]) :: "memory");
+}
+__device__ __forceinline__ void pin8(uint32_t* r) {
+    asm volatile("" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]) :: "memory");
 }
 __device__ __forceinline__ void pin16(uint32_t* r) {
     asm volatile(""
@@ -194,6 +222,8 @@ template <int BN, int STAGES, bool DUAL, bool INTO = false>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                 const __grid_constant__ CUtensorMap map_out, Gemm2Args g) {
+    LLB_STAMPS_BEGIN();
+    if (threadIdx.x == 64) LLB_STAMP(0);
     using S = Smem2<BN, STAGES, DUAL, INTO>;
     constexpr int ACCS = S::ACCS, ACC_COLS = S::ACC_COLS, NBUF = S::NBUF;
     extern __shared__ uint8_t smem_raw[];
@@ -224,7 +254,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(bar_acc_full + 8 * b, 1);      // one multicast commit per tile
-            mbar_init(bar_acc_empty + 8 * b, 16);    // the leader's is used: eight epilogue warps of each CTA
+            mbar_init(bar_acc_empty + 8 * b, 2 * (EPI_THREADS / 32));    // the leader's is used: the epilogue warps of both CTAs
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -342,8 +372,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     } else {
         // ---- epilogue: warp w may read tensor-memory lanes 32 (w mod 4) .. + 31; a thread owns one weight row and,
         // of every 32 columns, the first or the second 16
-        const int et = tid - 64;                                  // 0..255
-        const int h = ((warp - 2) >> 2) * 16;
+        const int et = tid - 64;                                  // 0 .. EPI_THREADS - 1
+        const int h = ((warp - 2) >> 2) * COLS;
         const int row = (warp & 3) * 32 + lane;
         const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
         const uint32_t acc_empty0 = mapa(bar_acc_empty, 0);
@@ -363,28 +393,29 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 s_epi_abort = 1;
                 if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC2_WAIT_ACC_FULL); }
             }
-            asm volatile("bar.sync 1, 256;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
+            if (et == 0 && ti < 2) LLB_STAMP(1 + 6 * ti);           // stamps: 1/7 accumulator ready, 2-4 first chunk, 5 chunks done, 6/8 handed back
             if (s_epi_abort) break;                               // written before the barrier only: the same for all
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t acc = lane_addr + buf * ACC_COLS;
             // the next 16 columns are on their way from tensor memory while these are worked on
-            uint32_t nxt0[16], nxt1[16];
-            tmem_ld16_nowait(acc + h, nxt0);
-            if (DUAL) tmem_ld16_nowait(acc + BN + h, nxt1);
+            uint32_t nxt0[COLS], nxt1[COLS];
+            tmem_ld_cols_nowait(acc + h, nxt0);
+            if (DUAL) tmem_ld_cols_nowait(acc + BN + h, nxt1);
 #pragma unroll 1
             for (int c = 0; c < BN; c += CHUNK, ++chunk_i) {
                 bf16* sb = stg + (chunk_i & 1) * (CHUNK * BM);
-                float v0[16], v1[16];
-                tmem_wait_ld(nxt0);
-                if (DUAL) pin16(nxt1);
+                float v0[COLS], v1[COLS];
+                if constexpr (COLS == 16) { tmem_wait_ld(nxt0); if (DUAL) pin16(nxt1); }
+                else { tmem_wait_ld8(nxt0); if (DUAL) pin8(nxt1); }
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
+                for (int j = 0; j < COLS; ++j) {
                     v0[j] = __uint_as_float(nxt0[j]);
                     if (DUAL) v1[j] = __uint_as_float(nxt1[j]);
                 }
                 if (c + CHUNK < BN) {
-                    tmem_ld16_nowait(acc + c + CHUNK + h, nxt0);
-                    if (DUAL) tmem_ld16_nowait(acc + BN + c + CHUNK + h, nxt1);
+                    tmem_ld_cols_nowait(acc + c + CHUNK + h, nxt0);
+                    if (DUAL) tmem_ld_cols_nowait(acc + BN + c + CHUNK + h, nxt1);
                 }
                 if (INTO) {
                     // this K range's partial sums of 32 tokens x 128 rows, laid out as they lie in the stream, then one
@@ -393,10 +424,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     // read it by then: the thread that issues them waits for that before it arrives.
                     float* sf = stgf + (chunk_i & 1) * (CHUNK * BM);
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) sf[(h + j) * BM + row] = v0[j] + bias_v;
+                    for (int j = 0; j < COLS; ++j) sf[(h + j) * BM + row] = v0[j] + bias_v;
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     if (et == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                    asm volatile("bar.sync 1, 256;" ::: "memory");
+                    asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
                     if (et == 0) {
                         asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
                                      ::"l"(&map_out), "r"(m0), "r"(n0 + c), "r"(smem_u32(sf)) : "memory");
@@ -404,29 +435,40 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     }
                     continue;
                 }
+                // A warp's 32 rows x COLS tokens go through the warp's own two buffers [COLS tokens][32 rows] and out as
+                // 64-byte pieces of COLS token rows: no barrier among the epilogue warps, so one warp's arithmetic (two
+                // special-function results per SwiGLU output) runs beside another warp's stores.
+                bf16* sw = stg + ((warp - 2) * 2 + (chunk_i & 1)) * (COLS * 32);
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
+                for (int j = 0; j < COLS; ++j) {
                     float v = v0[j];
-                    if (DUAL) v = v1[j] * __fdividef(v, 1.0f + __expf(-v));       // fast division: the result is rounded to bfloat16
-                    sb[(h + j) * BM + row] = __float2bfloat16_rn(v + bias_v);
+                    if (DUAL) v = v1[j] * v * rcp_ftz(1.0f + ex2_ftz(-1.4426950408889634f * v));   // up * gate / (1 + exp(-gate))
+                    else v += bias_v;                                                              // (the gate/up product has no bias)
+                    sw[j * 32 + lane] = __float2bfloat16_rn(v);
                 }
-                asm volatile("bar.sync 1, 256;" ::: "memory");
-                // 16 threads move one token's 128 outputs (256 bytes); 16 tokens per pass.  The other buffer is
-                // written next, and this one only after the next barrier, which every thread passes after its reads.
-                if (m0 + sub * 8 < g.rows_out) {
+                if (et == 0 && ti == 0 && c == 0) LLB_STAMP(2);
+                __syncwarp();
+                if (et == 0 && ti == 0 && c == 0) LLB_STAMP(3);
+                // four lanes move one token's 32 outputs (64 bytes); eight tokens per pass.  This buffer is written again
+                // two chunks on, behind the next chunk's __syncwarp, which every lane passes after these reads.
+                const int piece = lane & 3, mcol = m0 + (warp & 3) * 32 + piece * 8;
+                if (mcol < g.rows_out) {
 #pragma unroll
-                    for (int j = et >> 4; j < CHUNK; j += EPI_THREADS / 16) {
-                        const int n = n0 + c + j;
+                    for (int j = lane >> 2; j < COLS; j += 8) {
+                        const int n = n0 + c + h + j;
                         if (n < g.T)
-                            *reinterpret_cast<uint4*>(g.Y + (size_t)n * g.ldy + m0 + sub * 8) =
-                                *reinterpret_cast<const uint4*>(sb + j * BM + sub * 8);
+                            *reinterpret_cast<uint4*>(g.Y + (size_t)n * g.ldy + mcol) =
+                                *reinterpret_cast<const uint4*>(sw + j * 32 + piece * 8);
                     }
                 }
+                if (et == 0 && ti == 0 && c == 0) LLB_STAMP(4);
             }
+            if (et == 0 && ti == 0) LLB_STAMP(5);
             // this buffer may be overwritten by the tile after the next
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(acc_empty0 + 8 * buf);
+            if (et == 0 && ti < 2) LLB_STAMP(6 + 2 * ti);
         }
     }
 
@@ -480,6 +522,8 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, 
 
 }  // namespace
 
+LLB_DEFINE_SET_STAMPS
+
 // X [T, K] bf16 with row stride ldx; W [N, K] bf16 dense ([2 * dual_offset, K] when dual_offset > 0); Y [T, ldy]
 // bf16; bias [N] or null.  max_pairs: how many CTA pairs may run at once (SMs / 2).  Returns
 // cudaErrorInvalidValue for what this kernel does not take (the caller then uses the one-CTA kernel).
@@ -489,7 +533,7 @@ LLB_API int llb_gemm_tc2(const void* X, const void* W, const void* bias, int bia
     const int dual = dual_offset > 0;
     const int rows_out = dual ? dual_offset : N;
     if (K <= 0 || K % 8 || ldx % 8 || ldy % 8 || rows_out % 8 || max_pairs < 1 ||
-        (((uintptr_t)X | (uintptr_t)W | (uintptr_t)Y) & 15) || (dual && N != 2 * dual_offset))
+        (((uintptr_t)X | (uintptr_t)W | (uintptr_t)Y) & 15) || (dual && (N != 2 * dual_offset || bias)))
         return (int)cudaErrorInvalidValue;
     const int bn = 256;
     Gemm2Args g;

@@ -55,8 +55,8 @@ def _lib_basic():
 
 _launches = 0
 
-# LLAISYS_STAMPS=1: the three kernels of a decode step that can record cycle stamps (see csrc/common.cuh) are built
-# with them; set_stamps() then switches them on for launches of a given grid size.  Off by default: the product's
+# LLAISYS_STAMPS=1: the kernels that can record cycle stamps (see csrc/common.cuh: the decode step's three short ones and
+# the paired-SM product) are built with them; set_stamps() then switches them on for launches of a given grid size.  Off by default: the product's
 # builds contain no stamp.
 _STAMPS = {"LLB_STAMPS": 1} if __import__("os").environ.get("LLAISYS_STAMPS", "0") not in ("", "0") else {}
 _stamp_libs = {}
@@ -70,7 +70,7 @@ def _stamped(source: str, defines: Optional[dict] = None):
 
 
 def set_stamps(source: str, buf: Optional[torch.Tensor], blocks: int = 0) -> None:
-    """Cycle stamps of the kernels of `source` ("gemm_tc.cu", "attention_mma.cu", "mlp_tc.cu") into `buf` (int64
+    """Cycle stamps of the kernels of `source` ("gemm_tc.cu", "gemm_tc2.cu", "attention_mma.cu", "mlp_tc.cu") into `buf` (int64
     [blocks, 16] on the device) for launches of exactly `blocks` blocks; None switches them off.  Needs
     LLAISYS_STAMPS=1 in the environment before the package is imported, and the module in use already."""
     lib = _stamp_libs.get(source)
@@ -346,7 +346,7 @@ def _gemm_tc_pair(x, weight, bias, out, dual_offset=0):
     M, K = x.shape
     N = weight.shape[0]
     err = _tc_resources(x.device)[2]
-    f = _fn(load_module("gemm_tc2.cu"), "llb_gemm_tc2",
+    f = _fn(_stamped("gemm_tc2.cu"), "llb_gemm_tc2",
             [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(f(_ptr(x), _ptr(weight), _ptr(bias), _dt(bias) if bias is not None else 0, _ptr(out), M, N, K,
              x.stride(0), out.stride(0), dual_offset, _sm_count(x.device) // 2, _ptr(err), _stream()),
@@ -431,7 +431,7 @@ def linear_into(x: torch.Tensor, weight: torch.Tensor, bias, stream: torch.Tenso
         _check(f(_ptr(x), _ptr(weight), _ptr(bias), _dt(bias) if bias is not None else 0, _ptr(stream), T, N, K, x.stride(0),
                  stream.stride(0), bn, ksplit or splits, _ptr(err), _stream()), "linear into the residual stream (tensor cores)")
         return
-    f = _fn(load_module("gemm_tc2.cu"), "llb_gemm_tc2_into",
+    f = _fn(_stamped("gemm_tc2.cu"), "llb_gemm_tc2_into",
             [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(f(_ptr(x), _ptr(weight), _ptr(bias), _dt(bias) if bias is not None else 0, _ptr(stream), T, N, K, x.stride(0),
              stream.stride(0), ksplit, _sm_count(x.device) // 2, _ptr(err), _stream()), "linear into the residual stream (tensor cores, paired SMs)")
