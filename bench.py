@@ -267,6 +267,9 @@ STAMP_NAMES = {
     "gate_up": ("gemm_tc2.cu", ["start", "first tile: accumulators ready", "first 32 tokens computed", "(warp joined)", "first 32 tokens stored",
                                 "all tokens stored", "accumulators handed back", "second tile: accumulators ready",
                                 "second tile: accumulators handed back"]),
+    "down": ("gemm_tc2.cu", ["start", "first unit: accumulator ready", "second 32 tokens staged", "the reduction before has read its buffer",
+                             "reduction issued", "all reductions issued", "accumulator handed back", "second unit: accumulator ready",
+                             "second unit: accumulator handed back"]),
 }
 
 
@@ -283,23 +286,34 @@ def stamps_run(args, model, cfg, rng) -> int:
     from llaisys_b200.engine import Engine, StepEntry
     from llaisys_b200.kernels import ops
 
-    if args.stamps == "gate_up":
-        # the prefill's largest product alone (--tokens tokens on pairs of SMs): how long a tile's epilogue keeps the
-        # tensor cores waiting, in SM cycles after the block started
+    if args.stamps in ("gate_up", "down"):
+        # one of the prefill's two largest products alone (--tokens tokens on pairs of SMs): how long a tile's epilogue
+        # takes (and, for gate/up, keeps the tensor cores waiting), in SM cycles after the block started
         from llaisys_b200 import kernels
         source, names = STAMP_NAMES[args.stamps]
-        x = torch.randn(args.tokens, cfg.hidden_size, device="cuda:0", dtype=torch.bfloat16)
-        w = torch.randn(2 * cfg.intermediate_size, cfg.hidden_size, device="cuda:0", dtype=torch.bfloat16) * 0.02
+        if args.stamps == "gate_up":
+            x = torch.randn(args.tokens, cfg.hidden_size, device="cuda:0", dtype=torch.bfloat16)
+            w = torch.randn(2 * cfg.intermediate_size, cfg.hidden_size, device="cuda:0", dtype=torch.bfloat16) * 0.02
+
+            def product():
+                kernels.linear_swiglu(x, w)
+        else:
+            x = torch.randn(args.tokens, cfg.intermediate_size, device="cuda:0", dtype=torch.bfloat16)
+            w = torch.randn(cfg.hidden_size, cfg.intermediate_size, device="cuda:0", dtype=torch.bfloat16) * 0.02
+            stream = torch.zeros(args.tokens, cfg.hidden_size, device="cuda:0", dtype=torch.float32)
+
+            def product():
+                kernels.linear_into(x, w, None, stream)
         for _ in range(3):
-            kernels.linear_swiglu(x, w)
+            product()
         buf = torch.zeros((1 << 12, 16), dtype=torch.int64, device="cuda:0")
         ops.set_stamps(source, buf, 0)
-        kernels.linear_swiglu(x, w)
+        product()
         torch.cuda.synchronize()
         ops.set_stamps(source, None)
         st = buf.cpu().numpy().astype(np.float64)
         st = st[st[:, 1] != 0]
-        print(f"gate_up: {len(st)} blocks; SM cycles after the block's start ({args.tokens} tokens)")
+        print(f"{args.stamps}: {len(st)} blocks; SM cycles after the block's start ({args.tokens} tokens)")
         for i, name in enumerate(names):
             col = (st[:, i] - st[:, 0])[st[:, i] != 0]
             if i and len(col):
@@ -601,10 +615,10 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=None,
                     help="for measurements beside the reported one: tokens every sequence holds before decoding, and tokens of "
                          "the timed prefill step (default 2,048; the cache is sized for twice as many per sequence)")
-    ap.add_argument("--stamps", choices=["gemm", "attention", "mlp", "gate_up"], default=None,
+    ap.add_argument("--stamps", choices=["gemm", "attention", "mlp", "gate_up", "down"], default=None,
                     help="cycle stamps from inside one kernel of the decode step (the q/k/v product, decode attention or the "
-                         "one-launch feed-forward), in its place in the step replayed from its CUDA graph, or (gate_up) from the "
-                         "prefill's gate/up product alone at --tokens tokens; builds that kernel with -DLLB_STAMPS=1")
+                         "one-launch feed-forward), in its place in the step replayed from its CUDA graph, or (gate_up, down) from the "
+                         "prefill's gate/up or down product alone at --tokens tokens; builds that kernel with -DLLB_STAMPS=1")
     ap.add_argument("--timeline", choices=["decode", "prefill"], default=None,
                     help="print the per-kernel timeline of a step (torch.profiler, no ncu) instead of measuring")
     args = ap.parse_args()

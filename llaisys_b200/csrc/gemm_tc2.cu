@@ -394,7 +394,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                 if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC2_WAIT_ACC_FULL); }
             }
             asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
-            if (et == 0 && ti < 2) LLB_STAMP(1 + 6 * ti);           // stamps: 1/7 accumulator ready, 2-4 first chunk, 5 chunks done, 6/8 handed back
+            if (et == 0 && ti < 2) LLB_STAMP(1 + 6 * ti);           // stamps: 1/7 accumulator ready, 2-4 inside a chunk, 5 chunks done, 6/8 handed back
             if (s_epi_abort) break;                               // written before the barrier only: the same for all
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t acc = lane_addr + buf * ACC_COLS;
@@ -426,13 +426,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < COLS; ++j) sf[(h + j) * BM + row] = v0[j] + bias_v;
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    if (et == 0 && ti == 0 && c == CHUNK) LLB_STAMP(2);
                     if (et == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    if (et == 0 && ti == 0 && c == CHUNK) LLB_STAMP(3);
                     asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
                     if (et == 0) {
                         asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
                                      ::"l"(&map_out), "r"(m0), "r"(n0 + c), "r"(smem_u32(sf)) : "memory");
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
+                    if (et == 0 && ti == 0 && c == CHUNK) LLB_STAMP(4);
                     continue;
                 }
                 // A warp's 32 rows x COLS tokens go through the warp's own two buffers [COLS tokens][32 rows] and out as
