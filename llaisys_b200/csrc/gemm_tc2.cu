@@ -10,20 +10,25 @@
 // Two CTAs on neighbouring SMs (a cluster of two) work on one tile of 256 weight rows x BN tokens
 // with tcgen05.mma.cta_group::2: each CTA holds its own 128 weight rows and HALF of the token
 // tile in shared memory, the tensor cores of both SMs read both halves, and each CTA's tensor
-// memory receives its 128 rows x BN tokens.  An SM thus fills a third (a quarter with DUAL) less
-// shared memory per FLOP than it would alone.  The pair is persistent: it walks over tiles
-// pair, pair + pairs, ....  With one accumulator (256 tokens = 256 columns) tensor memory holds
-// two buffers, so the epilogue of a tile (tcgen05.ld, bias, transposition through shared memory,
-// 16-byte stores) runs while the tensor cores work on the next one; the two accumulators of DUAL
-// (2 x 256 columns) fill tensor memory, and the next tile's products wait for the epilogue
-// (measured faster than 128-token tiles with two buffers, whose products are slower per FLOP).
+// memory receives its 128 rows x BN tokens.  An SM thus fills a third less shared memory per FLOP
+// than it would alone.  The pair is persistent: it walks over tiles pair, pair + pairs, ....
+// An accumulator is 256 tokens = 256 columns, so tensor memory holds two, and the epilogue of a
+// tile (tcgen05.ld, bias or SwiGLU, transposition through shared memory, 16-byte stores) runs while
+// the tensor cores work on the next one.
+//
+// DUAL: a CTA's 128 weight rows are 64 gate rows followed by the 64 up rows of the same outputs
+// (two TMA boxes of 64 rows into one operand tile), so the one accumulator holds gate values in
+// lanes 0-63 and up values in lanes 64-127, and the epilogue warps of the upper lanes pass theirs
+// to the warps of the lower lanes through shared memory.  (Two accumulators of 128 + 128 rows
+// filled tensor memory and left every tile's epilogue exposed: 76 instead of 68 us for the
+// benchmark's gate/up product at 2,048 tokens.)
 //
 //   warp 0      TMA producer (one thread): ring of STAGES k-blocks, both CTAs, completion counted on the
 //               leader CTA's barrier
 //   warp 1      tcgen05.mma issue (one thread of the leader CTA); tcgen05.commit multicast frees the ring
 //               slot in both CTAs and, per tile, hands the accumulator to both epilogues
 //   warps 2-17  epilogue of this CTA's 128 rows: four warps per 32 rows, each with 8 of every 32 columns, transposed
-//               through a buffer of the warp's own (no barrier among the epilogue warps)
+//               through a buffer of the warp's own (no barrier among the storing warps)
 //
 // INTO (an instantiation of its own): the product is not stored but added to a float32 stream [T, N]
 // (the residual stream: an output projection or a down projection that ends in the residual add of
@@ -192,30 +197,25 @@ __device__ __forceinline__ void tmem_wait_ld8(uint32_t* r) {
     asm volatile("tcgen05.wait::ld.sync.aligned;"
                  : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]) :: "memory");
 }
-__device__ __forceinline__ void pin8(uint32_t* r) {
-    asm volatile("" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]) :: "memory");
-}
-__device__ __forceinline__ void pin16(uint32_t* r) {
-    asm volatile(""
-                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
-                 :: "memory");
-}
-
 template <int BN, int STAGES, bool DUAL, bool INTO = false>
 struct Smem2 {
-    static constexpr int ACCS = DUAL ? 2 : 1;
-    static constexpr int A_BYTES = BM * BK * 2;
+    static constexpr int A_BYTES = BM * BK * 2;                   // 128 weight rows (DUAL: 64 gate rows, then 64 up rows)
     static constexpr int B_BYTES = (BN / 2) * BK * 2;             // this CTA's half of the token tile
-    static constexpr int STAGE_BYTES = ACCS * A_BYTES + B_BYTES;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STG_OFFSET = STAGES * STAGE_BYTES;
-    static constexpr int STG_BYTES = 2 * CHUNK * BM * (INTO ? 4 : 2);   // two transposition buffers [32 tokens][128 rows], bf16 or (INTO) f32
-    static constexpr int BAR_OFFSET = STG_OFFSET + STG_BYTES;
+    // transposition buffers: INTO two of [32 tokens][128 rows] float32 for all; else two of [COLS tokens][32 rows] bf16
+    // per storing warp.  DUAL: behind them the exchange buffers, two of [COLS tokens][32 rows] float32 per up warp.
+    static constexpr int STG_BYTES = INTO ? 2 * CHUNK * BM * 4 : (EPI_THREADS / 32) * 2 * COLS * 32 * 2;
+    static constexpr int XCH_OFFSET = STG_OFFSET + STG_BYTES;
+    static constexpr int XCH_BYTES = DUAL ? (EPI_THREADS / 64) * 2 * COLS * 32 * 4 : 0;
+    static constexpr int BAR_OFFSET = XCH_OFFSET + XCH_BYTES;
     static constexpr int N_BARS = 2 * STAGES + 4;
     static constexpr int TOTAL = BAR_OFFSET + N_BARS * 8 + 16 + 1024;   // + slack to align the base
-    static constexpr int ACC_COLS = ACCS * BN;                    // tensor-memory columns of one accumulator buffer
-    static constexpr int NBUF = 512 / ACC_COLS;                   // buffers in the 512 columns of tensor memory: 2 or 1
-    static_assert(ACC_COLS == 256 || ACC_COLS == 512, "an accumulator buffer is a half or the whole of tensor memory");
+    static constexpr int ACC_COLS = BN;                           // tensor-memory columns of one accumulator buffer
+    static constexpr int NBUF = 512 / ACC_COLS;                   // buffers in the 512 columns of tensor memory
+    static constexpr int MROWS = DUAL ? BM / 2 : BM;              // output rows of one CTA's tile
+    static_assert(ACC_COLS == 256, "two accumulator buffers fill tensor memory");
+    static_assert(TOTAL <= 232448, "a block's shared memory");
 };
 
 template <int BN, int STAGES, bool DUAL, bool INTO = false>
@@ -225,7 +225,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     LLB_STAMPS_BEGIN();
     if (threadIdx.x == 64) LLB_STAMP(0);
     using S = Smem2<BN, STAGES, DUAL, INTO>;
-    constexpr int ACCS = S::ACCS, ACC_COLS = S::ACC_COLS, NBUF = S::NBUF;
+    constexpr int ACC_COLS = S::ACC_COLS, NBUF = S::NBUF, MROWS = S::MROWS;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -276,12 +276,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     const int prefetched = min(STAGES, unit_kb1(pair) - first_kb0);
     if (warp == 0 && lane == 0) {
         const uint32_t full0 = mapa(bar_full, 0);
-        const int m0 = (((pair % g.n_tiles) / g.tok_tiles) * 2 + (int)rank) * BM;
+        const int m0 = (((pair % g.n_tiles) / g.tok_tiles) * 2 + (int)rank) * MROWS;
         for (int i = 0; i < prefetched; ++i) {
             const uint32_t dst = base + i * S::STAGE_BYTES, bar = full0 + 8 * i;
             if (leader) mbar_expect_tx(bar_full + 8 * i, 2u * S::STAGE_BYTES);
-            tma_load_2d_pair(dst, &map_w, bar, (first_kb0 + i) * BK, m0, HINT_EVICT_FIRST);
-            if (DUAL) tma_load_2d_pair(dst + S::A_BYTES, &map_w, bar, (first_kb0 + i) * BK, m0 + g.dual_offset, HINT_EVICT_FIRST);
+            tma_load_2d_pair(dst, &map_w, bar, (first_kb0 + i) * BK, m0, HINT_EVICT_FIRST);      // DUAL: the map's box is 64 rows
+            if (DUAL) tma_load_2d_pair(dst + S::A_BYTES / 2, &map_w, bar, (first_kb0 + i) * BK, m0 + g.dual_offset, HINT_EVICT_FIRST);
         }
     }
     llb_grid_dependency_sync();      // from here on memory written by earlier kernels is touched
@@ -293,14 +293,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         if (elect_one()) {   // the activations of the k-blocks whose weight is on its way already
             const int n0 = ((pair % g.n_tiles) % g.tok_tiles) * BN + (int)rank * (BN / 2);
             for (int i = 0; i < prefetched; ++i)
-                tma_load_2d_pair(base + i * S::STAGE_BYTES + ACCS * S::A_BYTES, &map_x, full0 + 8 * i, (first_kb0 + i) * BK, n0, HINT_EVICT_LAST);
+                tma_load_2d_pair(base + i * S::STAGE_BYTES + S::A_BYTES, &map_x, full0 + 8 * i, (first_kb0 + i) * BK, n0, HINT_EVICT_LAST);
         }
         __syncwarp();
         int it = prefetched;
         bool ok = true;
         for (int u = pair; u < n_units && ok; u += g.n_pairs) {
             const int t = u % g.n_tiles, kb1 = unit_kb1(u);
-            const int m0 = ((t / g.tok_tiles) * 2 + (int)rank) * BM;
+            const int m0 = ((t / g.tok_tiles) * 2 + (int)rank) * MROWS;
             const int n0 = (t % g.tok_tiles) * BN + (int)rank * (BN / 2);
             for (int kb = unit_kb0(u) + (u == pair ? prefetched : 0); kb < kb1; ++kb, ++it) {
                 const int s = it % STAGES;
@@ -313,8 +313,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     const uint32_t dst = base + s * S::STAGE_BYTES, bar = full0 + 8 * s;
                     if (leader) mbar_expect_tx(bar_full + 8 * s, 2u * S::STAGE_BYTES);
                     tma_load_2d_pair(dst, &map_w, bar, kb * BK, m0, HINT_EVICT_FIRST);
-                    if (DUAL) tma_load_2d_pair(dst + S::A_BYTES, &map_w, bar, kb * BK, m0 + g.dual_offset, HINT_EVICT_FIRST);
-                    tma_load_2d_pair(dst + ACCS * S::A_BYTES, &map_x, bar, kb * BK, n0, HINT_EVICT_LAST);
+                    if (DUAL) tma_load_2d_pair(dst + S::A_BYTES / 2, &map_w, bar, kb * BK, m0 + g.dual_offset, HINT_EVICT_FIRST);
+                    tma_load_2d_pair(dst + S::A_BYTES, &map_x, bar, kb * BK, n0, HINT_EVICT_LAST);
                 }
                 __syncwarp();
             }
@@ -331,7 +331,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             // ---- tensor-core issue for both SMs: the warp waits as a whole, one elected lane issues; the operand
             // descriptors are made once and a stage's or an instruction's own differ from them by a constant
             const uint32_t idesc = umma_idesc_pair(BN);
-            const uint64_t a_desc0 = umma_desc(base), b_desc0 = umma_desc(base + ACCS * S::A_BYTES);
+            const uint64_t a_desc0 = umma_desc(base), b_desc0 = umma_desc(base + S::A_BYTES);
             int it = 0, ti = 0;
             bool ok = true;
             for (int u = pair; u < n_units && ok; u += g.n_pairs, ++ti) {
@@ -351,13 +351,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     if (elect_one()) {
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         const uint64_t so = (uint64_t)(s * (S::STAGE_BYTES >> 4));
-                        const uint64_t ad = a_desc0 + so, bd = b_desc0 + so, ad2 = ad + (uint64_t)(S::A_BYTES >> 4);
+                        const uint64_t ad = a_desc0 + so, bd = b_desc0 + so;
 #pragma unroll
                         for (int k = 0; k < BK / UMMA_K; ++k) {
                             const uint32_t accumulate = (kb > kb0 || k > 0) ? 1u : 0u;
                             const uint64_t step = (uint64_t)(k * UMMA_K * 2 >> 4);      // the start address field counts 16 bytes
                             umma_pair(acc, ad + step, bd + step, idesc, accumulate);
-                            if (DUAL) umma_pair(acc + BN, ad2 + step, bd + step, idesc, accumulate);
                         }
                         umma_commit_both(bar_empty + 8 * s);
                     }
@@ -370,53 +369,52 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         }
         __syncwarp();
     } else {
-        // ---- epilogue: warp w may read tensor-memory lanes 32 (w mod 4) .. + 31; a thread owns one weight row and,
-        // of every 32 columns, the first or the second 16
+        // ---- epilogue: warp w may read tensor-memory lanes 32 (w mod 4) .. + 31; a thread owns one weight row and COLS of
+        // every 32 columns.  DUAL: lanes 0-63 hold gate rows and lanes 64-127 the up rows of the same outputs, so a warp
+        // of the upper half hands its values to the warp of the lower half with the same rows and columns through shared
+        // memory, with a barrier of the two warps per chunk; the lower warps compute and store.
         const int et = tid - 64;                                  // 0 .. EPI_THREADS - 1
-        const int h = ((warp - 2) >> 2) * COLS;
-        const int row = (warp & 3) * 32 + lane;
-        const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+        const int q = warp & 3, share = (warp - 2) >> 2;
+        const int h = share * COLS;
+        const int row = q * 32 + lane;
+        const uint32_t lane_addr = tmem + ((uint32_t)(q * 32) << 16);
         const uint32_t acc_empty0 = mapa(bar_acc_empty, 0);
         bf16* stg = reinterpret_cast<bf16*>(gen_base + S::STG_OFFSET);
         float* stgf = reinterpret_cast<float*>(gen_base + S::STG_OFFSET);          // INTO: [2][32 tokens][128 rows] float32
-        const int sub = et & 15;
+        const bool up_warp = DUAL && q >= 2;
+        const int xpair = (q & 1) * EPI_SHARE + share;            // DUAL: the two warps' buffers and barrier (ids 2 ..)
+        float* xch = reinterpret_cast<float*>(gen_base + S::XCH_OFFSET) + xpair * (2 * COLS * 32);
+        const int out_row = DUAL ? (q & 1) * 32 : q * 32;         // this warp's first output row within the CTA's tile
+        const bool stamper = tid == (DUAL ? 128 : 64);            // (a storing warp's first thread)
         int ti = 0, chunk_i = 0;
         for (int u = pair; u < n_units; u += g.n_pairs, ++ti) {
             const int buf = ti % NBUF, t = u % g.n_tiles;
-            const int m0 = ((t / g.tok_tiles) * 2 + (int)rank) * BM;
+            const int m0 = ((t / g.tok_tiles) * 2 + (int)rank) * MROWS;
             const int n0 = (t % g.tok_tiles) * BN;
             const int m = m0 + row;
             float bias_v = 0.f;
-            if (g.bias && m < g.rows_out && u < g.n_tiles)             // the bias goes in with the first K range only
+            if (!DUAL && g.bias && m < g.rows_out && u < g.n_tiles)    // the bias goes in with the first K range only
                 bias_v = g.bias_dtype == LLB_F32 ? ((const float*)g.bias)[m] : to_f32(((const bf16*)g.bias)[m]);
             if (!mbar_wait(bar_acc_full + 8 * buf, (uint32_t)(ti / NBUF) & 1u, &s_abort)) {
                 s_epi_abort = 1;
                 if (!s_abort) { s_abort = 1; atomicExch(g.err, ERR_TC2_WAIT_ACC_FULL); }
             }
             asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
-            if (et == 0 && ti < 2) LLB_STAMP(1 + 6 * ti);           // stamps: 1/7 accumulator ready, 2-4 inside a chunk, 5 chunks done, 6/8 handed back
+            if (stamper && ti < 2) LLB_STAMP(1 + 6 * ti);             // stamps: 1/7 accumulator ready, 2-4 inside a chunk, 5 chunks done, 6/8 handed back
             if (s_epi_abort) break;                               // written before the barrier only: the same for all
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t acc = lane_addr + buf * ACC_COLS;
-            // the next 16 columns are on their way from tensor memory while these are worked on
-            uint32_t nxt0[COLS], nxt1[COLS];
+            // the next columns are on their way from tensor memory while these are worked on
+            uint32_t nxt0[COLS];
             tmem_ld_cols_nowait(acc + h, nxt0);
-            if (DUAL) tmem_ld_cols_nowait(acc + BN + h, nxt1);
 #pragma unroll 1
             for (int c = 0; c < BN; c += CHUNK, ++chunk_i) {
-                bf16* sb = stg + (chunk_i & 1) * (CHUNK * BM);
-                float v0[COLS], v1[COLS];
-                if constexpr (COLS == 16) { tmem_wait_ld(nxt0); if (DUAL) pin16(nxt1); }
-                else { tmem_wait_ld8(nxt0); if (DUAL) pin8(nxt1); }
+                float v0[COLS];
+                if constexpr (COLS == 16) tmem_wait_ld(nxt0);
+                else tmem_wait_ld8(nxt0);
 #pragma unroll
-                for (int j = 0; j < COLS; ++j) {
-                    v0[j] = __uint_as_float(nxt0[j]);
-                    if (DUAL) v1[j] = __uint_as_float(nxt1[j]);
-                }
-                if (c + CHUNK < BN) {
-                    tmem_ld_cols_nowait(acc + c + CHUNK + h, nxt0);
-                    if (DUAL) tmem_ld_cols_nowait(acc + BN + c + CHUNK + h, nxt1);
-                }
+                for (int j = 0; j < COLS; ++j) v0[j] = __uint_as_float(nxt0[j]);
+                if (c + CHUNK < BN) tmem_ld_cols_nowait(acc + c + CHUNK + h, nxt0);
                 if (INTO) {
                     // this K range's partial sums of 32 tokens x 128 rows, laid out as they lie in the stream, then one
                     // reduction into the stream.  The other buffer is written right after the barrier below (the next
@@ -426,35 +424,48 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
 #pragma unroll
                     for (int j = 0; j < COLS; ++j) sf[(h + j) * BM + row] = v0[j] + bias_v;
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                    if (et == 0 && ti == 0 && c == CHUNK) LLB_STAMP(2);
+                    if (stamper && ti == 0 && c == CHUNK) LLB_STAMP(2);
                     if (et == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                    if (et == 0 && ti == 0 && c == CHUNK) LLB_STAMP(3);
+                    if (stamper && ti == 0 && c == CHUNK) LLB_STAMP(3);
                     asm volatile("bar.sync 1, %0;" ::"n"(EPI_THREADS) : "memory");
                     if (et == 0) {
                         asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];"
                                      ::"l"(&map_out), "r"(m0), "r"(n0 + c), "r"(smem_u32(sf)) : "memory");
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
-                    if (et == 0 && ti == 0 && c == CHUNK) LLB_STAMP(4);
+                    if (stamper && ti == 0 && c == CHUNK) LLB_STAMP(4);
                     continue;
                 }
+                if (DUAL) {
+                    // The up warp writes buffer chunk_i & 1 and meets the gate warp at their barrier; it writes that buffer
+                    // again two chunks on, behind the next chunk's barrier, which the gate warp reaches after these reads.
+                    float* xb = xch + (chunk_i & 1) * (COLS * 32);
+                    if (up_warp) {
+#pragma unroll
+                        for (int j = 0; j < COLS; ++j) xb[j * 32 + lane] = v0[j];
+                        asm volatile("bar.sync %0, 64;" ::"r"(2 + xpair) : "memory");
+                        continue;
+                    }
+                    asm volatile("bar.sync %0, 64;" ::"r"(2 + xpair) : "memory");
+#pragma unroll
+                    for (int j = 0; j < COLS; ++j)                                  // up * gate / (1 + exp(-gate))
+                        v0[j] = xb[j * 32 + lane] * v0[j] * rcp_ftz(1.0f + ex2_ftz(-1.4426950408889634f * v0[j]));
+                } else {
+#pragma unroll
+                    for (int j = 0; j < COLS; ++j) v0[j] += bias_v;
+                }
                 // A warp's 32 rows x COLS tokens go through the warp's own two buffers [COLS tokens][32 rows] and out as
-                // 64-byte pieces of COLS token rows: no barrier among the epilogue warps, so one warp's arithmetic (two
-                // special-function results per SwiGLU output) runs beside another warp's stores.
+                // 64-byte pieces of COLS token rows: no barrier among the storing warps, so one warp's arithmetic runs
+                // beside another warp's stores.
                 bf16* sw = stg + ((warp - 2) * 2 + (chunk_i & 1)) * (COLS * 32);
 #pragma unroll
-                for (int j = 0; j < COLS; ++j) {
-                    float v = v0[j];
-                    if (DUAL) v = v1[j] * v * rcp_ftz(1.0f + ex2_ftz(-1.4426950408889634f * v));   // up * gate / (1 + exp(-gate))
-                    else v += bias_v;                                                              // (the gate/up product has no bias)
-                    sw[j * 32 + lane] = __float2bfloat16_rn(v);
-                }
-                if (et == 0 && ti == 0 && c == 0) LLB_STAMP(2);
+                for (int j = 0; j < COLS; ++j) sw[j * 32 + lane] = __float2bfloat16_rn(v0[j]);
+                if (stamper && ti == 0 && c == 0) LLB_STAMP(2);
                 __syncwarp();
-                if (et == 0 && ti == 0 && c == 0) LLB_STAMP(3);
+                if (stamper && ti == 0 && c == 0) LLB_STAMP(3);
                 // four lanes move one token's 32 outputs (64 bytes); eight tokens per pass.  This buffer is written again
                 // two chunks on, behind the next chunk's __syncwarp, which every lane passes after these reads.
-                const int piece = lane & 3, mcol = m0 + (warp & 3) * 32 + piece * 8;
+                const int piece = lane & 3, mcol = m0 + out_row + piece * 8;
                 if (mcol < g.rows_out) {
 #pragma unroll
                     for (int j = lane >> 2; j < COLS; j += 8) {
@@ -464,14 +475,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                                 *reinterpret_cast<const uint4*>(sw + j * 32 + piece * 8);
                     }
                 }
-                if (et == 0 && ti == 0 && c == 0) LLB_STAMP(4);
+                if (stamper && ti == 0 && c == 0) LLB_STAMP(4);
             }
-            if (et == 0 && ti == 0) LLB_STAMP(5);
+            if (stamper && ti == 0) LLB_STAMP(5);
             // this buffer may be overwritten by the tile after the next
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(acc_empty0 + 8 * buf);
-            if (et == 0 && ti < 2) LLB_STAMP(6 + 2 * ti);
+            if (stamper && ti < 2) LLB_STAMP(6 + 2 * ti);
         }
     }
 
@@ -543,7 +554,8 @@ LLB_API int llb_gemm_tc2(const void* X, const void* W, const void* bias, int bia
     g.bias = bias; g.bias_dtype = bias_dtype; g.Y = (bf16*)Y;
     g.T = T; g.K = K; g.ldy = ldy; g.rows_out = rows_out; g.dual_offset = dual_offset;
     g.tok_tiles = (T + bn - 1) / bn;
-    const long long tiles = (long long)((rows_out + 2 * BM - 1) / (2 * BM)) * g.tok_tiles;
+    const int tile_rows = dual ? BM : 2 * BM;          // output rows of a pair's tile (gate/up: 64 gate and 64 up rows per CTA)
+    const long long tiles = (long long)((rows_out + tile_rows - 1) / tile_rows) * g.tok_tiles;
     if (tiles > (1 << 30)) return (int)cudaErrorInvalidValue;
     g.n_tiles = (int)tiles;
     g.n_pairs = (int)(tiles < max_pairs ? tiles : max_pairs);
@@ -551,11 +563,11 @@ LLB_API int llb_gemm_tc2(const void* X, const void* W, const void* bias, int bia
     g.ksplit = 1;
     g.chunk_kb = (K + BK - 1) / BK;
     CUtensorMap mw, mx;
-    int rc = llb_tma::bf16_map_64(W, N, K, K, BM, &mw);
+    int rc = llb_tma::bf16_map_64(W, N, K, K, dual ? BM / 2 : BM, &mw);
     if (rc) return rc;
     rc = llb_tma::bf16_map_64(X, T, K, ldx, bn / 2, &mx);
     if (rc) return rc;
-    return dual ? launch<256, 4, true>(mw, mx, mw, g, stream) : launch<256, 6, false>(mw, mx, mw, g, stream);
+    return dual ? launch<256, 6, true>(mw, mx, mw, g, stream) : launch<256, 6, false>(mw, mx, mw, g, stream);
 }
 
 // K ranges per tile for llb_gemm_tc2_into: the count (1 to 4) that minimises rounds of units times the length of a
