@@ -16,12 +16,13 @@
 // tile (tcgen05.ld, bias or SwiGLU, transposition through shared memory, 16-byte stores) runs while
 // the tensor cores work on the next one.
 //
-// DUAL: a CTA's 128 weight rows are 64 gate rows followed by the 64 up rows of the same outputs
-// (two TMA boxes of 64 rows into one operand tile), so the one accumulator holds gate values in
-// lanes 0-63 and up values in lanes 64-127, and the epilogue warps of the upper lanes pass theirs
-// to the warps of the lower lanes through shared memory.  (Two accumulators of 128 + 128 rows
-// filled tensor memory and left every tile's epilogue exposed: 76 instead of 68 us for the
-// benchmark's gate/up product at 2,048 tokens.)
+// DUAL has two variants.  1 (a short K range): a CTA's 128 weight rows are 64 gate rows followed by
+// the 64 up rows of the same outputs (two TMA boxes of 64 rows into one operand tile), so the one
+// accumulator holds gate values in lanes 0-63 and up values in lanes 64-127, and the epilogue warps
+// of the upper lanes pass theirs to the warps of the lower lanes through shared memory.  2 (a long
+// K range): 128 gate rows and 128 up rows with an accumulator each, which fill tensor memory, so the
+// next tile's products wait for the epilogue, but an SM takes a third less from the L2 per FLOP.
+// (The benchmark's gate/up product at 2,048 tokens, K = 1536: 68 us with the first, 76 with the second.)
 //
 //   warp 0      TMA producer (one thread): ring of STAGES k-blocks, both CTAs, completion counted on the
 //               leader CTA's barrier
@@ -146,25 +147,12 @@ __device__ __forceinline__ void umma_commit_both(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
                  ::"r"(bar), "h"((uint16_t)3) : "memory");
 }
-// One row of 16 accumulator columns; the registers hold the values after the next tcgen05.wait::ld.
-__device__ __forceinline__ void tmem_ld16_nowait(uint32_t taddr, uint32_t* r) {
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr) : "memory");
-}
-
-// the same for COLS (8 or 16) columns
+// One row of COLS accumulator columns; the registers hold the values after the next tcgen05.wait::ld.
 __device__ __forceinline__ void tmem_ld_cols_nowait(uint32_t taddr, uint32_t* r) {
-    if constexpr (COLS == 16) {
-        tmem_ld16_nowait(taddr, r);
-    } else {
-        static_assert(COLS == 8 || COLS == 16, "a warp takes 8 or 16 of every 32 columns");
-        asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                     : "r"(taddr) : "memory");
-    }
+    static_assert(COLS == 8, "a warp takes 8 of every 32 columns");
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "r"(taddr) : "memory");
 }
 
 // The two special-function results of a SwiGLU output as single instructions: without .ftz each of them comes with
@@ -186,46 +174,46 @@ struct Gemm2Args {
 };
 
 // The loads issued so far have arrived.  The registers pass through the statement so that no use of them is
-// scheduled ahead of it (the compiler sees no other dependence between the load, the wait and the use).
-__device__ __forceinline__ void tmem_wait_ld(uint32_t* r) {
-    asm volatile("tcgen05.wait::ld.sync.aligned;"
-                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-                   "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
-                 :: "memory");
-}
-__device__ __forceinline__ void tmem_wait_ld8(uint32_t* r) {
+// scheduled ahead of it (the compiler sees no other dependence between the load, the wait and the use); pin_cols does
+// the same for a second set of registers loaded before the wait.
+__device__ __forceinline__ void tmem_wait_ld_cols(uint32_t* r) {
     asm volatile("tcgen05.wait::ld.sync.aligned;"
                  : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]) :: "memory");
 }
-template <int BN, int STAGES, bool DUAL, bool INTO = false>
+__device__ __forceinline__ void pin_cols(uint32_t* r) {
+    asm volatile("" : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]) :: "memory");
+}
+
+template <int BN, int STAGES, int DUAL, bool INTO = false>
 struct Smem2 {
-    static constexpr int A_BYTES = BM * BK * 2;                   // 128 weight rows (DUAL: 64 gate rows, then 64 up rows)
+    static constexpr int ACCS = DUAL == 2 ? 2 : 1;                // accumulators of a tile (DUAL 2: gate and up apart)
+    static constexpr int A_BYTES = BM * BK * 2;                   // 128 weight rows (DUAL 1: 64 gate rows, then 64 up rows)
     static constexpr int B_BYTES = (BN / 2) * BK * 2;             // this CTA's half of the token tile
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGE_BYTES = ACCS * A_BYTES + B_BYTES;
     static constexpr int STG_OFFSET = STAGES * STAGE_BYTES;
     // transposition buffers: INTO two of [32 tokens][128 rows] float32 for all; else two of [COLS tokens][32 rows] bf16
-    // per storing warp.  DUAL: behind them the exchange buffers, two of [COLS tokens][32 rows] float32 per up warp.
+    // per storing warp.  DUAL 1: behind them the exchange buffers, two of [COLS tokens][32 rows] float32 per up warp.
     static constexpr int STG_BYTES = INTO ? 2 * CHUNK * BM * 4 : (EPI_THREADS / 32) * 2 * COLS * 32 * 2;
     static constexpr int XCH_OFFSET = STG_OFFSET + STG_BYTES;
-    static constexpr int XCH_BYTES = DUAL ? (EPI_THREADS / 64) * 2 * COLS * 32 * 4 : 0;
+    static constexpr int XCH_BYTES = DUAL == 1 ? (EPI_THREADS / 64) * 2 * COLS * 32 * 4 : 0;
     static constexpr int BAR_OFFSET = XCH_OFFSET + XCH_BYTES;
     static constexpr int N_BARS = 2 * STAGES + 4;
     static constexpr int TOTAL = BAR_OFFSET + N_BARS * 8 + 16 + 1024;   // + slack to align the base
-    static constexpr int ACC_COLS = BN;                           // tensor-memory columns of one accumulator buffer
-    static constexpr int NBUF = 512 / ACC_COLS;                   // buffers in the 512 columns of tensor memory
-    static constexpr int MROWS = DUAL ? BM / 2 : BM;              // output rows of one CTA's tile
-    static_assert(ACC_COLS == 256, "two accumulator buffers fill tensor memory");
+    static constexpr int ACC_COLS = ACCS * BN;                    // tensor-memory columns of one accumulator buffer
+    static constexpr int NBUF = 512 / ACC_COLS;                   // buffers in the 512 columns of tensor memory: 2 or 1
+    static constexpr int MROWS = DUAL == 1 ? BM / 2 : BM;         // output rows of one CTA's tile
+    static_assert(ACC_COLS == 256 || ACC_COLS == 512, "an accumulator buffer is a half or the whole of tensor memory");
     static_assert(TOTAL <= 232448, "a block's shared memory");
 };
 
-template <int BN, int STAGES, bool DUAL, bool INTO = false>
+template <int BN, int STAGES, int DUAL, bool INTO = false>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                 const __grid_constant__ CUtensorMap map_out, Gemm2Args g) {
     LLB_STAMPS_BEGIN();
     if (threadIdx.x == 64) LLB_STAMP(0);
     using S = Smem2<BN, STAGES, DUAL, INTO>;
-    constexpr int ACC_COLS = S::ACC_COLS, NBUF = S::NBUF, MROWS = S::MROWS;
+    constexpr int ACCS = S::ACCS, ACC_COLS = S::ACC_COLS, NBUF = S::NBUF, MROWS = S::MROWS;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* gen_base = smem_raw + (base - smem_u32(smem_raw));
@@ -280,8 +268,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         for (int i = 0; i < prefetched; ++i) {
             const uint32_t dst = base + i * S::STAGE_BYTES, bar = full0 + 8 * i;
             if (leader) mbar_expect_tx(bar_full + 8 * i, 2u * S::STAGE_BYTES);
-            tma_load_2d_pair(dst, &map_w, bar, (first_kb0 + i) * BK, m0, HINT_EVICT_FIRST);      // DUAL: the map's box is 64 rows
-            if (DUAL) tma_load_2d_pair(dst + S::A_BYTES / 2, &map_w, bar, (first_kb0 + i) * BK, m0 + g.dual_offset, HINT_EVICT_FIRST);
+            tma_load_2d_pair(dst, &map_w, bar, (first_kb0 + i) * BK, m0, HINT_EVICT_FIRST);      // DUAL 1: the map's box is 64 rows
+            if (DUAL) tma_load_2d_pair(dst + S::A_BYTES / (3 - DUAL), &map_w, bar, (first_kb0 + i) * BK, m0 + g.dual_offset, HINT_EVICT_FIRST);
         }
     }
     llb_grid_dependency_sync();      // from here on memory written by earlier kernels is touched
@@ -293,7 +281,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         if (elect_one()) {   // the activations of the k-blocks whose weight is on its way already
             const int n0 = ((pair % g.n_tiles) % g.tok_tiles) * BN + (int)rank * (BN / 2);
             for (int i = 0; i < prefetched; ++i)
-                tma_load_2d_pair(base + i * S::STAGE_BYTES + S::A_BYTES, &map_x, full0 + 8 * i, (first_kb0 + i) * BK, n0, HINT_EVICT_LAST);
+                tma_load_2d_pair(base + i * S::STAGE_BYTES + ACCS * S::A_BYTES, &map_x, full0 + 8 * i, (first_kb0 + i) * BK, n0, HINT_EVICT_LAST);
         }
         __syncwarp();
         int it = prefetched;
@@ -313,8 +301,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     const uint32_t dst = base + s * S::STAGE_BYTES, bar = full0 + 8 * s;
                     if (leader) mbar_expect_tx(bar_full + 8 * s, 2u * S::STAGE_BYTES);
                     tma_load_2d_pair(dst, &map_w, bar, kb * BK, m0, HINT_EVICT_FIRST);
-                    if (DUAL) tma_load_2d_pair(dst + S::A_BYTES / 2, &map_w, bar, kb * BK, m0 + g.dual_offset, HINT_EVICT_FIRST);
-                    tma_load_2d_pair(dst + S::A_BYTES, &map_x, bar, kb * BK, n0, HINT_EVICT_LAST);
+                    if (DUAL) tma_load_2d_pair(dst + S::A_BYTES / (3 - DUAL), &map_w, bar, kb * BK, m0 + g.dual_offset, HINT_EVICT_FIRST);
+                    tma_load_2d_pair(dst + ACCS * S::A_BYTES, &map_x, bar, kb * BK, n0, HINT_EVICT_LAST);
                 }
                 __syncwarp();
             }
@@ -331,7 +319,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             // ---- tensor-core issue for both SMs: the warp waits as a whole, one elected lane issues; the operand
             // descriptors are made once and a stage's or an instruction's own differ from them by a constant
             const uint32_t idesc = umma_idesc_pair(BN);
-            const uint64_t a_desc0 = umma_desc(base), b_desc0 = umma_desc(base + S::A_BYTES);
+            const uint64_t a_desc0 = umma_desc(base), b_desc0 = umma_desc(base + ACCS * S::A_BYTES);
             int it = 0, ti = 0;
             bool ok = true;
             for (int u = pair; u < n_units && ok; u += g.n_pairs, ++ti) {
@@ -351,12 +339,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     if (elect_one()) {
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         const uint64_t so = (uint64_t)(s * (S::STAGE_BYTES >> 4));
-                        const uint64_t ad = a_desc0 + so, bd = b_desc0 + so;
+                        const uint64_t ad = a_desc0 + so, bd = b_desc0 + so, ad2 = ad + (uint64_t)(S::A_BYTES >> 4);
 #pragma unroll
                         for (int k = 0; k < BK / UMMA_K; ++k) {
                             const uint32_t accumulate = (kb > kb0 || k > 0) ? 1u : 0u;
                             const uint64_t step = (uint64_t)(k * UMMA_K * 2 >> 4);      // the start address field counts 16 bytes
                             umma_pair(acc, ad + step, bd + step, idesc, accumulate);
+                            if (DUAL == 2) umma_pair(acc + BN, ad2 + step, bd + step, idesc, accumulate);
                         }
                         umma_commit_both(bar_empty + 8 * s);
                     }
@@ -370,9 +359,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         __syncwarp();
     } else {
         // ---- epilogue: warp w may read tensor-memory lanes 32 (w mod 4) .. + 31; a thread owns one weight row and COLS of
-        // every 32 columns.  DUAL: lanes 0-63 hold gate rows and lanes 64-127 the up rows of the same outputs, so a warp
+        // every 32 columns.  DUAL 1: lanes 0-63 hold gate rows and lanes 64-127 the up rows of the same outputs, so a warp
         // of the upper half hands its values to the warp of the lower half with the same rows and columns through shared
-        // memory, with a barrier of the two warps per chunk; the lower warps compute and store.
+        // memory, with a barrier of the two warps per chunk; the lower warps compute and store.  DUAL 2: a thread reads
+        // its row's gate value from the first accumulator and its up value from the second.
         const int et = tid - 64;                                  // 0 .. EPI_THREADS - 1
         const int q = warp & 3, share = (warp - 2) >> 2;
         const int h = share * COLS;
@@ -381,11 +371,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
         const uint32_t acc_empty0 = mapa(bar_acc_empty, 0);
         bf16* stg = reinterpret_cast<bf16*>(gen_base + S::STG_OFFSET);
         float* stgf = reinterpret_cast<float*>(gen_base + S::STG_OFFSET);          // INTO: [2][32 tokens][128 rows] float32
-        const bool up_warp = DUAL && q >= 2;
-        const int xpair = (q & 1) * EPI_SHARE + share;            // DUAL: the two warps' buffers and barrier (ids 2 ..)
+        const bool up_warp = DUAL == 1 && q >= 2;
+        const int xpair = (q & 1) * EPI_SHARE + share;            // DUAL 1: the two warps' buffers and barrier (ids 2 ..)
         float* xch = reinterpret_cast<float*>(gen_base + S::XCH_OFFSET) + xpair * (2 * COLS * 32);
-        const int out_row = DUAL ? (q & 1) * 32 : q * 32;         // this warp's first output row within the CTA's tile
-        const bool stamper = tid == (DUAL ? 128 : 64);            // (a storing warp's first thread)
+        const int out_row = DUAL == 1 ? (q & 1) * 32 : q * 32;    // this warp's first output row within the CTA's tile
+        const bool stamper = tid == (DUAL == 1 ? 128 : 64);       // (a storing warp's first thread)
         int ti = 0, chunk_i = 0;
         for (int u = pair; u < n_units; u += g.n_pairs, ++ti) {
             const int buf = ti % NBUF, t = u % g.n_tiles;
@@ -405,16 +395,23 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t acc = lane_addr + buf * ACC_COLS;
             // the next columns are on their way from tensor memory while these are worked on
-            uint32_t nxt0[COLS];
+            uint32_t nxt0[COLS], nxt1[COLS];
             tmem_ld_cols_nowait(acc + h, nxt0);
+            if (DUAL == 2) tmem_ld_cols_nowait(acc + BN + h, nxt1);
 #pragma unroll 1
             for (int c = 0; c < BN; c += CHUNK, ++chunk_i) {
-                float v0[COLS];
-                if constexpr (COLS == 16) tmem_wait_ld(nxt0);
-                else tmem_wait_ld8(nxt0);
+                float v0[COLS], v1[COLS];
+                tmem_wait_ld_cols(nxt0);
+                if (DUAL == 2) pin_cols(nxt1);                     // (loaded before the wait: valid behind it)
 #pragma unroll
-                for (int j = 0; j < COLS; ++j) v0[j] = __uint_as_float(nxt0[j]);
-                if (c + CHUNK < BN) tmem_ld_cols_nowait(acc + c + CHUNK + h, nxt0);
+                for (int j = 0; j < COLS; ++j) {
+                    v0[j] = __uint_as_float(nxt0[j]);
+                    if (DUAL == 2) v1[j] = __uint_as_float(nxt1[j]);
+                }
+                if (c + CHUNK < BN) {
+                    tmem_ld_cols_nowait(acc + c + CHUNK + h, nxt0);
+                    if (DUAL == 2) tmem_ld_cols_nowait(acc + BN + c + CHUNK + h, nxt1);
+                }
                 if (INTO) {
                     // this K range's partial sums of 32 tokens x 128 rows, laid out as they lie in the stream, then one
                     // reduction into the stream.  The other buffer is written right after the barrier below (the next
@@ -436,7 +433,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
                     if (stamper && ti == 0 && c == CHUNK) LLB_STAMP(4);
                     continue;
                 }
-                if (DUAL) {
+                if (DUAL == 2) {
+#pragma unroll
+                    for (int j = 0; j < COLS; ++j)                                  // up * gate / (1 + exp(-gate))
+                        v0[j] = v1[j] * v0[j] * rcp_ftz(1.0f + ex2_ftz(-1.4426950408889634f * v0[j]));
+                } else if (DUAL == 1) {
                     // The up warp writes buffer chunk_i & 1 and meets the gate warp at their barrier; it writes that buffer
                     // again two chunks on, behind the next chunk's barrier, which the gate warp reaches after these reads.
                     float* xb = xch + (chunk_i & 1) * (COLS * 32);
@@ -498,7 +499,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant
     if (warp == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512u) : "memory");
 }
 
-template <int BN, int STAGES, bool DUAL, bool INTO = false>
+template <int BN, int STAGES, int DUAL, bool INTO = false>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const CUtensorMap& mo, const Gemm2Args& g, cudaStream_t stream) {
     auto k = gemm_tc2_kernel<BN, STAGES, DUAL, INTO>;
     constexpr int smem = Smem2<BN, STAGES, DUAL, INTO>::TOTAL;
@@ -554,7 +555,12 @@ LLB_API int llb_gemm_tc2(const void* X, const void* W, const void* bias, int bia
     g.bias = bias; g.bias_dtype = bias_dtype; g.Y = (bf16*)Y;
     g.T = T; g.K = K; g.ldy = ldy; g.rows_out = rows_out; g.dual_offset = dual_offset;
     g.tok_tiles = (T + bn - 1) / bn;
-    const int tile_rows = dual ? BM : 2 * BM;          // output rows of a pair's tile (gate/up: 64 gate and 64 up rows per CTA)
+    // gate/up: with a short K range the one-accumulator variant, whose epilogue runs beside the next tile's products
+    // (64 gate and 64 up rows per CTA); with a long one the two-accumulator variant, which takes a third less from the
+    // L2 per FLOP and loses little to its exposed epilogue (a prefill step of 2,048 tokens with the first variant: 4 %
+    // shorter at K 1536, I 8960; 4 % longer at K 3584, I 18944; the same at K 5120, I 27648).
+    const bool side_by_side = dual && K <= 2048;
+    const int tile_rows = side_by_side ? BM : 2 * BM;  // output rows of a pair's tile
     const long long tiles = (long long)((rows_out + tile_rows - 1) / tile_rows) * g.tok_tiles;
     if (tiles > (1 << 30)) return (int)cudaErrorInvalidValue;
     g.n_tiles = (int)tiles;
@@ -563,11 +569,12 @@ LLB_API int llb_gemm_tc2(const void* X, const void* W, const void* bias, int bia
     g.ksplit = 1;
     g.chunk_kb = (K + BK - 1) / BK;
     CUtensorMap mw, mx;
-    int rc = llb_tma::bf16_map_64(W, N, K, K, dual ? BM / 2 : BM, &mw);
+    int rc = llb_tma::bf16_map_64(W, N, K, K, side_by_side ? BM / 2 : BM, &mw);
     if (rc) return rc;
     rc = llb_tma::bf16_map_64(X, T, K, ldx, bn / 2, &mx);
     if (rc) return rc;
-    return dual ? launch<256, 6, true>(mw, mx, mw, g, stream) : launch<256, 6, false>(mw, mx, mw, g, stream);
+    if (side_by_side) return launch<256, 6, 1>(mw, mx, mw, g, stream);
+    return dual ? launch<256, 4, 2>(mw, mx, mw, g, stream) : launch<256, 6, 0>(mw, mx, mw, g, stream);
 }
 
 // K ranges per tile for llb_gemm_tc2_into: the count (1 to 4) that minimises rounds of units times the length of a
@@ -620,5 +627,5 @@ LLB_API int llb_gemm_tc2_into(const void* X, const void* W, const void* bias, in
     if (rc) return rc;
     rc = llb_tma::f32_map_plain(stream_, T, N, lds, BM, CHUNK, &mo);
     if (rc) return rc;
-    return launch<256, 6, false, true>(mw, mx, mo, g, stream);
+    return launch<256, 6, 0, true>(mw, mx, mo, g, stream);
 }

@@ -380,9 +380,11 @@ def test_linear_on_paired_sms_and_on_single_ones(T, N, K):
     assert kernels.tc_error(DEV) == 0
 
 
-@pytest.mark.parametrize("T,I,K", [(300, 264, 200), (257, 128, 64), (1000, 136, 96), (1500, 1000, 520)])
+@pytest.mark.parametrize("T,I,K", [(300, 264, 200), (257, 128, 64), (1000, 136, 96), (1500, 1000, 520), (300, 264, 2112)])
 @pytest.mark.parametrize("plan", [None, ("pair",), (256, 1)])
 def test_linear_swiglu_on_paired_sms_and_on_single_ones(T, I, K, plan):
+    """(The paired kernel has two gate/up variants: gate and up rows side by side in one accumulator up to K = 2,048,
+    two accumulators beyond; the last case takes the second.)"""
     from llaisys_b200 import kernels
     x, w, _ = _tc_case(T, 2 * I, K, T + I)
     w = (w.float() * 4).to(torch.bfloat16)
