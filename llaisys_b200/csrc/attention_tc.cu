@@ -237,9 +237,10 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = *tmem_slot;
-    llb_grid_dependency_sync();
 
-    // ---- which rows, which keys
+    // ---- which rows, which keys.  The step's index arrays (sequence starts and lengths, page tables) reach the device
+    // by a copy that has ended before the step's first kernel starts, so they are read here, while the kernel before
+    // this one may still be running; its output (queries, and the keys and values it appended) only behind the dependency.
     const int b = blockIdx.z, head = blockIdx.x;
     const int tok0 = p.seq_start[b], n_new = p.seq_start[b + 1] - tok0, len_before = p.seq_len_before[b];
     uint32_t rank = 0;
@@ -259,6 +260,10 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         n_tiles = q + ((int)rank < r ? 1 : 0);
     }
     const int* table = p.page_table + (size_t)b * p.table_stride;
+    auto page_row = [&](int i) { return i < n_tiles ? (table[tile_lo + i] * p.nkvh + kvh) * BKV : 0; };
+    int r0 = 0, r1 = 0, r2 = 0, r3 = 0;                             // the issuing warp: page rows of its first four tiles
+    if (warp == 4) { r0 = page_row(0); r1 = page_row(1); r2 = page_row(2); r3 = page_row(3); }
+    llb_grid_dependency_sync();
     bool failed = false;
     float m = -INFINITY, l = 0.f;                                   // row threads: the exponent base of the row, its sum
     const uint32_t lane_addr = tmem + ((uint32_t)((warp & 3) * 32) << 16);
@@ -270,7 +275,6 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         const uint64_t q_desc = desc_kmajor(base), k_desc0 = desc_kmajor(base + OFF_K),
                        v_desc0 = desc_mnmajor(base + OFF_V, BKV * 128);
         constexpr uint32_t IDESC_S = idesc_f16(BKV, false), IDESC_O = idesc_f16(DH, true);
-        auto page_row = [&](int i) { return i < n_tiles ? (table[tile_lo + i] * p.nkvh + kvh) * BKV : 0; };
         // keys / values of one tile into `stage`; the bytes count on `bar`, which also gets one arrival
         auto issue_k = [&](int stage, int row, uint32_t bar) {
             mbar_expect_tx(bar, KV_BYTES);
@@ -295,14 +299,13 @@ attn_tc_prefill_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                      kd + (uint64_t)(((ks / 4) * (BKV * 128) + (ks % 4) * 32) >> 4), IDESC_S, ks > 0 ? 1u : 0u);
             umma_commit(bar_s + 8 * buf);
         };
-        int r1 = page_row(1), r2 = page_row(2), r3 = page_row(3);     // page rows of tiles i + 1, i + 2, i + 3
+        // r1, r2, r3: page rows of tiles i + 1, i + 2, i + 3
         if (n_tiles > 0) {
             if (elect_one()) {
                 mbar_expect_tx(bar_q, Q_BYTES);
 #pragma unroll
                 for (int blk = 0; blk < NBLK; ++blk)
                     tma_load_2d(base + blk * (BQ * 128), &map_q, bar_q, head * DH + blk * 64, tok0 + t0);
-                const int r0 = page_row(0);
                 // the first two key tiles have a barrier of their own (one arrival, the bytes of both)
                 mbar_expect_tx(bar_k01, KV_BYTES * min(2, n_tiles));
 #pragma unroll

@@ -429,21 +429,35 @@ rope_append_vec_kernel(bf16* __restrict__ qkv, int row_stride, int nh, int nkvh,
                        const int* __restrict__ seq_start, const int* __restrict__ seq_len_before,
                        bf16* __restrict__ kpool, bf16* __restrict__ vpool, const int* __restrict__ page_table,
                        int table_stride, int ring, int* err) {
-    llb_grid_dependency_sync();
+    // The step's index arrays reach the device by a copy that has ended before the step's first kernel starts, and the
+    // rotation tables are older still, so they are read while the kernel before this one may still be running; its
+    // output, the rows of qkv, only behind the dependency.
     const int t = blockIdx.x, pos = tok_pos[t], half = dh >> 1, vec_per_half = half >> 3;
     bf16* row = qkv + (size_t)t * row_stride;
-    const int* table = nullptr;
     bool store = false;
+    size_t page_base = 0;                     // element offset of the token's row of kv head 0 in the pools
     if (APPEND) {
         const int s = tok_seq[t];
-        table = page_table + (size_t)s * table_stride;
+        const int* table = page_table + (size_t)s * table_stride;
         const int last = seq_len_before[s] + (seq_start[s + 1] - seq_start[s]) - 1;
         store = (pos / LLB_PAGE) + ring > (last / LLB_PAGE);
+        if (store) page_base = paged_row(table, ring, pos, 0, nkvh, dh);
     }
     if (ROPE && (pos < 0 || pos >= table_rows)) {
         if (threadIdx.x == 0) atomicExch(err, 2);
         return;
     }
+    const size_t head_step = (size_t)LLB_PAGE * dh;            // from one kv head's row to the next one's
+    // the angles of this thread's first work item
+    float4 pc0 = {}, pc1 = {}, ps0 = {}, ps1 = {};
+    if (ROPE && (int)threadIdx.x < (nh + nkvh) * vec_per_half) {
+        const int j = ((int)threadIdx.x % vec_per_half) * 8;
+        pc0 = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + j);
+        pc1 = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + j + 4);
+        ps0 = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + j);
+        ps1 = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + j + 4);
+    }
+    llb_grid_dependency_sync();
     // work items: (nh + nkvh) heads x vec_per_half pieces of rotation (or key copy), then nkvh x 2 vec_per_half of values
     const int n_rot = (nh + nkvh) * vec_per_half, n_val = APPEND && store ? nkvh * 2 * vec_per_half : 0;
     for (int i = threadIdx.x; i < n_rot + n_val; i += blockDim.x) {
@@ -453,10 +467,13 @@ rope_append_vec_kernel(bf16* __restrict__ qkv, int row_stride, int nh, int nkvh,
             bf16* x = row + h * dh;
             uint4 lo = *reinterpret_cast<const uint4*>(x + j), hi = *reinterpret_cast<const uint4*>(x + j + half);
             if (ROPE) {
-                const float4 c0 = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + j),
-                             c1 = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + j + 4),
-                             s0 = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + j),
-                             s1 = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + j + 4);
+                float4 c0 = pc0, c1 = pc1, s0 = ps0, s1 = ps1;
+                if (i != (int)threadIdx.x) {
+                    c0 = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + j);
+                    c1 = *reinterpret_cast<const float4*>(cos_t + (size_t)pos * half + j + 4);
+                    s0 = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + j);
+                    s1 = *reinterpret_cast<const float4*>(sin_t + (size_t)pos * half + j + 4);
+                }
                 const float c[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
                 const float sn[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
                 bf16* a = reinterpret_cast<bf16*>(&lo);
@@ -471,13 +488,13 @@ rope_append_vec_kernel(bf16* __restrict__ qkv, int row_stride, int nh, int nkvh,
                 *reinterpret_cast<uint4*>(x + j + half) = hi;
             }
             if (APPEND && store && h >= nh) {
-                const size_t o = paged_row(table, ring, pos, h - nh, nkvh, dh);
+                const size_t o = page_base + (size_t)(h - nh) * head_step;
                 *reinterpret_cast<uint4*>(kpool + o + j) = lo;
                 *reinterpret_cast<uint4*>(kpool + o + j + half) = hi;
             }
         } else {
             const int v = i - n_rot, h = v / (2 * vec_per_half), j = (v - h * 2 * vec_per_half) * 8;
-            *reinterpret_cast<uint4*>(vpool + paged_row(table, ring, pos, h, nkvh, dh) + j) =
+            *reinterpret_cast<uint4*>(vpool + page_base + (size_t)h * head_step + j) =
                 *reinterpret_cast<const uint4*>(row + (nh + nkvh + h) * dh + j);
         }
     }
