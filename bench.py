@@ -267,6 +267,9 @@ STAMP_NAMES = {
     "gate_up": ("gemm_tc2.cu", ["start", "first tile: accumulators ready", "first 32 tokens computed", "(warp joined)", "first 32 tokens stored",
                                 "all tokens stored", "accumulators handed back", "second tile: accumulators ready",
                                 "second tile: accumulators handed back"]),
+    "qkv": ("gemm_tc2.cu", ["start", "first tile: accumulator ready", "first 32 tokens computed", "(warp joined)", "first 32 tokens stored",
+                            "all tokens stored", "accumulator handed back", "second tile: accumulator ready",
+                            "second tile: accumulator handed back"]),
     "down": ("gemm_tc2.cu", ["start", "first unit: accumulator ready", "second 32 tokens staged", "the reduction before has read its buffer",
                              "reduction issued", "all reductions issued", "accumulator handed back", "second unit: accumulator ready",
                              "second unit: accumulator handed back"]),
@@ -286,7 +289,7 @@ def stamps_run(args, model, cfg, rng) -> int:
     from llaisys_b200.engine import Engine, StepEntry
     from llaisys_b200.kernels import ops
 
-    if args.stamps in ("gate_up", "down"):
+    if args.stamps in ("gate_up", "down", "qkv"):
         # one of the prefill's two largest products alone (--tokens tokens on pairs of SMs): how long a tile's epilogue
         # takes (and, for gate/up, keeps the tensor cores waiting), in SM cycles after the block started
         from llaisys_b200 import kernels
@@ -297,6 +300,14 @@ def stamps_run(args, model, cfg, rng) -> int:
 
             def product():
                 kernels.linear_swiglu(x, w)
+        elif args.stamps == "qkv":
+            n_qkv = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * cfg.head_dim
+            x = torch.randn(args.tokens, cfg.hidden_size, device="cuda:0", dtype=torch.bfloat16)
+            w = torch.randn(n_qkv, cfg.hidden_size, device="cuda:0", dtype=torch.bfloat16) * 0.02
+            bias = torch.randn(n_qkv, device="cuda:0", dtype=torch.bfloat16)
+
+            def product():
+                kernels.linear(x, w, bias)
         else:
             x = torch.randn(args.tokens, cfg.intermediate_size, device="cuda:0", dtype=torch.bfloat16)
             w = torch.randn(cfg.hidden_size, cfg.intermediate_size, device="cuda:0", dtype=torch.bfloat16) * 0.02
@@ -615,10 +626,10 @@ def main() -> int:
     ap.add_argument("--prompt-len", type=int, default=None,
                     help="for measurements beside the reported one: tokens every sequence holds before decoding, and tokens of "
                          "the timed prefill step (default 2,048; the cache is sized for twice as many per sequence)")
-    ap.add_argument("--stamps", choices=["gemm", "attention", "mlp", "gate_up", "down"], default=None,
+    ap.add_argument("--stamps", choices=["gemm", "attention", "mlp", "gate_up", "down", "qkv"], default=None,
                     help="cycle stamps from inside one kernel of the decode step (the q/k/v product, decode attention or the "
-                         "one-launch feed-forward), in its place in the step replayed from its CUDA graph, or (gate_up, down) from the "
-                         "prefill's gate/up or down product alone at --tokens tokens; builds that kernel with -DLLB_STAMPS=1")
+                         "one-launch feed-forward), in its place in the step replayed from its CUDA graph, or (gate_up, down, qkv) from one "
+                         "of the prefill's products alone at --tokens tokens; builds that kernel with -DLLB_STAMPS=1")
     ap.add_argument("--timeline", choices=["decode", "prefill"], default=None,
                     help="print the per-kernel timeline of a step (torch.profiler, no ncu) instead of measuring")
     args = ap.parse_args()
