@@ -361,6 +361,20 @@ def _gemm_tc(x, weight, bias, out, dual_offset=0, plan=None):
     if plan is not None and plan[0] == "pair":
         return _gemm_tc_pair(x, weight, bias, out, dual_offset)
     scratch, counters, err = _tc_resources(x.device)
+    # gate/up for 17 to 64 tokens: a block per 64 outputs (gate and up rows side by side in one accumulator), twice as
+    # many blocks as with a tile of 128 gate rows, which without a K split leaves half of the SMs idle at these sizes
+    side_by_side = plan is not None and plan[0] == "gateup"
+    if plan is None and dual_offset and 16 < M <= 64:
+        side_by_side = True
+    if side_by_side and dual_offset and bias is None and _pair_ok(out, dual_offset):
+        bn = plan[1] if plan is not None else (32 if M <= 32 else 64)
+        f = _fn(_stamped("gemm_tc.cu"), "llb_gemm_tc_gateup",
+                [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+        _check(f(_ptr(x), _ptr(weight), _ptr(out), M, dual_offset, K, x.stride(0), out.stride(0), bn, _ptr(err), _stream()),
+               "gate/up (tensor cores, rows side by side)")
+        return
+    if side_by_side:
+        plan = None
     plan = plan or tc_plan(M, dual_offset or N, K, _sm_count(x.device), bool(dual_offset))
     bn, splits = plan[0], plan[1]
     cluster = plan[2] if len(plan) > 2 else 1            # (bn, splits, 0) forces the reduction through scratch

@@ -426,7 +426,10 @@ def test_linear_tensor_cores_sixteen_splits_in_one_cluster(bn, T):
 
 @pytest.mark.parametrize("T,I,K,plan", [(8, 8960, 1536, None), (3, 200, 72, None), (70, 136, 96, None), (300, 264, 200, None),
                                         (20, 300, 712, (32, 3)), (20, 300, 712, (256, 2)), (130, 300, 712, (128, 4)),
-                                        (130, 300, 712, (128, 4, 0)), (9, 300, 1096, (16, 8)), (40, 136, 520, (64, 2))])
+                                        (130, 300, 712, (128, 4, 0)), (9, 300, 1096, (16, 8)), (40, 136, 520, (64, 2)),
+                                        (17, 8960, 1536, None), (64, 8960, 1536, None), (40, 136, 520, (64, 1)),
+                                        (20, 72, 200, ("gateup", 32)), (33, 200, 72, ("gateup", 64)), (100, 328, 1096, ("gateup", 64)),
+                                        (64, 64, 64, ("gateup", 64)), (70, 1000, 520, ("gateup", 32)), (50, 264, 2112, ("gateup", 64))])
 def test_linear_swiglu_tensor_cores(T, I, K, plan):
     from llaisys_b200 import kernels
     x, w, _ = _tc_case(T, 2 * I, K, T + I)
