@@ -42,12 +42,8 @@ __device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
     return (b.v > a.v || (b.v == a.v && b.i < a.i)) ? b : a;
 }
 
-__device__ ArgMax block_argmax(const float* row, int V, ArgMax* red) {
-    ArgMax best = {-INFINITY, INT_MAX};
-    for (int i = threadIdx.x; i < V; i += SB) {
-        float v = row[i];
-        if (v > best.v || best.i == INT_MAX) best = {v, i};     // increasing i: first maximum stays
-    }
+// the best of the block's threads' candidates, in every thread
+__device__ ArgMax block_best(ArgMax best, ArgMax* red) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         ArgMax other = {__shfl_xor_sync(0xffffffffu, best.v, o), __shfl_xor_sync(0xffffffffu, best.i, o)};
@@ -71,6 +67,15 @@ __device__ ArgMax block_argmax(const float* row, int V, ArgMax* red) {
     return best;
 }
 
+__device__ ArgMax block_argmax(const float* row, int V, ArgMax* red) {
+    ArgMax best = {-INFINITY, INT_MAX};
+    for (int i = threadIdx.x; i < V; i += SB) {
+        float v = row[i];
+        if (v > best.v || best.i == INT_MAX) best = {v, i};     // increasing i: first maximum stays
+    }
+    return block_best(best, red);
+}
+
 __global__ void __launch_bounds__(SB) argmax_kernel(const float* __restrict__ logits, long long ld,
                                                     int V, int* __restrict__ out) {
     __shared__ ArgMax red[32];
@@ -79,10 +84,80 @@ __global__ void __launch_bounds__(SB) argmax_kernel(const float* __restrict__ lo
     if (threadIdx.x == 0) out[blockIdx.x] = b.i;
 }
 
+// Few rows of a wide vocabulary (a decode step: 8 rows of 151,936 logits) leave most SMs without a block when a block
+// takes a whole row: 11 us for 4.9 MB.  Here gridDim.x blocks share a row; each leaves its part's first maximum in
+// `part`, and the block that finds itself the last of its row (a counter per row, back at zero afterwards) takes the
+// best of the parts.  The order in which the blocks finish does not change the result: ties go to the lower index.
+constexpr int SPLIT_THREADS = 256, MAX_PARTS = 64;
+__global__ void __launch_bounds__(SPLIT_THREADS)
+argmax_split_kernel(const float* __restrict__ logits, long long ld, int V, int chunk, ArgMax* __restrict__ part,
+                    int* __restrict__ counters, int* __restrict__ out) {
+    __shared__ ArgMax red[32];
+    __shared__ int s_last;
+    llb_grid_dependency_sync();
+    const int r = blockIdx.y, c = blockIdx.x, C = gridDim.x, tid = threadIdx.x;
+    const int lo = min(V, c * chunk), hi = min(V, lo + chunk);
+    const float* row = logits + (size_t)r * ld;
+    ArgMax best = {-INFINITY, INT_MAX};
+    auto take = [&](float v, int i) { if (v > best.v || best.i == INT_MAX) best = {v, i}; };      // increasing i: first maximum stays
+    int done = lo;
+    if ((reinterpret_cast<uintptr_t>(row + lo) & 15) == 0) {
+        const int n4 = (hi - lo) >> 2;
+        const float4* row4 = reinterpret_cast<const float4*>(row + lo);
+        for (int i = tid; i < n4; i += SPLIT_THREADS) {
+            const float4 v = row4[i];
+            const int at = lo + 4 * i;
+            take(v.x, at); take(v.y, at + 1); take(v.z, at + 2); take(v.w, at + 3);
+        }
+        done = lo + 4 * n4;
+    }
+    for (int i = done + tid; i < hi; i += SPLIT_THREADS) take(row[i], i);      // (a thread's indices still increase)
+    // block_best() reduces over 32 warps' places: the places of the warps this block does not have stay neutral
+    if (tid < 32) red[tid] = {-INFINITY, INT_MAX};
+    __syncthreads();
+    best = block_best(best, red);
+    if (tid == 0) {
+        part[(size_t)r * C + c] = best;
+        __threadfence();
+        s_last = atomicAdd(counters + r, 1) == C - 1;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (tid < 32) {
+        ArgMax b = {-INFINITY, INT_MAX};
+        for (int k = tid; k < C; k += 32) {
+            const volatile ArgMax* q = part + (size_t)r * C + k;
+            ArgMax o = {q->v, q->i};
+            if (o.i != INT_MAX) b = b.i == INT_MAX ? o : better(b, o);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            ArgMax other = {__shfl_xor_sync(0xffffffffu, b.v, o), __shfl_xor_sync(0xffffffffu, b.i, o)};
+            if (other.i != INT_MAX) b = b.i == INT_MAX ? other : better(b, other);
+        }
+        if (tid == 0) {
+            out[r] = b.i;
+            counters[r] = 0;
+        }
+    }
+}
+
 LLB_API int llb_argmax(const float* logits, long long ld, int R, int V, int* out, cudaStream_t stream) {
     if (R == 0) return 0;
     if (V <= 0) return (int)cudaErrorInvalidValue;
     llb_launch(argmax_kernel, dim3(R), dim3(SB), 0, stream, logits, ld, V, out);
+    return llb_status();
+}
+
+// The same with `parts` blocks per row (2 to 64): part [R * parts] pairs of (float, int) of scratch, counters [R] ints
+// that are zero before the call and zero again after it.
+LLB_API int llb_argmax_split(const float* logits, long long ld, int R, int V, int parts, void* part, int* counters, int* out,
+                             cudaStream_t stream) {
+    if (R == 0) return 0;
+    if (V <= 0 || parts < 2 || parts > MAX_PARTS || R > 65535 || !part || !counters) return (int)cudaErrorInvalidValue;
+    const int chunk = (((V + parts - 1) / parts) + 3) & ~3;            // whole 16-byte pieces
+    llb_launch(argmax_split_kernel, dim3(parts, R), dim3(SPLIT_THREADS), 0, stream, logits, ld, V, chunk, (ArgMax*)part, counters, out);
     return llb_status();
 }
 

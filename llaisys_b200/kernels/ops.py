@@ -680,12 +680,26 @@ def attention_decode(qkv, nh, nkvh, dh, kpool, vpool, page_table, ring, seq_star
 
 
 # ------------------------------------------------------------------ choice of the next token
+_argmax_counters = {}          # device -> int32 [4096], zero between launches (the split arg-max's per-row counters)
+
+
 def argmax(logits: torch.Tensor) -> torch.Tensor:
     """int32 index of the first maximum of every row of float32 logits [R, V]."""
     _need_cuda(logits)
     assert logits.dtype == torch.float32 and logits.stride(1) == 1
     R, V = logits.shape
     out = torch.empty((R,), dtype=torch.int32, device=logits.device)
+    # few rows of a wide vocabulary: several blocks share a row, so that the device's SMs all read
+    parts = min(64, (2 * _sm_count(logits.device)) // max(R, 1), V // 2048)
+    if parts >= 2 and R <= 4096:
+        counters = _argmax_counters.get(logits.device)
+        if counters is None:
+            counters = _argmax_counters[logits.device] = torch.zeros(4096, dtype=torch.int32, device=logits.device)
+        part = torch.empty((R * parts, 2), dtype=torch.int32, device=logits.device)
+        f = _fn(load_module("sampling.cu"), "llb_argmax_split",
+                [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+        _check(f(_ptr(logits), logits.stride(0), R, V, parts, _ptr(part), _ptr(counters), _ptr(out), _stream()), "argmax")
+        return out
     f = _fn(load_module("sampling.cu"), "llb_argmax", [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p])
     _check(f(_ptr(logits), logits.stride(0), R, V, _ptr(out), _stream()), "argmax")
     return out

@@ -276,6 +276,25 @@ def test_argmax_first_maximum():
     assert got == [plain.argmax(r) for r in x] and got[1] == 77 and got[2] == 0
 
 
+@pytest.mark.parametrize("R,V,pad", [(8, 151936, 0), (1, 151937, 3), (3, 40001, 1), (64, 20000, 0), (300, 4100, 2)])
+def test_argmax_of_few_wide_rows(R, V, pad):
+    """Few rows of a wide vocabulary go to several blocks per row: the first maximum, also where the maxima of a tie
+    lie in different blocks' parts, at a part's first and last place, and with rows that start off 16-byte boundaries."""
+    from llaisys_b200 import kernels
+    rng = np.random.default_rng(R + V)
+    x = rng.normal(size=(R, V + pad)).astype(np.float32)
+    x[0, V - 1] = 40.0                                   # the very last place
+    if R > 1:
+        x[1, 5] = x[1, V // 2] = x[1, V - 2] = 30.0      # a tie across parts: the first wins
+    if R > 2:
+        x[2, :V] = -np.inf                               # nothing but -inf: index 0
+    wide = torch.from_numpy(x).to(DEV)
+    for _ in range(2):                                   # the counters are back at zero after a launch
+        got = kernels.argmax(wide[:, :V]).tolist()
+        assert got == [plain.argmax(r[:V]) for r in x]
+    assert got[0] == V - 1 and (R < 2 or got[1] == 5) and (R < 3 or got[2] == 0)
+
+
 @pytest.mark.parametrize("V", [257, 5000, 151936])
 @pytest.mark.parametrize("temperature,top_k,top_p", [(1.0, 0, 1.0), (0.7, 0, 1.0), (1.0, 50, 1.0), (1.0, 0, 0.8),
                                                      (0.8, 50, 0.8), (1.3, 7, 0.3), (1.0, 1, 1.0), (0.0, 0, 1.0)])
